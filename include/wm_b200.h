@@ -1,0 +1,191 @@
+/*
+ * wm_b200.h -- C ABI of the B200 (sm_100a) attention kernels for WhiteMatter.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides and
+ * a CUDA stream handle; no framework types cross this boundary.  All launches
+ * are asynchronous on `stream`; nothing here synchronises the host, allocates
+ * device memory or mutates an input.  Scratch memory is supplied by the caller
+ * (`workspace`, size from the matching *_workspace_bytes query).
+ *
+ * Return value: 0 on success, a negative WM_E* code otherwise; the text of the
+ * last failure on the calling thread is available from wm_last_error().
+ *
+ * The entry points stand in for these operators of the upstream project
+ * (paths relative to the upstream repository root):
+ *
+ *   wm_cyclic_attn_fwd      white_matter::cyclic_attn_fwd
+ *                           src/white_matter/ops/cyclic_attention/_tilelang/registration.py:164-173
+ *   wm_cyclic_attn_bwd      white_matter::cyclic_attn_bwd            registration.py:184-197
+ *   wm_cyclic_attn_doc_fwd  white_matter::cyclic_attn_doc_fwd        registration.py:261-274
+ *   wm_cyclic_attn_doc_bwd  white_matter::cyclic_attn_doc_bwd        registration.py:280-296
+ *   wm_strict_attn_fwd/bwd  the dense branch of strict_causal_attention
+ *                           src/white_matter/ops/strict_causal_attention.py:299-322,432-458
+ *   wm_strict_packed_fwd/bwd  the packed-document branch (varlen FlashAttention
+ *                           call with gather/scatter) strict_causal_attention.py:397-431
+ *   wm_strict_decode        white_matter::flash_attention_decode / torch_flash_decode
+ *                           src/white_matter/ops/flash_attention.py:15-36,52-103
+ *   wm_mix_sources_fwd/bwd  the mixture step of the KV pool
+ *                           src/white_matter/modules/routing.py:116-122,
+ *                           src/white_matter/blocks/feedback_transformer.py:35-36
+ */
+#ifndef WM_B200_H
+#define WM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WM_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define WM_API __attribute__((visibility("default")))
+#else
+#define WM_API
+#endif
+
+/* element types */
+#define WM_F32 0
+#define WM_BF16 1
+
+/* error codes */
+#define WM_OK 0
+#define WM_EINVAL (-1)     /* argument rejected before any launch */
+#define WM_EUNSUPPORTED (-2) /* shape / type outside what the kernels cover */
+#define WM_ECUDA (-3)      /* a CUDA runtime call failed */
+#define WM_EWORKSPACE (-4) /* workspace missing or too small */
+
+/* mask families (wm_attn_args.mask) */
+#define WM_MASK_CYCLIC 0 /* query i sees key slots j <= query_offset + query_stride*i */
+#define WM_MASK_STRICT 1 /* query at real position p sees real slots s < min(p, kv_length) (+ dummy slot 0) */
+#define WM_MASK_PACKED 2 /* schedule groups with bottom-right causal alignment */
+
+/* kernel family selection (wm_attn_args.kernel) */
+#define WM_KERNEL_AUTO 0   /* tensor-core kernel when the problem qualifies, else the SIMT kernel */
+#define WM_KERNEL_SIMT 1   /* force the fp32-accumulate SIMT kernel (all types and head sizes) */
+#define WM_KERNEL_TCGEN05 2 /* force the tcgen05/TMEM kernel; WM_EUNSUPPORTED if the problem does not qualify */
+
+/*
+ * One description of an attention problem, shared by all attention entry
+ * points.  Fields an entry point does not use must be zero / NULL.
+ *
+ * Tensors are (batch, heads, tokens, head_dim) with unit stride in head_dim;
+ * the three strides are in ELEMENTS for batch, head and token.  The output is
+ * addressed the same way, so the caller chooses (B,T,H,D) or (B,H,T,D) storage.
+ */
+typedef struct wm_attn_args {
+  /* forward operands */
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;  /* forward: written; backward: read (the forward result) */
+  float* lse; /* (batch, q_heads, q_len) contiguous; natural-log sum-exp of the scaled scores, +inf for empty rows */
+  /* backward operands */
+  const void* dout;
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t q_strides[3];
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t out_strides[3];
+  int64_t dout_strides[3];
+  int64_t dq_strides[3];
+  int64_t dk_strides[3];
+  int64_t dv_strides[3];
+  /* scratch supplied by the caller */
+  void* workspace;
+  size_t workspace_bytes;
+  /* sizes */
+  int32_t dtype; /* WM_F32 or WM_BF16, common to q/k/v/out and gradients */
+  int32_t batch;
+  int32_t q_heads;
+  int32_t kv_heads; /* q_heads % kv_heads == 0 */
+  int32_t q_len;
+  int32_t k_len; /* number of key slots addressed (cache capacity for the strict family) */
+  int32_t head_dim;
+  float scale;
+  int32_t mask;
+  int32_t kernel;
+  /* WM_MASK_CYCLIC */
+  int32_t query_stride;
+  int32_t query_offset; /* already lowered by one for strict_past; may be -1 */
+  const int32_t* q_seg;       /* (batch, q_len) document of each query, or NULL */
+  const int32_t* k_seg;       /* (batch, k_len) document of each key slot; -1 marks the shared dummy */
+  const int32_t* q_key_start; /* (batch, q_len) first key slot of the query's document */
+  const int32_t* k_query_end; /* (batch, k_len) exclusive upper query bound of each key */
+  /* WM_MASK_STRICT: device-resident bounds (either may be NULL) */
+  const void* query_start; /* (batch,) int32 or int64 real position of the first query */
+  const void* kv_lengths;  /* (batch,) int32 or int64 number of committed real tokens */
+  int32_t query_start_is64;
+  int32_t kv_lengths_is64;
+  int64_t query_start_value; /* used when query_start == NULL */
+  const uint8_t* key_mask;   /* (batch, k_len) 0/1, or NULL */
+  int32_t use_dummy;         /* slot 0 is the always-visible dummy */
+  /* WM_MASK_PACKED */
+  int32_t n_groups;
+  const int32_t* groups;        /* (n_groups, 4): query begin, query end, key begin, key end in the packed lists */
+  const int64_t* query_indices; /* flat (batch*q_len) row of each packed query */
+  const int64_t* key_indices;   /* flat (batch*k_len) slot of each packed key */
+  /* Tile tables for packed problems: (n, 2) rows of {group, first row of the tile
+   * relative to the group}, cut every wm_attn_tile_rows() rows. */
+  int32_t n_query_tiles;
+  const int32_t* query_tiles;
+  int32_t n_key_tiles; /* backward only */
+  const int32_t* key_tiles;
+} wm_attn_args;
+
+/* Mixture of S source tensors of n elements each: out = sum_s softmax(logits)[s] * src[s]. */
+typedef struct wm_mix_args {
+  const void* sources;    /* (n_sources, n) */
+  int64_t source_stride;  /* elements between consecutive sources */
+  const float* logits;    /* (n_sources,) fp32, device */
+  void* out;              /* (n,) forward result */
+  const void* dout;       /* (n,) backward input */
+  void* dsources;         /* (n_sources, n) backward result, same stride as sources; may be NULL */
+  float* dlogits;         /* (n_sources,) fp32 backward result; may be NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  int64_t n;
+  int32_t n_sources; /* 1..64 */
+  int32_t dtype;
+} wm_mix_args;
+
+WM_API int wm_abi_version(void);
+WM_API const char* wm_last_error(void);
+
+/* Rows per tile that the kernel selected for `args` cuts packed groups into
+ * (queries when key_side == 0, keys otherwise; backward != 0 for the gradient kernels). */
+WM_API int wm_attn_tile_rows(const wm_attn_args* args, int backward, int key_side);
+
+/* Scratch sizes for the calls below (bytes, may be 0). */
+WM_API size_t wm_attn_fwd_workspace_bytes(const wm_attn_args* args);
+WM_API size_t wm_attn_bwd_workspace_bytes(const wm_attn_args* args);
+WM_API size_t wm_strict_decode_workspace_bytes(const wm_attn_args* args);
+WM_API size_t wm_mix_workspace_bytes(const wm_mix_args* args);
+
+/* cyclic attention without / with document metadata */
+WM_API int wm_cyclic_attn_fwd(const wm_attn_args* args, void* stream);
+WM_API int wm_cyclic_attn_bwd(const wm_attn_args* args, void* stream);
+WM_API int wm_cyclic_attn_doc_fwd(const wm_attn_args* args, void* stream);
+WM_API int wm_cyclic_attn_doc_bwd(const wm_attn_args* args, void* stream);
+
+/* strict-past attention: dense bounds (Jacobi without documents, cached-prefix prefill) */
+WM_API int wm_strict_attn_fwd(const wm_attn_args* args, void* stream);
+WM_API int wm_strict_attn_bwd(const wm_attn_args* args, void* stream);
+/* strict-past attention over a packed-document schedule */
+WM_API int wm_strict_packed_fwd(const wm_attn_args* args, void* stream);
+WM_API int wm_strict_packed_bwd(const wm_attn_args* args, void* stream);
+/* single-query read of a KV pool, split over the key axis; lengths stay on the device */
+WM_API int wm_strict_decode(const wm_attn_args* args, void* stream);
+
+/* KV source mixing */
+WM_API int wm_mix_sources_fwd(const wm_mix_args* args, void* stream);
+WM_API int wm_mix_sources_bwd(const wm_mix_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WM_B200_H */

@@ -1,0 +1,107 @@
+"""Shared test helpers: golden-vector access, seeded inputs and error measures."""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+import torch
+
+GOLDEN_DIR = Path(__file__).resolve().parent / "golden"
+
+
+class Golden:
+    """Replay of tests/golden/reference_vectors.npz (written by make_golden.py from the upstream package)."""
+
+    def __init__(self) -> None:
+        self.cases = json.loads((GOLDEN_DIR / "cases.json").read_text())
+        self.arrays = np.load(GOLDEN_DIR / "reference_vectors.npz")
+
+    def names(self, kind: str) -> list[str]:
+        return sorted(n for n, c in self.cases.items() if c["kind"] == kind)
+
+    def has(self, case: str, field: str) -> bool:
+        return f"{case}/{field}" in self.arrays.files
+
+    def get(self, case: str, field: str) -> torch.Tensor:
+        return torch.from_numpy(self.arrays[f"{case}/{field}"])
+
+    def maybe(self, case: str, field: str):
+        return self.get(case, field) if self.has(case, field) else None
+
+    def cyclic_inputs(self, case: str):
+        """q, k, v, probe (fp32) and metadata tuple or None, as the generator drew them."""
+        c = self.cases[case]
+        if c["inputs_stored"]:
+            q, k, v, probe = (self.get(case, n) for n in ("q", "k", "v", "probe"))
+        else:
+            torch.manual_seed(c["seed"])
+            q = torch.randn(c["B"], c["HQ"], c["Q"], c["D"])
+            k = torch.randn(c["B"], c["HKV"], c["K"], c["D"])
+            v = torch.randn(c["B"], c["HKV"], c["K"], c["D"])
+            probe = torch.randn(c["B"], c["HQ"], c["Q"], c["D"])
+        metadata = None
+        if c["docs"] is not None:
+            metadata = tuple(self.get(case, n) for n in ("q_seg", "k_seg", "q_start", "k_end"))
+        return q, k, v, probe, metadata
+
+    def strict_inputs(self, case: str):
+        c = self.cases[case]
+        if c["inputs_stored"]:
+            q, k, v, probe = (self.get(case, n) for n in ("q", "k", "v", "probe"))
+        else:
+            torch.manual_seed(c["seed"])
+            q = torch.randn(c["B"], c["H"], c["T"], c["D"])
+            k = torch.randn(c["B"], c["HKV"], c["N"], c["D"])
+            v = torch.randn(c["B"], c["HKV"], c["N"], c["D"])
+            probe = torch.randn(c["B"], c["T"], c["H"], c["D"])
+        start = self.maybe(case, "query_start_t")
+        if start is None:
+            start = c["query_start"]
+        return dict(
+            q=q, k=k, v=v, probe=probe, query_start=start, kv_lengths=self.maybe(case, "kv_lengths"),
+            key_mask=self.maybe(case, "key_mask"), docs=self.maybe(case, "docs"), dummy=c["dummy"],
+        )
+
+
+def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
+    return (a.double() - b.double()).abs().max().item() if a.numel() else 0.0
+
+
+def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
+    denom = b.double().norm().item()
+    return (a.double() - b.double()).norm().item() / max(denom, 1e-30)
+
+
+def assert_parity(actual: torch.Tensor, expected: torch.Tensor, *, max_abs_tol: float, rel_l2_tol: float, what: str = ""):
+    """The parity gate of the attention path: max-abs and relative L2 error against the reference result."""
+    actual, expected = actual.detach().cpu(), expected.detach().cpu()
+    assert actual.shape == expected.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}"
+    assert torch.isfinite(actual.float()).all(), f"{what}: non-finite values"
+    ma, rl = max_abs(actual, expected), rel_l2(actual, expected)
+    assert ma <= max_abs_tol and rl <= rel_l2_tol, f"{what}: max_abs={ma:.3e} (tol {max_abs_tol}), rel_l2={rl:.3e} (tol {rel_l2_tol})"
+
+
+# Tolerances of the parity contract: bf16 results within max-abs 2e-2 and
+# relative L2 1e-2 of the reference backend, fp32 results within 1e-4.
+BF16_TOL = dict(max_abs_tol=2e-2, rel_l2_tol=1e-2)
+F32_TOL = dict(max_abs_tol=1e-4, rel_l2_tol=1e-4)
+
+
+def geometric_documents(batch: int, length: int, mean: int, seed: int) -> torch.Tensor:
+    """(batch, length) document ids: lengths drawn geometric with the given mean, truncated to fill each row."""
+    gen = torch.Generator().manual_seed(seed)
+    rows = []
+    p = 1.0 / mean
+    for _ in range(batch):
+        ids, at, doc = torch.empty(length, dtype=torch.long), 0, 0
+        while at < length:
+            u = torch.rand((), generator=gen).item()
+            n = max(1, int(np.ceil(np.log(max(1.0 - u, 1e-12)) / np.log(1.0 - p))))
+            n = min(n, length - at)
+            ids[at : at + n] = doc
+            at += n
+            doc += 1
+        rows.append(ids)
+    return torch.stack(rows)

@@ -1,0 +1,209 @@
+"""cyclic_attention on the GPU against the golden vectors and the CPU oracle (calls go through the C ABI)."""
+
+import pytest
+import torch
+
+from helpers import BF16_TOL, F32_TOL, Golden, assert_parity, geometric_documents
+from oracle import attention_oracle as oracle
+from white_matter_b200 import cyclic_attention, prepare_cyclic_attention_metadata, prepare_feedback_metadata
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not torch.cuda.is_available(), reason="requires CUDA")]
+G = Golden()
+BACKENDS = ["sm100_simt", "sm100"]
+
+
+def run(q, k, v, probe, metadata, c, dtype, backend):
+    dev = "cuda"
+    qq, kk, vv = (t.to(dev, dtype).requires_grad_() for t in (q, k, v))
+    md = None if metadata is None else tuple(t.to(dev) for t in metadata)
+    out = cyclic_attention(
+        qq, kk, vv, query_stride=c["stride"], query_offset=c["offset"], strict_past=c["strict_past"], metadata=md,
+        backend=backend,
+    )
+    assert out.transpose(1, 2).is_contiguous()  # (B,Q,H,D) storage, ready for the output projection
+    grads = torch.autograd.grad(out, (qq, kk, vv), probe.to(dev, dtype))
+    return out, grads
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("case", G.names("cyclic"))
+def test_fp32_matches_reference_vectors(case, backend):
+    c = G.cases[case]
+    q, k, v, probe, metadata = G.cyclic_inputs(case)
+    out, grads = run(q, k, v, probe, metadata, c, torch.float32, backend)
+    assert_parity(out, G.get(case, "out_f32"), what="out", **F32_TOL)
+    for g, name in zip(grads, ("dq_f32", "dk_f32", "dv_f32")):
+        assert_parity(g, G.get(case, name), what=name, **F32_TOL)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("case", G.names("cyclic"))
+def test_bf16_matches_reference(case, backend):
+    c = G.cases[case]
+    q, k, v, probe, metadata = G.cyclic_inputs(case)
+    q, k, v, probe = (t.bfloat16() for t in (q, k, v, probe))
+    out, grads = run(q, k, v, probe, metadata, c, torch.bfloat16, backend)
+    # reference arithmetic on the same bf16 inputs
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp = oracle.cyclic_attention_oracle(
+        qo, ko, vo, query_stride=c["stride"], query_offset=c["offset"], strict_past=c["strict_past"], metadata=metadata
+    )
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert_parity(g.float(), e, what=name, **BF16_TOL)
+    if G.has(case, "out_bf16"):
+        # the upstream backend evaluated in bf16 on the CPU (its own rounding included)
+        assert_parity(out.float(), G.get(case, "out_bf16"), what="out vs upstream bf16", max_abs_tol=3e-2, rel_l2_tol=2e-2)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("head_dim", [64, 96, 128])
+@pytest.mark.parametrize("gqa", [1, 2, 3])
+@pytest.mark.parametrize("documents", [False, True])
+def test_ragged_tiles_groups_and_documents(documents, gqa, head_dim, backend):
+    torch.manual_seed(23)
+    q = torch.randn(2, 2 * gqa, 33, head_dim).bfloat16()
+    k = torch.randn(2, 2, 132, head_dim).bfloat16()
+    v = torch.randn(2, 2, 132, head_dim).bfloat16()
+    probe = torch.randn(2, 2 * gqa, 33, head_dim).bfloat16()
+    metadata = None
+    if documents:
+        seg = torch.stack((torch.arange(132) // 19, torch.arange(132) // 31))
+        metadata = prepare_cyclic_attention_metadata(seg[:, 1::4], torch.cat((seg.new_full((2, 1), -1), seg[:, :-1]), 1))
+    c = dict(stride=4, offset=1, strict_past=False)
+    out, grads = run(q, k, v, probe, metadata, c, torch.bfloat16, backend)
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp = oracle.cyclic_attention_oracle(qo, ko, vo, query_stride=4, query_offset=1, metadata=metadata)
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert_parity(g.float(), e, what=name, **BF16_TOL)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("stride", [1, 4])
+@pytest.mark.parametrize("packed", [False, True])
+def test_strict_past_all_residues(packed, stride, backend):
+    torch.manual_seed(5)
+    T, B, H, D = 137, 2, 2, 64
+    k = torch.randn(B, H, T, D).bfloat16()
+    v = torch.randn(B, H, T, D).bfloat16()
+    docs = geometric_documents(B, T, 40, seed=3)
+    groups = [torch.arange(r, T, stride) for r in range(stride)]
+    metas = prepare_feedback_metadata(docs, groups, T, use_dummy_token=False) if packed else [None] * stride
+    for r in range(stride):
+        n = groups[r].numel()
+        q = torch.randn(B, H, n, D).bfloat16()
+        probe = torch.randn(B, H, n, D).bfloat16()
+        c = dict(stride=stride, offset=r, strict_past=True)
+        out, grads = run(q, k, v, probe, metas[r], c, torch.bfloat16, backend)
+        qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+        exp = oracle.cyclic_attention_oracle(qo, ko, vo, query_stride=stride, query_offset=r, strict_past=True, metadata=metas[r])
+        exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.double())
+        assert_parity(out.float(), exp, what=f"out r={r}", **BF16_TOL)
+        for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+            assert_parity(g.float(), e, what=f"{name} r={r}", **BF16_TOL)
+        if r == 0:
+            assert out[:, :, 0].abs().max().item() == 0  # the first token of the row sees nothing
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("documents", [False, True])
+def test_equal_scores_average_exactly_to_zero(documents, backend):
+    # upstream tests/gpu/test_cyclic_attention.py:61-76: rescaling by anything but one biases earlier tiles
+    q = torch.full((1, 2, 1, 128), 13.0, device="cuda", dtype=torch.bfloat16)
+    k = torch.full((1, 1, 4096, 128), 29.0, device="cuda", dtype=torch.bfloat16)
+    v = torch.ones_like(k)
+    v[:, :, 2048:].neg_()
+    metadata = None
+    if documents:
+        kseg = torch.zeros((1, 4096), device="cuda", dtype=torch.long)
+        kseg[:, 0] = -1
+        metadata = prepare_cyclic_attention_metadata(torch.zeros((1, 1), device="cuda", dtype=torch.long), kseg)
+    out = cyclic_attention(q, k, v, query_stride=4096, query_offset=4095, metadata=metadata, backend=backend)
+    assert out.abs().max().item() == 0
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("documents", [False, True])
+def test_invisible_keys_get_exactly_zero_gradient(documents, backend):
+    # upstream tests/gpu/test_cyclic_attention.py:134-157
+    torch.manual_seed(127)
+    q = torch.randn(1, 4, 1, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(1, 2, 513, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn_like(k, requires_grad=True)
+    metadata = None
+    if documents:
+        kseg = torch.zeros((1, 513), device="cuda", dtype=torch.int32)
+        kseg[:, 0] = -1
+        metadata = prepare_cyclic_attention_metadata(torch.zeros((1, 1), device="cuda", dtype=torch.int32), kseg)
+    out = cyclic_attention(q, k, v, query_stride=4, query_offset=0, metadata=metadata, backend=backend)
+    grads = torch.autograd.grad(out, (q, k, v), torch.randn_like(out))
+    for g in grads[1:]:
+        assert g[:, :, 1:].abs().max().item() == 0
+        assert g[:, :, :1].abs().max().item() > 0
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_strided_cache_views_are_bitwise_equal_to_contiguous(backend):
+    # upstream tests/gpu/test_cyclic_attention.py:79-96: batch slice, channel selection, unused capacity
+    torch.manual_seed(29)
+    q = torch.randn(2, 4, 33, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    storage = [torch.randn(4, 3, 2, 145, 128, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    k, v = [t[1:3, 1, :, :132].detach().requires_grad_() for t in storage]
+    assert not k.is_contiguous()
+    kc, vc = [t.detach().contiguous().requires_grad_() for t in (k, v)]
+    opts = dict(query_stride=4, query_offset=1, backend=backend)
+    a = cyclic_attention(q, k, v, **opts)
+    b = cyclic_attention(q, kc, vc, **opts)
+    probe = torch.randn_like(a)
+    ga = torch.autograd.grad(a, (q, k, v), probe)
+    gb = torch.autograd.grad(b, (q, kc, vc), probe)
+    assert torch.equal(a, b)
+    for x, y in zip(ga, gb):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_deterministic(backend):
+    torch.manual_seed(1)
+    q = torch.randn(2, 4, 65, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(2, 4, 260, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn_like(k, requires_grad=True)
+    probe = torch.randn_like(q)
+    runs = []
+    for _ in range(2):
+        out = cyclic_attention(q, k, v, query_stride=4, backend=backend)
+        runs.append((out, *torch.autograd.grad(out, (q, k, v), probe)))
+    for x, y in zip(*runs):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("backend", ["sm100"])
+def test_training_shape_properties_at_full_size(backend):
+    """B=16,H=16,K=2048,D=64, stride 8 with packed documents: too large for the CPU oracle.
+
+    Checked through properties that do not depend on the size: the SIMT and the
+    selected kernel agree, every document's first token is exactly zero, and
+    the result is linear in V.
+    """
+    torch.manual_seed(0)
+    B, H, T, D, S = 16, 16, 2048, 64, 8
+    docs = geometric_documents(B, T, 1024, seed=7).cuda()
+    groups = [torch.arange(r, T, S, device="cuda") for r in range(S)]
+    metas = prepare_feedback_metadata(docs, groups, T, use_dummy_token=False)
+    k = torch.randn(B, H, T, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, H, T, D, device="cuda", dtype=torch.bfloat16)
+    r = 3
+    q = torch.randn(B, H, T // S, D, device="cuda", dtype=torch.bfloat16)
+    opts = dict(query_stride=S, query_offset=r, strict_past=True, metadata=metas[r])
+    out = cyclic_attention(q, k, v, backend=backend, **opts)
+    ref = cyclic_attention(q, k, v, backend="sm100_simt", **opts)
+    assert_parity(out.float(), ref.float(), what="kernel families", **BF16_TOL)
+    starts = torch.ones_like(docs, dtype=torch.bool)
+    starts[:, 1:] = docs[:, 1:] != docs[:, :-1]
+    first_rows = starts[:, r::S]
+    assert out.transpose(1, 2)[first_rows].abs().max().item() == 0
+    out2 = cyclic_attention(q, k, 2 * v, backend=backend, **opts)
+    assert_parity(out2.float(), 2 * out.float(), what="linearity in V", max_abs_tol=4e-2, rel_l2_tol=1e-2)

@@ -1,0 +1,27 @@
+"""B200 (sm_100a) kernels for the WhiteMatter attention hot path.
+
+Public names match ``white_matter.ops`` of the upstream project; the kernels
+live in ``libwm_b200.so`` behind the C ABI of ``include/wm_b200.h``.
+"""
+
+from .cyclic import cyclic_attention
+from .metadata import (
+    CyclicAttentionMetadata,
+    StrictCausalMetadata,
+    prepare_cyclic_attention_metadata,
+    prepare_feedback_metadata,
+    prepare_strict_causal_metadata,
+)
+from .mixing import mix_kv_sources
+from .strict import strict_causal_attention
+
+__all__ = [
+    "StrictCausalMetadata",
+    "prepare_strict_causal_metadata",
+    "strict_causal_attention",
+    "CyclicAttentionMetadata",
+    "cyclic_attention",
+    "prepare_cyclic_attention_metadata",
+    "prepare_feedback_metadata",
+    "mix_kv_sources",
+]

@@ -1,0 +1,343 @@
+// Single-query strict-past read of a KV pool, split over the key axis.
+//
+// The kernel is bound by HBM bandwidth: every visible K and V row is read
+// exactly once with 128-bit loads (LPK lanes cover one row), the per-key dot
+// product is reduced with warp shuffles inside the LPK lanes, and every lane
+// group keeps its own online-softmax state so that no cross-lane traffic is
+// needed until the block's final merge.  Blocks whose key range starts at or
+// beyond the row's visible length (read on the device) exit at once, which
+// keeps the launch shape independent of the lengths and so capturable in a
+// CUDA graph.  A second, tiny kernel merges the split partials.
+//
+// Algorithmic bytes per step: sum_b 2 * kv_heads * visible_b * head_dim * sizeof(T).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace wm {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / 32;
+constexpr int kUnroll = 4;
+
+template <typename T>
+struct VecOf;
+template <>
+struct VecOf<float> {
+  static constexpr int N = 4;
+};
+template <>
+struct VecOf<__nv_bfloat16> {
+  static constexpr int N = 8;
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack(const uint4& raw, float (&x)[VecOf<T>::N]);
+template <>
+__device__ __forceinline__ void unpack<float>(const uint4& raw, float (&x)[4]) {
+  x[0] = __uint_as_float(raw.x);
+  x[1] = __uint_as_float(raw.y);
+  x[2] = __uint_as_float(raw.z);
+  x[3] = __uint_as_float(raw.w);
+}
+template <>
+__device__ __forceinline__ void unpack<__nv_bfloat16>(const uint4& raw, float (&x)[8]) {
+  const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __uint_as_float(w[i] << 16);
+    x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+// partial record per (batch, q_head, split): m, l, acc[head_dim]
+__device__ __forceinline__ long long partial_at(const wm_attn_args& a, int b, int h, int split, int splits) {
+  return ((static_cast<long long>(b) * a.q_heads + h) * splits + split) * (a.head_dim + 2);
+}
+
+template <typename T, int LPK, int G>
+__global__ void __launch_bounds__(kThreads) decode_split_kernel(const wm_attn_args a, float* partial, int chunk,
+                                                                int splits) {
+  constexpr int VEC = VecOf<T>::N;
+  constexpr int KPW = 32 / LPK;  // keys per warp per step
+  __shared__ float sm_m[kWarps][G];
+  __shared__ float sm_l[kWarps][G];
+  __shared__ float sm_acc[kWarps][G][LPK * VEC];
+
+  const int b = blockIdx.z;
+  const int split = blockIdx.x;
+  const int heads_per_kv = a.q_heads / a.kv_heads;
+  // G == heads_per_kv: blockIdx.y is the KV head; G == 1 otherwise: blockIdx.y is the query head
+  const int kv_head = G == heads_per_kv ? blockIdx.y : blockIdx.y / heads_per_kv;
+  const int head0 = G == heads_per_kv ? blockIdx.y * G : blockIdx.y;
+
+  GroupCtx g = group_ctx(a, 0);
+  const int n = row_bound(a, g, b, 0).hi;
+  const int j_begin = split * chunk;
+  if (j_begin >= n) return;
+  const int j_end = min(n, j_begin + chunk);
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int c = lane % LPK;
+  const int kk = lane / LPK;
+  const bool dlive = c * VEC < a.head_dim;
+
+  float q[G][VEC];
+  const float sl2 = a.scale * kLog2e;
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    const T* qrow = static_cast<const T*>(a.q) + b * a.q_strides[0] + (head0 + h) * a.q_strides[1];
+    if (dlive) {
+      uint4 raw = *reinterpret_cast<const uint4*>(qrow + c * VEC);
+      unpack<T>(raw, q[h]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) q[h][e] = 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) q[h][e] *= sl2;
+  }
+  float m[G], l[G], acc[G][VEC];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[h][e] = 0.f;
+  }
+
+  const T* kbase = static_cast<const T*>(a.k) + b * a.k_strides[0] + kv_head * a.k_strides[1] + c * VEC;
+  const T* vbase = static_cast<const T*>(a.v) + b * a.v_strides[0] + kv_head * a.v_strides[1] + c * VEC;
+  const unsigned char* mask = a.key_mask ? a.key_mask + static_cast<long long>(b) * a.k_len : nullptr;
+
+  for (int j0 = j_begin + warp * KPW * kUnroll; j0 < j_end; j0 += kWarps * KPW * kUnroll) {
+    uint4 kraw[kUnroll], vraw[kUnroll];
+    bool vis[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      int j = j0 + u * KPW + kk;
+      vis[u] = j < j_end && (mask == nullptr || mask[j] != 0);
+      kraw[u] = make_uint4(0, 0, 0, 0);
+      vraw[u] = make_uint4(0, 0, 0, 0);
+      if (vis[u] && dlive) {
+        kraw[u] = ld_stream(kbase + static_cast<long long>(j) * a.k_strides[2]);
+        vraw[u] = ld_stream(vbase + static_cast<long long>(j) * a.v_strides[2]);
+      }
+    }
+    float kf[kUnroll][VEC];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) unpack<T>(kraw[u], kf[u]);
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      float s[kUnroll];
+      float top = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) d = fmaf(q[h][e], kf[u][e], d);
+#pragma unroll
+        for (int sft = LPK / 2; sft > 0; sft >>= 1) d += __shfl_xor_sync(0xffffffffu, d, sft);
+        s[u] = vis[u] ? d : -INFINITY;
+        top = fmaxf(top, s[u]);
+      }
+      if (top != -INFINITY) {
+        float m_new = fmaxf(m[h], top);
+        float corr = exp2f(m[h] - m_new);
+        l[h] *= corr;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[h][e] *= corr;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          if (vis[u]) {
+            float p = exp2f(s[u] - m_new);
+            float vf[VEC];
+            unpack<T>(vraw[u], vf);
+            l[h] += p;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[h][e] = fmaf(p, vf[e], acc[h][e]);
+          }
+        }
+        m[h] = m_new;
+      }
+    }
+  }
+
+  // merge the KPW lane groups of the warp (lanes with equal c)
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+#pragma unroll
+    for (int sft = LPK; sft < 32; sft <<= 1) {
+      float m_o = __shfl_xor_sync(0xffffffffu, m[h], sft);
+      float l_o = __shfl_xor_sync(0xffffffffu, l[h], sft);
+      float m_new = fmaxf(m[h], m_o);
+      float ca = m[h] == -INFINITY ? 0.f : exp2f(m[h] - m_new);
+      float cb = m_o == -INFINITY ? 0.f : exp2f(m_o - m_new);
+      l[h] = l[h] * ca + l_o * cb;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float a_o = __shfl_xor_sync(0xffffffffu, acc[h][e], sft);
+        acc[h][e] = acc[h][e] * ca + a_o * cb;
+      }
+      m[h] = m_new;
+    }
+    if (kk == 0) {
+      if (c == 0) {
+        sm_m[warp][h] = m[h];
+        sm_l[warp][h] = l[h];
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) sm_acc[warp][h][c * VEC + e] = acc[h][e];
+    }
+  }
+  __syncthreads();
+  // merge the warps; thread t handles (head, dim) pairs
+  for (int idx = threadIdx.x; idx < G * LPK * VEC; idx += kThreads) {
+    int h = idx / (LPK * VEC);
+    int d = idx - h * (LPK * VEC);
+    if (d >= a.head_dim) continue;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) top = fmaxf(top, sm_m[w][h]);
+    float lsum = 0.f, asum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      float cw = sm_m[w][h] == -INFINITY ? 0.f : exp2f(sm_m[w][h] - top);
+      lsum += sm_l[w][h] * cw;
+      asum += sm_acc[w][h][d] * cw;
+    }
+    long long at = partial_at(a, b, head0 + h, split, splits);
+    if (d == 0) {
+      partial[at] = top;
+      partial[at + 1] = lsum;
+    }
+    partial[at + 2 + d] = asum;
+  }
+}
+
+template <typename T>
+__global__ void decode_merge_kernel(const wm_attn_args a, const float* partial, int chunk, int splits) {
+  const int b = blockIdx.y;
+  const int h = blockIdx.x;
+  GroupCtx g = group_ctx(a, 0);
+  const int n = row_bound(a, g, b, 0).hi;
+  const int live = (n + chunk - 1) / chunk;
+  T* orow = static_cast<T*>(a.out) + b * a.out_strides[0] + h * a.out_strides[1];
+  for (int d = threadIdx.x; d < a.head_dim; d += blockDim.x) {
+    float top = -INFINITY;
+    for (int s = 0; s < live; ++s) top = fmaxf(top, partial[partial_at(a, b, h, s, splits)]);
+    float lsum = 0.f, asum = 0.f;
+    for (int s = 0; s < live; ++s) {
+      long long at = partial_at(a, b, h, s, splits);
+      float ms = partial[at];
+      float cw = ms == -INFINITY ? 0.f : exp2f(ms - top);
+      lsum += partial[at + 1] * cw;
+      asum += partial[at + 2 + d] * cw;
+    }
+    orow[d] = from_float<T>(lsum > 0.f ? asum / lsum : 0.f);
+    if (d == 0 && a.lse != nullptr)
+      a.lse[static_cast<long long>(b) * a.q_heads + h] = lsum > 0.f ? (top + log2f(lsum)) * kLn2 : INFINITY;
+  }
+}
+
+int pick_chunk(const wm_attn_args& a) {
+  // Aim for at least ~8 blocks per SM when every row is full; 64 <= chunk <= 256 keys.
+  long long rows = static_cast<long long>(a.batch) * a.kv_heads;
+  long long want = 148LL * 8;
+  long long chunk = (static_cast<long long>(a.k_len) * rows + want - 1) / want;
+  int c = 64;
+  while (c < 256 && c < chunk) c <<= 1;
+  return c;
+}
+
+int lanes_per_key(const wm_attn_args& a) {
+  int vec = a.dtype == WM_F32 ? 4 : 8;
+  int need = (a.head_dim + vec - 1) / vec;
+  int lpk = 1;
+  while (lpk < need) lpk <<= 1;
+  return lpk;
+}
+
+template <typename T, int LPK>
+int launch(const wm_attn_args& a, float* partial, cudaStream_t stream) {
+  const int chunk = pick_chunk(a);
+  const int splits = (a.k_len + chunk - 1) / chunk;
+  const int hpk = a.q_heads / a.kv_heads;
+  if (hpk == 2) {
+    dim3 grid(splits, a.kv_heads, a.batch);
+    decode_split_kernel<T, LPK, 2><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits);
+  } else if (hpk == 4) {
+    dim3 grid(splits, a.kv_heads, a.batch);
+    decode_split_kernel<T, LPK, 4><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits);
+  } else {
+    dim3 grid(splits, a.q_heads, a.batch);
+    if (hpk == 1) {
+      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits);
+    } else {
+      // other group sizes: one block per query head, K/V re-read through L2
+      wm_attn_args single = a;
+      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(single, partial, chunk, splits);
+    }
+  }
+  WM_CUDA(cudaGetLastError());
+  int threads = a.head_dim <= 64 ? 64 : 128;
+  decode_merge_kernel<T><<<dim3(a.q_heads, a.batch), threads, 0, stream>>>(a, partial, chunk, splits);
+  return cuda_check(cudaGetLastError(), "decode_merge_kernel");
+}
+
+template <typename T>
+int dispatch(const wm_attn_args& a, float* partial, cudaStream_t stream) {
+  switch (lanes_per_key(a)) {
+    case 1:
+    case 2:
+    case 4:
+      return launch<T, 4>(a, partial, stream);
+    case 8:
+      return launch<T, 8>(a, partial, stream);
+    case 16:
+      return launch<T, 16>(a, partial, stream);
+    default:
+      return launch<T, 32>(a, partial, stream);
+  }
+}
+
+}  // namespace
+
+bool decode_supported(const wm_attn_args& a) {
+  size_t es = a.dtype == WM_F32 ? 4 : 2;
+  int vec = a.dtype == WM_F32 ? 4 : 8;
+  if (a.q_len != 1 || a.mask != WM_MASK_STRICT) return false;
+  if (a.head_dim % vec || a.head_dim > 32 * vec) return false;
+  auto ok_ptr = [&](const void* p) { return (reinterpret_cast<uintptr_t>(p) % 16) == 0; };
+  auto ok_str = [&](const int64_t* s) { return (s[0] * es) % 16 == 0 && (s[1] * es) % 16 == 0 && (s[2] * es) % 16 == 0; };
+  return ok_ptr(a.q) && ok_ptr(a.k) && ok_ptr(a.v) && ok_str(a.q_strides) && ok_str(a.k_strides) && ok_str(a.v_strides);
+}
+
+size_t decode_workspace(const wm_attn_args& a) {
+  const int chunk = pick_chunk(a);
+  const int splits = (a.k_len + chunk - 1) / chunk;
+  return static_cast<size_t>(a.batch) * a.q_heads * splits * (a.head_dim + 2) * sizeof(float);
+}
+
+int decode_launch_with_scratch(const wm_attn_args& a, float* scratch, cudaStream_t stream) {
+  return a.dtype == WM_F32 ? dispatch<float>(a, scratch, stream) : dispatch<__nv_bfloat16>(a, scratch, stream);
+}
+
+int decode_launch(const wm_attn_args& a, cudaStream_t stream) {
+  size_t need = decode_workspace(a);
+  if (a.workspace == nullptr || a.workspace_bytes < need)
+    return fail(WM_EWORKSPACE, "decode needs %zu workspace bytes, got %zu", need, a.workspace_bytes);
+  return decode_launch_with_scratch(a, static_cast<float*>(a.workspace), stream);
+}
+
+}  // namespace wm
