@@ -1,0 +1,463 @@
+"""Benchmark of the WhiteMatter attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (N=1 and per rank for N>1, weak scaling): the training configuration
+of cyclic attention -- bf16, B=16, H=16, key length 2048 (256 queries per
+residue), head_dim 64, query_stride 8, packed documents with geometric lengths
+of mean 1024, no dummy token (strict past).  One step is one sweep over the 8
+residues, forward and backward, 16 operator calls.  Inputs are synthetic
+(seeded N(0,1)); K+V alone are 134 MB per sweep, larger than the 126 MB L2.
+
+The headline ``value`` is TFLOP/s on the visible (query,key) pairs only,
+14*head_dim FLOP per pair (4 forward, 10 backward), with inputs resident in
+HBM.  ``e2e`` is the same metric with pinned host buffers copied in and the
+results copied back inside the timed region.  The same line also reports the
+pool-read (decode) bandwidth and the source-mixing bandwidth, each with its
+roofline fraction, and the CPU oracle timed on a bounded sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+B, H, T, D, STRIDE = 16, 16, 2048, 64, 8
+DOC_MEAN = 1024
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def geometric_documents(batch, length, mean, seed):
+    """(batch, length) document ids with geometric lengths (support >= 1) truncated to fill each row exactly."""
+    gen = torch.Generator().manual_seed(seed)
+    dist_p = 1.0 / mean
+    rows = []
+    for _ in range(batch):
+        ids, at, doc = torch.empty(length, dtype=torch.long), 0, 0
+        while at < length:
+            u = torch.rand((), generator=gen).item()
+            n = max(1, int(torch.ceil(torch.log(torch.tensor(max(1.0 - u, 1e-12))) / torch.log(torch.tensor(1.0 - dist_p))).item()))
+            n = min(n, length - at)
+            ids[at : at + n] = doc
+            at += n
+            doc += 1
+        rows.append(ids)
+    return torch.stack(rows)
+
+
+def visible_pairs_per_head(docs, residue, stride):
+    """Visible (query,key) pairs of one residue, summed over the batch rows (strict past, same document)."""
+    total = 0
+    for row in docs.tolist():
+        start = 0
+        for t in range(len(row)):
+            if t and row[t] != row[t - 1]:
+                start = t
+            if t % stride == residue:
+                total += t - start
+    return total
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+
+    QUERY = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        clocks, top, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in text.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                top = float(parts[2])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": top,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+# --------------------------------------------------------------------------- workload
+
+
+class TrainingSweep:
+    """Device-resident inputs of one 8-residue sweep and the calls of one step."""
+
+    def __init__(self, device, seed, backend="sm100"):
+        from white_matter_b200 import cyclic_attention, prepare_feedback_metadata
+
+        self.attention = cyclic_attention
+        self.backend = backend
+        self.device = device
+        self.docs = geometric_documents(B, T, DOC_MEAN, seed=7 + seed)
+        groups = [torch.arange(r, T, STRIDE) for r in range(STRIDE)]
+        metas = prepare_feedback_metadata(self.docs, groups, T, use_dummy_token=False)
+        self.metas = [tuple(t.to(device) for t in m) for m in metas]
+        gen = torch.Generator().manual_seed(seed)
+        shape_q, shape_k = (B, H, T // STRIDE, D), (B, H, T, D)
+        # pinned host copies feed the end-to-end arm; the device copies feed the kernel arm
+        self.host = {
+            "q": [torch.randn(shape_q, generator=gen).bfloat16().pin_memory() for _ in range(STRIDE)],
+            "g": [torch.randn(shape_q, generator=gen).bfloat16().pin_memory() for _ in range(STRIDE)],
+            "k": torch.randn(shape_k, generator=gen).bfloat16().pin_memory(),
+            "v": torch.randn(shape_k, generator=gen).bfloat16().pin_memory(),
+        }
+        self.q = [t.to(device).requires_grad_() for t in self.host["q"]]
+        self.g = [t.to(device) for t in self.host["g"]]
+        self.k = self.host["k"].to(device).requires_grad_()
+        self.v = self.host["v"].to(device).requires_grad_()
+        self.pairs = sum(visible_pairs_per_head(self.docs, r, STRIDE) for r in range(STRIDE)) * H
+        self.flops_fwd = 4 * D * self.pairs
+        self.flops = 14 * D * self.pairs
+
+    def forward(self, r, q=None, k=None, v=None):
+        return self.attention(
+            self.q[r] if q is None else q, self.k if k is None else k, self.v if v is None else v,
+            query_stride=STRIDE, query_offset=r, strict_past=True, metadata=self.metas[r], backend=self.backend,
+        )
+
+    def step(self):
+        """All 8 residues forward and backward; returns nothing, gradients are discarded."""
+        for r in range(STRIDE):
+            out = self.forward(r)
+            torch.autograd.grad(out, (self.q[r], self.k, self.v), self.g[r])
+
+    def step_e2e(self, staging):
+        """One step from pinned host buffers to pinned host results."""
+        k = staging["k"].copy_(self.host["k"], non_blocking=True).detach().requires_grad_()
+        v = staging["v"].copy_(self.host["v"], non_blocking=True).detach().requires_grad_()
+        dk_sum = dv_sum = None
+        for r in range(STRIDE):
+            q = staging["q"][r].copy_(self.host["q"][r], non_blocking=True).detach().requires_grad_()
+            g = staging["g"][r].copy_(self.host["g"][r], non_blocking=True)
+            out = self.forward(r, q, k, v)
+            dq, dk, dv = torch.autograd.grad(out, (q, k, v), g)
+            staging["out_host"][r].copy_(out.detach().transpose(1, 2), non_blocking=True)
+            staging["dq_host"][r].copy_(dq, non_blocking=True)
+            dk_sum = dk if dk_sum is None else dk_sum.add_(dk)
+            dv_sum = dv if dv_sum is None else dv_sum.add_(dv)
+        staging["dk_host"].copy_(dk_sum, non_blocking=True)
+        staging["dv_host"].copy_(dv_sum, non_blocking=True)
+
+    @staticmethod
+    def staging_bytes():
+        q_bytes = B * H * (T // STRIDE) * D * 2
+        k_bytes = B * H * T * D * 2
+        return 2 * STRIDE * q_bytes + 2 * k_bytes, 2 * STRIDE * q_bytes + 2 * k_bytes
+
+    def staging(self):
+        dev = self.device
+        shape_q, shape_k = (B, H, T // STRIDE, D), (B, H, T, D)
+        mk = lambda s: torch.empty(s, dtype=torch.bfloat16, device=dev)
+        pin = lambda s: torch.empty(s, dtype=torch.bfloat16).pin_memory()
+        s = {
+            "q": [mk(shape_q) for _ in range(STRIDE)], "g": [mk(shape_q) for _ in range(STRIDE)],
+            "k": mk(shape_k), "v": mk(shape_k),
+            "out_host": [pin((B, T // STRIDE, H, D)) for _ in range(STRIDE)],
+            "dq_host": [pin(shape_q) for _ in range(STRIDE)],
+            "dk_host": pin(shape_k), "dv_host": pin(shape_k),
+        }
+        q_bytes = B * H * (T // STRIDE) * D * 2
+        k_bytes = B * H * T * D * 2
+        s["h2d"] = 2 * STRIDE * q_bytes + 2 * k_bytes
+        s["d2h"] = 2 * STRIDE * q_bytes + 2 * k_bytes
+        return s
+
+
+def time_steps(fn, steps, warmup, sync):
+    """Device time of exactly ``steps`` calls of fn (ms), events on the current stream, barriers both sides."""
+    for _ in range(warmup):
+        fn()
+    sync()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    sync()
+    return begin.elapsed_time(end)
+
+
+# --------------------------------------------------------------------------- secondary workloads
+
+
+def bench_decode(device, peaks, iters=20):
+    """Pool read: B=64, H=16, D=64, 8192 slots, lengths uniform in [1,8192]; GB/s over the visible K/V bytes."""
+    from white_matter_b200 import strict_causal_attention
+
+    gen = torch.Generator().manual_seed(0)
+    batch, heads, slots, dim = 64, 16, 8192, 64
+    lengths = torch.randint(1, slots + 1, (batch,), generator=gen).to(device)
+    k = torch.randn(batch, heads, slots, dim, device=device, dtype=torch.bfloat16)
+    v = torch.randn(batch, heads, slots, dim, device=device, dtype=torch.bfloat16)
+    q = torch.randn(batch, heads, 1, dim, device=device, dtype=torch.bfloat16)
+    call = lambda: strict_causal_attention(q, k, v, query_start=lengths, kv_lengths=lengths)
+    ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+    nbytes = int(lengths.sum().item()) * 2 * heads * dim * 2
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {
+        "workload": "strict decode B=64 H=16 D=64 lengths~U[1,8192] bf16 (pool 2.15 GB > L2)",
+        "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+    }
+
+
+def bench_mixing(device, peaks, iters=10):
+    """25-source mixture of a per-GPU shard: sources (25, 2, 16, 2048, 64) bf16 = 210 MB, read once."""
+    from white_matter_b200 import mix_kv_sources
+
+    src = torch.randn(25, 2, 16, 2048, 64, device=device, dtype=torch.bfloat16)
+    logits = torch.randn(25, device=device)
+    call = lambda: mix_kv_sources(src, logits)
+    ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+    nbytes = src.numel() * 2 + src[0].numel() * 2
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {
+        "workload": "mix 25 sources (25,2,16,2048,64) bf16, 210 MB read + 8 MB written",
+        "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+    }
+
+
+def cpu_sample(rows=2, residue=3, repeats=1):
+    """The CPU oracle on a bounded sample of the training workload: `rows` batch rows of one residue, fwd+bwd, fp32.
+
+    Returns (TFLOP/s over the sample's visible pairs, seconds per repeat, threads, description).
+    """
+    from oracle import attention_oracle as oracle
+    from white_matter_b200 import prepare_feedback_metadata
+
+    docs = geometric_documents(B, T, DOC_MEAN, seed=7)[:rows]
+    groups = [torch.arange(r, T, STRIDE) for r in range(STRIDE)]
+    meta = prepare_feedback_metadata(docs, groups, T, use_dummy_token=False)[residue]
+    gen = torch.Generator().manual_seed(0)
+    q = torch.randn(rows, H, T // STRIDE, D, generator=gen).requires_grad_()
+    k = torch.randn(rows, H, T, D, generator=gen).requires_grad_()
+    v = torch.randn(rows, H, T, D, generator=gen).requires_grad_()
+    g = torch.randn(rows, H, T // STRIDE, D, generator=gen)
+    flops = 14 * D * visible_pairs_per_head(docs, residue, STRIDE) * H
+    best = None
+    for _ in range(repeats + 1):  # first pass warms the allocator
+        t0 = time.perf_counter()
+        out = oracle.cyclic_attention_oracle(
+            q, k, v, query_stride=STRIDE, query_offset=residue, strict_past=True, metadata=meta,
+            compute_dtype=torch.float32,
+        )
+        torch.autograd.grad(out, (q, k, v), g)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    what = f"{rows} of {B} batch rows, residue {residue} of {STRIDE}, fwd+bwd fp32, oracle port on torch CPU"
+    return flops / best / 1e12, best, torch.get_num_threads(), what
+
+
+# --------------------------------------------------------------------------- drivers
+
+
+def run_reference_arm(args, rank, world):
+    """The upstream algorithm on the host cores (the CPU oracle port), bounded sample per step."""
+    if rank != 0:
+        return
+    rows = 2
+    for _ in range(args.warmup):
+        cpu_sample(rows=rows, repeats=0)
+    t0 = time.perf_counter()
+    values = [cpu_sample(rows=rows, repeats=0) for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    tflops = statistics.median(v[0] for v in values)
+    line = {
+        "impl": "reference", "metric": "cyclic_attention fwd+bwd TFLOP/s", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": values[0][2], "kind": "port", "sample": values[0][3]},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "cyclic_attention training sweep fwd+bwd: B=16 H=16 K=2048 Q=256/residue D=64 stride=8, "
+                    "8 residues per step, packed documents (geometric, mean 1024), strict_past, bf16",
+        "per_gpu_batch": B, "global_batch": B * n_gpus, "heads": H, "key_len": T, "head_dim": D,
+        "query_stride": STRIDE, "parallelism": f"replicas x{n_gpus} over batch (no collective)",
+        "l2": "inputs larger than L2: K+V 134 MB per sweep, rotated over 2 input sets",
+        "flops": "14*D per visible (query,key) pair",
+    }
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--backend", default="sm100", help="kernel family: sm100 | sm100_simt | sm100_tcgen05")
+    parser.add_argument("--skip-extras", action="store_true", help="only the headline workload (used for profiling)")
+    args = parser.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sm_100a kernels have no CPU path")
+    args.warmup = max(args.warmup, 3)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    from white_matter_b200 import _native
+
+    lib = _native.load_library()
+    peaks, peak_kind = load_peaks()
+    sets = [TrainingSweep(device, seed=rank * 2 + i, backend=args.backend) for i in range(2)]
+    turn = [0]
+
+    def step():
+        sets[turn[0] % 2].step()
+        turn[0] += 1
+
+    sampler = ClockSampler(local)
+    for _ in range(args.warmup):
+        step()
+    sync()
+    sampler.start()
+    launches0 = lib.wm_kernel_launch_count()
+    ms = time_steps(step, args.steps, 0, sync)
+    launches = lib.wm_kernel_launch_count() - launches0
+    clocks = sampler.stop()
+    flops = sum(sets[i % 2].flops for i in range(args.steps))
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    f = torch.tensor([float(flops)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(f, op=dist.ReduceOp.SUM)
+    value = f.item() / (t.item() * 1e-3) / 1e12
+
+    # per-operator device time inside a timed pass: forward (one kernel) and backward (its kernel group)
+    work = sets[0]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(STRIDE)]
+    for r in range(STRIDE):
+        ev[r][0].record()
+        out = work.forward(r)
+        ev[r][1].record()
+        torch.autograd.grad(out, (work.q[r], work.k, work.v), work.g[r])
+        ev[r][2].record()
+    torch.cuda.synchronize()
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / STRIDE
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / STRIDE
+    tensor_peak = peaks["bf16_tflops_sustained"]
+    fwd_tf = work.flops_fwd / STRIDE / (fwd_ms * 1e-3) / 1e12
+    bwd_tf = (work.flops - work.flops_fwd) / STRIDE / (bwd_ms * 1e-3) / 1e12
+
+    # end to end: pinned host -> device -> pinned host every step
+    staging = sets[0].staging()
+    e2e_step = lambda: sets[0].step_e2e(staging)
+    e2e_ms = time_steps(e2e_step, max(2, args.steps // 2), 2, sync)
+    e2e_steps = max(2, args.steps // 2)
+    te = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = sets[0].flops * e2e_steps * world / (te.item() * 1e-3) / 1e12
+
+    extras = {}
+    if not args.skip_extras:
+        del staging
+        torch.cuda.empty_cache()
+        extras["decode"] = bench_decode(device, peaks)
+        extras["mixing"] = bench_mixing(device, peaks)
+    if rank == 0:
+        line = {
+            "metric": "cyclic_attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t.item() / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
+            "backend": args.backend,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": sets[0].staging_bytes()[0],
+                    "d2h_bytes_per_step": sets[0].staging_bytes()[1]},
+            "roofline": {"bound": "tensor", "kernel": "backward kernel group of one residue call",
+                         "achieved": bwd_tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": bwd_tf / tensor_peak,
+                         "traffic": None, "peak_kind": f"{peak_kind} bf16_tflops_sustained", "ms": bwd_ms},
+            "roofline_forward": {"bound": "tensor", "kernel": "forward kernel of one residue call",
+                                 "achieved": fwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
+                                 "frac": fwd_tf / tensor_peak, "traffic": None, "ms": fwd_ms},
+        }
+        line.update(extras)
+        if world == 1 and not args.skip_extras:
+            tf, secs, cores, what = cpu_sample(rows=2, repeats=1)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": what, "seconds": secs}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -155,6 +155,12 @@ typedef struct wm_mix_args {
 
 WM_API int wm_abi_version(void);
 WM_API const char* wm_last_error(void);
+/* Status word of the pipelined kernels on the current device: 0 when every bounded
+ * wait inside them completed, else the code of the first wait that gave up.
+ * Synchronises the device; reset != 0 clears the word. */
+WM_API int wm_device_status(int reset);
+/* Number of kernels this library has launched in the process so far (diagnostic). */
+WM_API unsigned long long wm_kernel_launch_count(void);
 
 /* Rows per tile that the kernel selected for `args` cuts packed groups into
  * (queries when key_side == 0, keys otherwise; backward != 0 for the gradient kernels). */

@@ -1,0 +1,181 @@
+"""strict_causal_attention on the GPU: Jacobi prefill, cached-prefix prefill and decode (through the C ABI)."""
+
+import pytest
+import torch
+
+from helpers import BF16_TOL, F32_TOL, Golden, assert_parity, geometric_documents
+from oracle import attention_oracle as oracle
+from white_matter_b200 import prepare_strict_causal_metadata, strict_causal_attention
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not torch.cuda.is_available(), reason="requires CUDA")]
+G = Golden()
+BACKENDS = ["sm100_simt", "sm100"]
+
+
+def run_case(case, dtype, backend):
+    c = G.cases[case]
+    d = G.strict_inputs(case)
+    dev = "cuda"
+    q, k, v = (d[n].to(dev, dtype).requires_grad_(c["grads"]) for n in ("q", "k", "v"))
+    start = d["query_start"].to(dev) if isinstance(d["query_start"], torch.Tensor) else d["query_start"]
+    lengths = None if d["kv_lengths"] is None else d["kv_lengths"].to(dev)
+    mask = None if d["key_mask"] is None else d["key_mask"].to(dev)
+    metadata = None
+    if c["packed"]:
+        metadata = prepare_strict_causal_metadata(
+            d["docs"].to(dev), c["T"], query_start=start, kv_lengths=lengths, use_dummy_token=c["dummy"]
+        )
+    out = strict_causal_attention(
+        q, k, v, query_start=start, kv_lengths=lengths, use_dummy_token=c["dummy"], metadata=metadata, key_mask=mask,
+        backend=backend,
+    )
+    assert out.shape == (c["B"], c["T"], c["H"], c["D"])
+    grads = None
+    if c["grads"]:
+        grads = torch.autograd.grad(out, (q, k, v), d["probe"].to(dev, dtype))
+    return out, grads, d
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("case", G.names("strict"))
+def test_fp32_matches_reference_vectors(case, backend):
+    out, grads, _ = run_case(case, torch.float32, backend)
+    assert_parity(out, G.get(case, "out_f32"), what="out", **F32_TOL)
+    if grads is not None:
+        for g, name in zip(grads, ("dq_f32", "dk_f32", "dv_f32")):
+            assert_parity(g, G.get(case, name), what=name, **F32_TOL)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("case", G.names("strict"))
+def test_bf16_matches_reference(case, backend):
+    c = G.cases[case]
+    out, grads, d = run_case(case, torch.bfloat16, backend)
+    qo, ko, vo = (d[n].bfloat16().double().requires_grad_(c["grads"]) for n in ("q", "k", "v"))
+    metadata = None
+    if c["packed"]:
+        metadata = prepare_strict_causal_metadata(
+            d["docs"], c["T"], query_start=d["query_start"], kv_lengths=d["kv_lengths"], use_dummy_token=c["dummy"]
+        )
+    exp = oracle.strict_causal_oracle(
+        qo, ko, vo, query_start=d["query_start"], kv_lengths=d["kv_lengths"], use_dummy_token=c["dummy"],
+        metadata=metadata, key_mask=d["key_mask"],
+    )
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    if grads is not None:
+        exp_grads = torch.autograd.grad(exp, (qo, ko, vo), d["probe"].bfloat16().double())
+        for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+            assert_parity(g.float(), e, what=name, **BF16_TOL)
+
+
+@pytest.mark.parametrize("dummy", [False, True])
+def test_unused_capacity_may_hold_nan(dummy):
+    # upstream tests/unit/test_strict_causal_attention.py:80-94
+    torch.manual_seed(2)
+    q = torch.randn(3, 4, 1, 64, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(3, 2, 9 + int(dummy), 64, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    lengths = torch.tensor([0, 3, 7], device="cuda", dtype=torch.int32)
+    for b, n in enumerate(lengths.tolist()):
+        k[b, :, n + int(dummy):] = float("nan")
+        v[b, :, n + int(dummy):] = float("nan")
+    out = strict_causal_attention(q, k, v, query_start=lengths, kv_lengths=lengths, use_dummy_token=dummy)
+    exp = oracle.strict_per_query_oracle(q.cpu(), k.cpu(), v.cpu(), lengths.cpu(), dummy)
+    assert torch.isfinite(out).all()
+    assert_parity(out.float(), exp, what="decode", **BF16_TOL)
+    if not dummy:
+        assert out[0].abs().max().item() == 0  # a row without keys is exactly zero
+
+
+def test_future_keys_get_exactly_zero_gradient():
+    q = torch.randn(1, 2, 1, 64, device="cuda", requires_grad=True)
+    k = torch.randn(1, 1, 7, 64, device="cuda", requires_grad=True)
+    v = torch.randn_like(k, requires_grad=True)
+    strict_causal_attention(q, k, v, query_start=3).sum().backward()
+    assert k.grad[..., 3:, :].count_nonzero() == v.grad[..., 3:, :].count_nonzero() == 0
+    assert k.grad[..., :3, :].count_nonzero() > 0
+
+
+@pytest.mark.parametrize("dummy", [False, True])
+def test_decode_in_cuda_graph_with_device_lengths(dummy):
+    # upstream tests/unit/test_strict_causal_attention.py:277-331: lengths change between replays
+    torch.manual_seed(4)
+    q = torch.randn(3, 4, 1, 64, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(3, 4, 33 + int(dummy), 64, device="cuda", dtype=torch.bfloat16)[:, :2]  # strided head view
+    v = torch.randn(3, 4, 33 + int(dummy), 64, device="cuda", dtype=torch.bfloat16)[:, :2]
+    lengths = torch.tensor([0, 7, 16], device="cuda", dtype=torch.int32)
+
+    def step():
+        return strict_causal_attention(q, k, v, query_start=lengths, use_dummy_token=dummy, static_cache=True)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = step()
+    for values in ([0, 7, 16], [3, 12, 32]):
+        lengths.copy_(torch.tensor(values, device="cuda", dtype=torch.int32))
+        for row, n in enumerate(values):
+            k[row, :, : n + int(dummy)].normal_()
+            v[row, :, : n + int(dummy)].normal_()
+            k[row, :, n + int(dummy):] = float("nan")
+            v[row, :, n + int(dummy):] = float("nan")
+        graph.replay()
+        eager = step()
+        exp = oracle.strict_per_query_oracle(q.cpu(), k.cpu(), v.cpu(), lengths.cpu(), dummy)
+        assert_parity(captured.float(), exp, what="replayed", **BF16_TOL)
+        assert torch.equal(captured, eager)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_jacobi_prefill_reuses_one_schedule(backend):
+    """Packed documents (geometric lengths), one schedule reused over iterations with fresh Q/K/V."""
+    B, H, T, D = 2, 4, 512, 64
+    docs = geometric_documents(B, T, 128, seed=7)
+    schedule = prepare_strict_causal_metadata(docs.cuda(), T)
+    cpu_schedule = prepare_strict_causal_metadata(docs, T)
+    for it in range(2):
+        torch.manual_seed(100 + it)
+        q = (torch.randn(B, H, T, D) / 8).bfloat16()
+        k = torch.randn(B, H, T, D).bfloat16()
+        v = torch.randn(B, H, T, D).bfloat16()
+        out = strict_causal_attention(q.cuda(), k.cuda(), v.cuda(), metadata=schedule, backend=backend)
+        exp = oracle.strict_causal_oracle(q, k, v, metadata=cpu_schedule)
+        assert_parity(out.float(), exp, what=f"iteration {it}", **BF16_TOL)
+        starts = torch.ones_like(docs, dtype=torch.bool)
+        starts[:, 1:] = docs[:, 1:] != docs[:, :-1]
+        assert out[starts.cuda()].abs().max().item() == 0  # each document's first token
+
+
+def test_pool_read_at_full_size_matches_a_device_side_evaluation():
+    """B=64,H=16,D=64 pool of 8192 slots, lengths uniform in [1,8192]; decode and 128-token cached-prefix prefill.
+
+    Too large for the CPU oracle: the expected values are evaluated per batch
+    row with plain fp32 tensor arithmetic on the device.
+    """
+    torch.manual_seed(0)
+    B, H, N, D = 64, 16, 8192, 64
+    lengths = torch.randint(1, N + 1, (B,), device="cuda")
+    k = torch.randn(B, H, N, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, H, N, D, device="cuda", dtype=torch.bfloat16)
+    for b in range(B):
+        k[b, :, int(lengths[b]):] = float("nan")
+        v[b, :, int(lengths[b]):] = float("nan")
+    q1 = torch.randn(B, H, 1, D, device="cuda", dtype=torch.bfloat16)
+    out = strict_causal_attention(q1, k, v, query_start=lengths, kv_lengths=lengths)
+    q128 = torch.randn(B, H, 128, D, device="cuda", dtype=torch.bfloat16)
+    starts = (lengths - 128).clamp_min(0)
+    pre = strict_causal_attention(q128, k, v, query_start=starts, kv_lengths=lengths)
+    for b in range(0, B, 7):
+        n = int(lengths[b])
+        kk, vv = k[b, :, :n].float(), v[b, :, :n].float()
+        exp = torch.softmax(q1[b].float() @ kk.transpose(-1, -2) / 8, -1) @ vv
+        assert_parity(out[b].transpose(0, 1).float(), exp, what=f"decode row {b}", **BF16_TOL)
+        pos = int(starts[b]) + torch.arange(128, device="cuda")
+        keep = torch.arange(n, device="cuda")[None, :] < pos[:, None]
+        s = (q128[b].float() @ kk.transpose(-1, -2) / 8).masked_fill(~keep, float("-inf"))
+        p = torch.softmax(s, -1).nan_to_num(0.0)
+        assert_parity(pre[b].transpose(0, 1).float(), p @ vv, what=f"prefill row {b}", **BF16_TOL)

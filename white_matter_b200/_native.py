@@ -112,6 +112,8 @@ MIX_ENTRY_POINTS = ("wm_mix_sources_fwd", "wm_mix_sources_bwd")
 QUERY_ENTRY_POINTS = (
     "wm_abi_version",
     "wm_last_error",
+    "wm_kernel_launch_count",
+    "wm_device_status",
     "wm_attn_tile_rows",
     "wm_attn_fwd_workspace_bytes",
     "wm_attn_bwd_workspace_bytes",
@@ -149,6 +151,10 @@ def load_library() -> ctypes.CDLL:
         lib.wm_abi_version.restype = ctypes.c_int
         lib.wm_last_error.argtypes = []
         lib.wm_last_error.restype = ctypes.c_char_p
+        lib.wm_kernel_launch_count.argtypes = []
+        lib.wm_kernel_launch_count.restype = ctypes.c_ulonglong
+        lib.wm_device_status.argtypes = [ctypes.c_int]
+        lib.wm_device_status.restype = ctypes.c_int
         lib.wm_attn_tile_rows.argtypes = [ctypes.POINTER(AttnArgs), ctypes.c_int, ctypes.c_int]
         lib.wm_attn_tile_rows.restype = ctypes.c_int
         for name in ("wm_attn_fwd_workspace_bytes", "wm_attn_bwd_workspace_bytes", "wm_strict_decode_workspace_bytes"):
@@ -188,3 +194,8 @@ def call(name: str, args, device: torch.device) -> None:
     if status != 0:
         message = lib.wm_last_error().decode(errors="replace")
         raise RuntimeError(f"{name} failed ({status}): {message}")
+
+
+def device_status(reset: bool = True) -> int:
+    """Status word of the pipelined kernels (0 = every bounded wait completed); synchronises the device."""
+    return load_library().wm_device_status(int(reset))

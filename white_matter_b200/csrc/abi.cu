@@ -1,7 +1,9 @@
 // extern "C" entry points of libwm_b200: argument validation and kernel
 // selection.  Nothing here allocates device memory or synchronises the host.
+#include <atomic>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -9,7 +11,10 @@ namespace wm {
 
 namespace {
 thread_local char g_error[512] = "";
+std::atomic<unsigned long long> g_launches{0};
 }
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -64,6 +69,17 @@ int validate_attn(const wm_attn_args* a, bool backward, const char* who) {
   return WM_OK;
 }
 
+// WM_B200_FORCE_SIMT=1 in the environment routes every attention call to the SIMT kernels (bring-up aid).
+bool force_simt() {
+  static const bool forced = [] {
+    const char* v = getenv("WM_B200_FORCE_SIMT");
+    return v != nullptr && v[0] == '1';
+  }();
+  return forced;
+}
+
+bool want_tc(const wm_attn_args* a) { return a->kernel != WM_KERNEL_SIMT && !(force_simt() && a->kernel == WM_KERNEL_AUTO); }
+
 namespace {
 
 int run_fwd(const wm_attn_args* a, void* stream, int family, bool docs, const char* who) {
@@ -73,7 +89,7 @@ int run_fwd(const wm_attn_args* a, void* stream, int family, bool docs, const ch
   if (family == WM_MASK_CYCLIC && docs != (a->q_seg != nullptr))
     return fail(WM_EINVAL, "%s: document tensors %s", who, docs ? "are required" : "must be NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (a->kernel != WM_KERNEL_SIMT && tc_fwd_supported(*a)) return tc_attn_fwd(*a, s);
+  if (want_tc(a) && tc_fwd_supported(*a)) return tc_attn_fwd(*a, s);
   if (a->kernel == WM_KERNEL_TCGEN05) return fail(WM_EUNSUPPORTED, "%s: problem does not qualify for the tcgen05 kernel", who);
   return simt_attn_fwd(*a, s);
 }
@@ -85,7 +101,7 @@ int run_bwd(const wm_attn_args* a, void* stream, int family, bool docs, const ch
   if (family == WM_MASK_CYCLIC && docs != (a->q_seg != nullptr))
     return fail(WM_EINVAL, "%s: document tensors %s", who, docs ? "are required" : "must be NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (a->kernel != WM_KERNEL_SIMT && tc_bwd_supported(*a)) return tc_attn_bwd(*a, s);
+  if (want_tc(a) && tc_bwd_supported(*a)) return tc_attn_bwd(*a, s);
   if (a->kernel == WM_KERNEL_TCGEN05) return fail(WM_EUNSUPPORTED, "%s: problem does not qualify for the tcgen05 kernel", who);
   return simt_attn_bwd(*a, s);
 }
@@ -99,10 +115,14 @@ int wm_abi_version(void) { return WM_B200_ABI_VERSION; }
 
 const char* wm_last_error(void) { return wm::g_error; }
 
+int wm_device_status(int reset) { return wm::tc_device_status(reset != 0); }
+
+unsigned long long wm_kernel_launch_count(void) { return wm::g_launches.load(std::memory_order_relaxed); }
+
 int wm_attn_tile_rows(const wm_attn_args* a, int backward, int key_side) {
   if (a == nullptr) return 0;
   (void)key_side;
-  if (a->kernel != WM_KERNEL_SIMT && (backward ? wm::tc_bwd_supported(*a) : wm::tc_fwd_supported(*a))) return 128;
+  if (wm::want_tc(a) && (backward ? wm::tc_bwd_supported(*a) : wm::tc_fwd_supported(*a))) return 128;
   return wm::simt_tile_rows(a->head_dim);
 }
 
@@ -113,7 +133,7 @@ size_t wm_attn_fwd_workspace_bytes(const wm_attn_args* a) {
 
 size_t wm_attn_bwd_workspace_bytes(const wm_attn_args* a) {
   if (a == nullptr) return 0;
-  if (a->kernel != WM_KERNEL_SIMT && wm::tc_bwd_supported(*a)) return wm::tc_attn_bwd_workspace(*a);
+  if (wm::want_tc(a) && wm::tc_bwd_supported(*a)) return wm::tc_attn_bwd_workspace(*a);
   return wm::simt_attn_bwd_workspace(*a);
 }
 

@@ -654,13 +654,13 @@ int launch_fwd(const wm_attn_args& a, cudaStream_t stream) {
     long long rows = static_cast<long long>(a.batch) * a.q_heads * a.q_len;
     int blocks = static_cast<int>(rows / 8 + 1 < 4096 ? rows / 8 + 1 : 4096);
     zero_rows_kernel<T><<<blocks, zb, 0, stream>>>(static_cast<T*>(a.out), a.out_strides[0], a.out_strides[1],
-                                                    a.out_strides[2], a.batch, a.q_heads, a.q_len, a.head_dim, a.lse);
+                                                    a.out_strides[2], a.batch, a.q_heads, a.q_len, a.head_dim, a.lse); count_launch();
     if (a.n_query_tiles == 0) return cuda_check(cudaGetLastError(), "zero_rows_kernel");
     grid = dim3(a.n_query_tiles, a.q_heads, 1);
   } else {
     grid = dim3((a.q_len + ROWS - 1) / ROWS, a.q_heads, a.batch);
   }
-  attn_fwd_kernel<T, TPR><<<grid, kThreads, 0, stream>>>(a, f);
+  attn_fwd_kernel<T, TPR><<<grid, kThreads, 0, stream>>>(a, f); count_launch();
   return cuda_check(cudaGetLastError(), "attn_fwd_kernel");
 }
 
@@ -687,31 +687,31 @@ int launch_bwd(const wm_attn_args& a, cudaStream_t stream) {
     long long rows = static_cast<long long>(a.batch) * a.q_heads * a.q_len;
     int blocks = static_cast<int>(rows / 8 + 1 < 4096 ? rows / 8 + 1 : 4096);
     zero_rows_kernel<T><<<blocks, zb, 0, stream>>>(static_cast<T*>(a.dq), a.dq_strides[0], a.dq_strides[1],
-                                                    a.dq_strides[2], a.batch, a.q_heads, a.q_len, a.head_dim, nullptr);
+                                                    a.dq_strides[2], a.batch, a.q_heads, a.q_len, a.head_dim, nullptr); count_launch();
     qgrid = dim3(a.n_query_tiles, a.q_heads, 1);
   } else {
     qgrid = dim3((a.q_len + ROWS - 1) / ROWS, a.q_heads, a.batch);
     kgrid = dim3((a.k_len + ROWS - 1) / ROWS, a.kv_heads, a.batch);
   }
   if (a.mask != WM_MASK_PACKED || a.n_query_tiles > 0) {
-    attn_dq_kernel<T, TPR><<<qgrid, kThreads, 0, stream>>>(a, f, delta);
+    attn_dq_kernel<T, TPR><<<qgrid, kThreads, 0, stream>>>(a, f, delta); count_launch();
     WM_CUDA(cudaGetLastError());
   }
   if (a.mask == WM_MASK_PACKED) {
     if (a.n_key_tiles > 0) {
       kgrid = dim3(a.n_key_tiles, a.kv_heads, 1);
-      attn_dkv_kernel<T, TPR><<<kgrid, kThreads, 0, stream>>>(a, f, delta, dk_acc, dv_acc);
+      attn_dkv_kernel<T, TPR><<<kgrid, kThreads, 0, stream>>>(a, f, delta, dk_acc, dv_acc); count_launch();
       WM_CUDA(cudaGetLastError());
     }
     dim3 zb(32, 8);
     long long rows = static_cast<long long>(a.batch) * a.kv_heads * a.k_len;
     int blocks = static_cast<int>(rows / 8 + 1 < 4096 ? rows / 8 + 1 : 4096);
     cast_rows_kernel<T><<<blocks, zb, 0, stream>>>(dk_acc, static_cast<T*>(a.dk), a.dk_strides[0], a.dk_strides[1],
-                                                    a.dk_strides[2], a.batch, a.kv_heads, a.k_len, a.head_dim);
+                                                    a.dk_strides[2], a.batch, a.kv_heads, a.k_len, a.head_dim); count_launch();
     cast_rows_kernel<T><<<blocks, zb, 0, stream>>>(dv_acc, static_cast<T*>(a.dv), a.dv_strides[0], a.dv_strides[1],
-                                                    a.dv_strides[2], a.batch, a.kv_heads, a.k_len, a.head_dim);
+                                                    a.dv_strides[2], a.batch, a.kv_heads, a.k_len, a.head_dim); count_launch();
   } else {
-    attn_dkv_kernel<T, TPR><<<kgrid, kThreads, 0, stream>>>(a, f, delta, nullptr, nullptr);
+    attn_dkv_kernel<T, TPR><<<kgrid, kThreads, 0, stream>>>(a, f, delta, nullptr, nullptr); count_launch();
   }
   return cuda_check(cudaGetLastError(), "attention backward");
 }

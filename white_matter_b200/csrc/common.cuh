@@ -14,6 +14,7 @@ namespace wm {
 // ---------------------------------------------------------------- host helpers
 int fail(int code, const char* fmt, ...);
 int cuda_check(cudaError_t status, const char* what);
+void count_launch();  // one more kernel launched by this library (diagnostic counter)
 
 #define WM_CUDA(expr)                                   \
   do {                                                  \
@@ -39,6 +40,7 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream);
 bool tc_bwd_supported(const wm_attn_args& a);
 int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream);
 size_t tc_attn_bwd_workspace(const wm_attn_args& a);
+int tc_device_status(bool reset);
 
 // ---------------------------------------------------------------- device side
 constexpr float kLog2e = 1.4426950408889634f;

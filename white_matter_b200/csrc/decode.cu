@@ -275,23 +275,23 @@ int launch(const wm_attn_args& a, float* partial, cudaStream_t stream) {
   const int hpk = a.q_heads / a.kv_heads;
   if (hpk == 2) {
     dim3 grid(splits, a.kv_heads, a.batch);
-    decode_split_kernel<T, LPK, 2><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits);
+    decode_split_kernel<T, LPK, 2><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits); count_launch();
   } else if (hpk == 4) {
     dim3 grid(splits, a.kv_heads, a.batch);
-    decode_split_kernel<T, LPK, 4><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits);
+    decode_split_kernel<T, LPK, 4><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits); count_launch();
   } else {
     dim3 grid(splits, a.q_heads, a.batch);
     if (hpk == 1) {
-      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits);
+      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits); count_launch();
     } else {
       // other group sizes: one block per query head, K/V re-read through L2
       wm_attn_args single = a;
-      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(single, partial, chunk, splits);
+      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(single, partial, chunk, splits); count_launch();
     }
   }
   WM_CUDA(cudaGetLastError());
   int threads = a.head_dim <= 64 ? 64 : 128;
-  decode_merge_kernel<T><<<dim3(a.q_heads, a.batch), threads, 0, stream>>>(a, partial, chunk, splits);
+  decode_merge_kernel<T><<<dim3(a.q_heads, a.batch), threads, 0, stream>>>(a, partial, chunk, splits); count_launch();
   return cuda_check(cudaGetLastError(), "decode_merge_kernel");
 }
 

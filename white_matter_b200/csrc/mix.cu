@@ -222,10 +222,12 @@ int mix_fwd_launch(const wm_mix_args& a, cudaStream_t stream) {
   int status = check(a, false);
   if (status != WM_OK) return status;
   if (a.n == 0) return WM_OK;
-  if (a.dtype == WM_F32)
+  if (a.dtype == WM_F32) {
     mix_fwd_kernel<float><<<grid_for(a.n / 4), kThreads, 0, stream>>>(a);
-  else
+  } else {
     mix_fwd_kernel<__nv_bfloat16><<<grid_for(a.n / 8), kThreads, 0, stream>>>(a);
+  }
+  count_launch();
   return cuda_check(cudaGetLastError(), "mix_fwd_kernel");
 }
 
@@ -235,14 +237,16 @@ int mix_bwd_launch(const wm_mix_args& a, cudaStream_t stream) {
   float* gsum = a.dlogits != nullptr ? static_cast<float*>(a.workspace) : nullptr;
   if (gsum != nullptr) WM_CUDA(cudaMemsetAsync(gsum, 0, kMaxSources * sizeof(float), stream));
   if (a.n > 0) {
-    if (a.dtype == WM_F32)
+    if (a.dtype == WM_F32) {
       mix_bwd_kernel<float><<<grid_for(a.n / 4), kThreads, 0, stream>>>(a, gsum);
-    else
+    } else {
       mix_bwd_kernel<__nv_bfloat16><<<grid_for(a.n / 8), kThreads, 0, stream>>>(a, gsum);
+    }
+    count_launch();
     WM_CUDA(cudaGetLastError());
   }
   if (gsum != nullptr) {
-    mix_dlogits_kernel<<<1, 32, 0, stream>>>(a.logits, gsum, a.dlogits, a.n_sources);
+    mix_dlogits_kernel<<<1, 32, 0, stream>>>(a.logits, gsum, a.dlogits, a.n_sources); count_launch();
     WM_CUDA(cudaGetLastError());
   }
   return WM_OK;
