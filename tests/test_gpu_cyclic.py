@@ -142,7 +142,8 @@ def test_invisible_keys_get_exactly_zero_gradient(documents, backend):
     grads = torch.autograd.grad(out, (q, k, v), torch.randn_like(out))
     for g in grads[1:]:
         assert g[:, :, 1:].abs().max().item() == 0
-        assert g[:, :, :1].abs().max().item() > 0
+    # the single visible key takes all the weight: dV there is the upstream gradient, dK is exactly zero
+    assert grads[2][:, :, :1].abs().max().item() > 0
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
