@@ -175,6 +175,28 @@ class TrainingSweep:
             out = self.forward(r)
             torch.autograd.grad(out, (self.q[r], self.k, self.v), self.g[r])
 
+    def capture(self):
+        """Capture one step in a CUDA graph (the 16 operator calls are launch-bound when issued eagerly).
+
+        Returns the number of kernels of this library inside the graph."""
+        from white_matter_b200 import _native
+
+        lib = _native.load_library()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        before = lib.wm_kernel_launch_count()
+        with torch.cuda.graph(self.graph):
+            self.step()
+        return lib.wm_kernel_launch_count() - before
+
+    def replay(self):
+        self.graph.replay()
+
     def step_e2e(self, staging):
         """One step from pinned host buffers to pinned host results."""
         k = staging["k"].copy_(self.host["k"], non_blocking=True).detach().requires_grad_()
@@ -348,6 +370,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--backend", default="sm100", help="kernel family: sm100 | sm100_simt | sm100_tcgen05")
+    parser.add_argument("--no-graph", action="store_true", help="issue the operator calls eagerly instead of replaying a CUDA graph")
     parser.add_argument("--skip-extras", action="store_true", help="only the headline workload (used for profiling)")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -378,9 +401,15 @@ def main():
     peaks, peak_kind = load_peaks()
     sets = [TrainingSweep(device, seed=rank * 2 + i, backend=args.backend) for i in range(2)]
     turn = [0]
+    per_step_launches = None
+    if not args.no_graph:
+        per_step_launches = [s.capture() for s in sets][0]
 
     def step():
-        sets[turn[0] % 2].step()
+        if args.no_graph:
+            sets[turn[0] % 2].step()
+        else:
+            sets[turn[0] % 2].replay()
         turn[0] += 1
 
     sampler = ClockSampler(local)
@@ -391,6 +420,8 @@ def main():
     launches0 = lib.wm_kernel_launch_count()
     ms = time_steps(step, args.steps, 0, sync)
     launches = lib.wm_kernel_launch_count() - launches0
+    if per_step_launches is not None:
+        launches = per_step_launches * args.steps  # kernels inside the replayed graphs
     clocks = sampler.stop()
     flops = sum(sets[i % 2].flops for i in range(args.steps))
     t = torch.tensor([ms], device=device, dtype=torch.float64)
@@ -438,7 +469,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": t.item() / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
-            "backend": args.backend,
+            "backend": args.backend, "launch_mode": "eager" if args.no_graph else "cuda graph replay of one step",
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": sets[0].staging_bytes()[0],
                     "d2h_bytes_per_step": sets[0].staging_bytes()[1]},
             "roofline": {"bound": "tensor", "kernel": "backward kernel group of one residue call",

@@ -1,0 +1,437 @@
+// Backward pipeline of the tcgen05 attention kernel (included by attn_tc.cu).
+#pragma once
+
+// ===========================================================================
+// backward: one CTA per tile of 128 key slots of one (batch, kv head).
+//
+// For every query tile that can see the key tile (and every query head of the
+// group) the CTA recomputes S = Q K^T and dP = dO V^T on the tensor cores,
+// forms P = exp2(S*scale*log2e - lse) and dS = P*(dP - delta) in registers
+// (thread t == query row t), stores both as bf16 in one [query][key] swizzled
+// shared-memory tile each, and issues dV += P^T dO, dK += dS^T Q (accumulated
+// in TMEM over the whole walk) and dQ = dS K (added to an fp32 accumulator in
+// global memory with vector reductions, converted to bf16 by a last kernel).
+// The same shared tile serves as K-major operand (dS K) and as MN-major
+// operand (P^T dO, dS^T Q); Q and dO tiles likewise serve as A (K-major) and
+// as B (MN-major).
+// TMEM columns: S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ [384,448).
+constexpr int kBwdStages = 2;
+
+struct BwdShared {
+  unsigned char k[kTileBytes];
+  unsigned char v[kTileBytes];
+  unsigned char q[kBwdStages][kTileBytes];
+  unsigned char g[kBwdStages][kTileBytes];  // dO tiles
+  unsigned char p[2 * kTileBytes];
+  unsigned char ds[2 * kTileBytes];
+  uint64_t kv_full, kv_ready;
+  uint64_t qg_full[kBwdStages], qg_empty[kBwdStages];
+  uint64_t sdp_full, pds_full, mma_done, dq_full, dq_free;
+  int key_seg[kTileN];
+  int key_end[kTileN];
+  int summary[4][4];  // per warp: min seg, max seg, min end, max end
+  int row_first, row_end;
+  uint32_t tmem_base;
+  int abort_flag;
+  int epoch;
+};
+
+// delta = rowsum(dO * O) in fp32, one thread per (batch, head, query) row of 64 values
+__global__ void bwd_delta_kernel(const wm_attn_args a, float* delta) {
+  const long long rows = static_cast<long long>(a.batch) * a.q_heads * a.q_len;
+  const long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (row >= rows) return;
+  const int i = static_cast<int>(row % a.q_len);
+  const int h = static_cast<int>((row / a.q_len) % a.q_heads);
+  const int b = static_cast<int>(row / (static_cast<long long>(a.q_len) * a.q_heads));
+  const uint4* o = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.out) + b * a.out_strides[0] +
+                                                  h * a.out_strides[1] + static_cast<long long>(i) * a.out_strides[2]);
+  const uint4* g = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.dout) + b * a.dout_strides[0] +
+                                                  h * a.dout_strides[1] + static_cast<long long>(i) * a.dout_strides[2]);
+  float acc = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 x = o[c], y = g[c];
+    const unsigned xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      acc = fmaf(__uint_as_float(xs[e] << 16), __uint_as_float(ys[e] << 16), acc);
+      acc = fmaf(__uint_as_float(xs[e] & 0xffff0000u), __uint_as_float(ys[e] & 0xffff0000u), acc);
+    }
+  }
+  delta[row] = acc;
+}
+
+// dq = bf16(scale * accumulator); accumulator is (batch, heads, queries, 64) fp32
+__global__ void bwd_dq_convert_kernel(const wm_attn_args a, const float* acc) {
+  const long long chunks = static_cast<long long>(a.batch) * a.q_heads * a.q_len * 8;  // 8 values each
+  const long long at = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (at >= chunks) return;
+  const long long row = at >> 3;
+  const int c = static_cast<int>(at & 7);
+  const int i = static_cast<int>(row % a.q_len);
+  const int h = static_cast<int>((row / a.q_len) % a.q_heads);
+  const int b = static_cast<int>(row / (static_cast<long long>(a.q_len) * a.q_heads));
+  const float4 lo = *reinterpret_cast<const float4*>(acc + row * kHeadDim + c * 8);
+  const float4 hi = *reinterpret_cast<const float4*>(acc + row * kHeadDim + c * 8 + 4);
+  const float s = a.scale;
+  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.dq) + b * a.dq_strides[0] + h * a.dq_strides[1] +
+                       static_cast<long long>(i) * a.dq_strides[2] + c * 8;
+  *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(lo.x * s, lo.y * s), pack_bf16(lo.z * s, lo.w * s),
+                                              pack_bf16(hi.x * s, hi.y * s), pack_bf16(hi.z * s, hi.w * s));
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a0, float a1, float a2, float a3) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a0), "f"(a1), "f"(a2), "f"(a3)
+               : "memory");
+}
+
+struct BwdWalk {
+  int qt_first;  // first query tile that can see the key tile
+  int qt_count;  // number of query tiles to visit (0: none)
+  int heads;     // query heads per kv head
+  int n_iter;    // qt_count * heads
+  int kvis;      // exclusive bound of key slots any query can see
+};
+
+__device__ __forceinline__ void bwd_iter_coords(const BwdWalk& w, int it, int kv_head, int& head, int& qt) {
+  const int g = it / w.qt_count;
+  qt = w.qt_first + (it - g * w.qt_count);
+  head = kv_head * w.heads + g;
+}
+
+__device__ __forceinline__ void bwd_producer(BwdShared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
+                                             const CUtensorMap* map_v, const CUtensorMap* map_g, const BwdWalk& w,
+                                             int j0, int kv_head, int batch) {
+  ptx::prefetch_tmap(map_q);
+  ptx::prefetch_tmap(map_k);
+  ptx::prefetch_tmap(map_v);
+  ptx::prefetch_tmap(map_g);
+  ptx::mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
+  ptx::tma_load_4d(sm.k, map_k, &sm.kv_full, 0, j0, kv_head, batch);
+  ptx::tma_load_4d(sm.v, map_v, &sm.kv_full, 0, j0, kv_head, batch);
+  for (int it = 0; it < w.n_iter; ++it) {
+    const int s = it % kBwdStages;
+    int head, qt;
+    bwd_iter_coords(w, it, kv_head, head, qt);
+    if (!wait_or_abort(sm, &sm.qg_empty[s], ((it / kBwdStages) & 1) ^ 1, 41)) return;
+    ptx::mbar_expect_tx(&sm.qg_full[s], 2 * kTileBytes);
+    ptx::tma_load_4d(sm.q[s], map_q, &sm.qg_full[s], 0, qt * kTileM, head, batch);
+    ptx::tma_load_4d(sm.g[s], map_g, &sm.qg_full[s], 0, qt * kTileM, head, batch);
+  }
+}
+
+__device__ __forceinline__ void bwd_mma(BwdShared& sm, uint32_t tmem, const BwdWalk& w) {
+  if (!wait_or_abort(sm, &sm.kv_ready, 0, 50)) return;
+  ptx::tc_fence_after();
+  constexpr uint32_t idesc_s = ptx::make_idesc_bf16(kTileM, kTileN, 0, 0);      // Q K^T, dO V^T
+  constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, kHeadDim, 1, 1);    // P^T dO, dS^T Q
+  constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);    // dS K
+  const uint32_t k_base = ptx::smem_u32(sm.k), v_base = ptx::smem_u32(sm.v);
+  const uint32_t p_base = ptx::smem_u32(sm.p), ds_base = ptx::smem_u32(sm.ds);
+  for (int it = 0; it < w.n_iter; ++it) {
+    const int s = it % kBwdStages;
+    if (!wait_or_abort(sm, &sm.qg_full[s], (it / kBwdStages) & 1, 51)) return;
+    ptx::tc_fence_after();
+    const uint32_t q_base = ptx::smem_u32(sm.q[s]), g_base = ptx::smem_u32(sm.g[s]);
+#pragma unroll
+    for (int kk = 0; kk < kHeadDim / 16; ++kk)
+      ptx::mma_bf16_ss(tmem, ptx::make_smem_desc_sw128(q_base + kk * 32, 16, 1024),
+                       ptx::make_smem_desc_sw128(k_base + kk * 32, 16, 1024), idesc_s, kk > 0);
+#pragma unroll
+    for (int kk = 0; kk < kHeadDim / 16; ++kk)
+      ptx::mma_bf16_ss(tmem + kTileN, ptx::make_smem_desc_sw128(g_base + kk * 32, 16, 1024),
+                       ptx::make_smem_desc_sw128(v_base + kk * 32, 16, 1024), idesc_s, kk > 0);
+    ptx::mma_commit(&sm.sdp_full);
+    if (!wait_or_abort(sm, &sm.pds_full, it & 1, 52)) return;
+    ptx::tc_fence_after();
+#pragma unroll
+    for (int kk = 0; kk < kTileM / 16; ++kk)  // 16 queries per instruction
+      ptx::mma_bf16_ss(tmem + 2 * kTileN, ptx::make_smem_desc_sw128(p_base + kk * 2048, kTileBytes, 1024),
+                       ptx::make_smem_desc_sw128(g_base + kk * 2048, 1024, 1024), idesc_t, (it > 0) || (kk > 0));
+#pragma unroll
+    for (int kk = 0; kk < kTileM / 16; ++kk)
+      ptx::mma_bf16_ss(tmem + 2 * kTileN + kHeadDim, ptx::make_smem_desc_sw128(ds_base + kk * 2048, kTileBytes, 1024),
+                       ptx::make_smem_desc_sw128(q_base + kk * 2048, 1024, 1024), idesc_t, (it > 0) || (kk > 0));
+    if (!wait_or_abort(sm, &sm.dq_free, (it & 1) ^ 1, 53)) return;
+    ptx::tc_fence_after();
+#pragma unroll
+    for (int kk = 0; kk < kTileN / 16; ++kk)  // 16 keys per instruction
+      ptx::mma_bf16_ss(tmem + 2 * kTileN + 2 * kHeadDim,
+                       ptx::make_smem_desc_sw128(ds_base + (kk >> 2) * kTileBytes + (kk & 3) * 32, 16, 1024),
+                       ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, kk > 0);
+    ptx::mma_commit(&sm.qg_empty[s]);
+    ptx::mma_commit(&sm.mma_done);
+    ptx::mma_commit(&sm.dq_full);
+  }
+}
+
+// compute threads of the backward kernel: thread t owns query row t of the current query tile (and, in
+// the prologue / epilogue, key row t of the CTA's key tile)
+__device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a, uint32_t tmem, const BwdWalk& w,
+                                            const float* delta, float* dq_acc, int j0, int kv_head, int batch) {
+  const int t = threadIdx.x;
+  const int warp = t >> 5;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const float sl2 = a.scale * kLog2e;
+  const bool docs = a.q_seg != nullptr;
+  const GroupCtx g = group_ctx(a, 0);
+
+  // prologue: key rows at or beyond the last visible slot may hold anything; clear them for the MMAs
+  if (!wait_or_abort(sm, &sm.kv_full, 0, 60)) return;
+  if (j0 + t >= w.kvis) {
+    uint4* krow = reinterpret_cast<uint4*>(sm.k + t * 128);
+    uint4* vrow = reinterpret_cast<uint4*>(sm.v + t * 128);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      krow[c] = make_uint4(0, 0, 0, 0);
+      vrow[c] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  ptx::fence_async_shared();
+  ptx::mbar_arrive(&sm.kv_ready);
+
+  int smin = 0, smax = 0, emin = 0;
+  if (docs) {
+    smin = min(min(sm.summary[0][0], sm.summary[1][0]), min(sm.summary[2][0], sm.summary[3][0]));
+    smax = max(max(sm.summary[0][1], sm.summary[1][1]), max(sm.summary[2][1], sm.summary[3][1]));
+    emin = min(min(sm.summary[0][2], sm.summary[1][2]), min(sm.summary[2][2], sm.summary[3][2]));
+  }
+
+  for (int it = 0; it < w.n_iter; ++it) {
+    int head, qt;
+    bwd_iter_coords(w, it, kv_head, head, qt);
+    const int i = qt * kTileM + t;
+    const bool live = i < a.q_len;
+    RowBound rb;
+    rb.lo = 0;
+    rb.hi = 0;
+    rb.seg = 0;
+    rb.qi = i;
+    float lse2 = INFINITY, dl = 0.f;
+    const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + i;
+    if (live) {
+      rb = row_bound(a, g, batch, i);
+      lse2 = a.lse[stat] * kLog2e;
+      dl = delta[stat];
+    }
+    bool none = !live || j0 >= rb.hi;
+    bool full = live && j0 + kTileN <= rb.hi;
+    if (docs && !none) {
+      const bool uniform = smin == smax;
+      full = full && uniform && smin == rb.seg && j0 >= rb.lo && emin > rb.qi;
+      if (uniform && smin != -1 && smin != rb.seg) none = true;
+    }
+    if (!wait_or_abort(sm, &sm.sdp_full, it & 1, 61)) return;
+    ptx::tc_fence_after();
+    // the shared P / dS tiles were last read by the MMAs of the previous iteration
+    if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 62)) return;
+    unsigned char* prow = sm.p + (t >> 3) * 1024 + (t & 7) * 128;
+    unsigned char* drow = sm.ds + (t >> 3) * 1024 + (t & 7) * 128;
+    const int lim = rb.hi - j0;
+#pragma unroll 1
+    for (int c = 0; c < kTileN / 32; ++c) {
+      uint32_t xs[32], ys[32];
+      ptx::tmem_ld32(tmem + lane_base + c * 32, xs);
+      ptx::tmem_ld32(tmem + kTileN + lane_base + c * 32, ys);
+      ptx::tmem_wait_ld();
+      uint32_t pp[16], dd[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int col = c * 32 + 2 * e + u;
+          bool vis = !none && (full || col < lim);
+          if (vis && docs && !full) vis = doc_visible(rb, j0 + col, sm.key_seg[col], sm.key_end[col]);
+          const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e + u]), sl2, -lse2));
+          pv[u] = vis ? p : 0.f;
+          dv[u] = vis ? p * (__uint_as_float(ys[2 * e + u]) - dl) : 0.f;
+        }
+        pp[e] = pack_bf16(pv[0], pv[1]);
+        dd[e] = pack_bf16(dv[0], dv[1]);
+      }
+      const int sub = (c >> 1) * kTileBytes;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int off = sub + ((((c & 1) * 4 + u) ^ (t & 7)) << 4);
+        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+        *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+      }
+    }
+    ptx::fence_async_shared();
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(&sm.pds_full);
+    // dQ of this (query tile, key tile) pair: add to the fp32 accumulator
+    if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return;
+    ptx::tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < kHeadDim / 32; ++c) {
+      uint32_t raw[32];
+      ptx::tmem_ld32(tmem + 2 * kTileN + 2 * kHeadDim + lane_base + c * 32, raw);
+      ptx::tmem_wait_ld();
+      if (live && !none) {
+        float* dst = dq_acc + stat * kHeadDim + c * 32;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          red_add_v4(dst + 4 * e, __uint_as_float(raw[4 * e]), __uint_as_float(raw[4 * e + 1]),
+                     __uint_as_float(raw[4 * e + 2]), __uint_as_float(raw[4 * e + 3]));
+      }
+    }
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(&sm.dq_free);
+  }
+
+  // epilogue: dV and dK rows of this key tile (dq_full of the last iteration covers every earlier MMA)
+  const int j = j0 + t;
+  uint32_t dv_pack[kHeadDim / 2], dk_pack[kHeadDim / 2];
+#pragma unroll
+  for (int e = 0; e < kHeadDim / 2; ++e) dv_pack[e] = dk_pack[e] = 0u;
+  if (w.n_iter > 0) {
+#pragma unroll
+    for (int c = 0; c < kHeadDim / 32; ++c) {
+      uint32_t raw[32];
+      ptx::tmem_ld32(tmem + 2 * kTileN + lane_base + c * 32, raw);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int e = 0; e < 16; ++e)
+        dv_pack[c * 16 + e] = pack_bf16(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1]));
+      ptx::tmem_ld32(tmem + 2 * kTileN + kHeadDim + lane_base + c * 32, raw);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int e = 0; e < 16; ++e)
+        dk_pack[c * 16 + e] =
+            pack_bf16(__uint_as_float(raw[2 * e]) * a.scale, __uint_as_float(raw[2 * e + 1]) * a.scale);
+    }
+  }
+  if (j < a.k_len) {
+    uint4* dvrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dv) + batch * a.dv_strides[0] +
+                                            kv_head * a.dv_strides[1] + static_cast<long long>(j) * a.dv_strides[2]);
+    uint4* dkrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dk) + batch * a.dk_strides[0] +
+                                            kv_head * a.dk_strides[1] + static_cast<long long>(j) * a.dk_strides[2]);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      dvrow[c] = make_uint4(dv_pack[4 * c], dv_pack[4 * c + 1], dv_pack[4 * c + 2], dv_pack[4 * c + 3]);
+      dkrow[c] = make_uint4(dk_pack[4 * c], dk_pack[4 * c + 1], dk_pack[4 * c + 2], dk_pack[4 * c + 3]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreadsFwd, 1)
+    attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_g,
+                       const wm_attn_args a, const float* delta, float* dq_acc, const int epoch) {
+  extern __shared__ unsigned char smem_raw[];
+  BwdShared& sm = *reinterpret_cast<BwdShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int j0 = blockIdx.x * kTileN;
+  const int kv_head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const GroupCtx g = group_ctx(a, 0);
+  const bool docs = a.q_seg != nullptr;
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    sm.epoch = epoch;
+  }
+  if (tid < kSoftmaxThreads && docs) {
+    int seg = INT_MIN, end = 0;
+    if (j0 + tid < a.k_len) {
+      const long long at = static_cast<long long>(batch) * a.k_len + j0 + tid;
+      seg = a.k_seg[at];
+      end = a.k_query_end[at];
+    }
+    sm.key_seg[tid] = seg;
+    sm.key_end[tid] = end;
+    // rows beyond the tensor do not take part in the summaries
+    const bool in = j0 + tid < a.k_len;
+    const int smin = __reduce_min_sync(0xffffffffu, in ? seg : INT_MAX);
+    const int smax = __reduce_max_sync(0xffffffffu, in ? seg : INT_MIN);
+    const int emin = __reduce_min_sync(0xffffffffu, in ? end : INT_MAX);
+    const int emax = __reduce_max_sync(0xffffffffu, end);
+    if (lane == 0) {
+      sm.summary[warp][0] = smin;
+      sm.summary[warp][1] = smax;
+      sm.summary[warp][2] = emin;
+      sm.summary[warp][3] = emax;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    // every mask family has a visibility bound that does not decrease with the query index
+    const int kvis = row_bound(a, g, batch, a.q_len - 1).hi;
+    int first = a.q_len;
+    if (j0 < kvis) {
+      int lo = 0, hi = a.q_len - 1;  // smallest i with bound(i) > j0
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (row_bound(a, g, batch, mid).hi > j0) hi = mid; else lo = mid + 1;
+      }
+      first = lo;
+    }
+    int end = a.q_len;
+    if (docs) {
+      const int emax = max(max(sm.summary[0][3], sm.summary[1][3]), max(sm.summary[2][3], sm.summary[3][3]));
+      end = min(end, emax);
+    }
+    sm.row_first = first;
+    sm.row_end = end;
+    sm.tmem_base = 0;
+    sm.summary[0][3] = kvis;  // reuse: publish the visible bound
+  }
+  __syncthreads();
+  BwdWalk w;
+  w.kvis = sm.summary[0][3];
+  w.heads = a.q_heads / a.kv_heads;
+  w.qt_first = sm.row_first / kTileM;
+  w.qt_count = sm.row_first < sm.row_end ? (sm.row_end - 1) / kTileM - w.qt_first + 1 : 0;
+  w.n_iter = w.qt_count * w.heads;
+  if (w.n_iter == 0) {
+    // no query sees this key tile: exactly zero gradients, no pipeline
+    if (tid < kSoftmaxThreads && j0 + tid < a.k_len) {
+      uint4* dvrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dv) + batch * a.dv_strides[0] +
+                                              kv_head * a.dv_strides[1] + static_cast<long long>(j0 + tid) * a.dv_strides[2]);
+      uint4* dkrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dk) + batch * a.dk_strides[0] +
+                                              kv_head * a.dk_strides[1] + static_cast<long long>(j0 + tid) * a.dk_strides[2]);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        dvrow[c] = make_uint4(0, 0, 0, 0);
+        dkrow[c] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+  if (tid == 0) {
+    ptx::mbar_init(&sm.kv_full, 1);
+    ptx::mbar_init(&sm.kv_ready, kSoftmaxThreads);
+    for (int s = 0; s < kBwdStages; ++s) {
+      ptx::mbar_init(&sm.qg_full[s], 1);
+      ptx::mbar_init(&sm.qg_empty[s], 1);
+    }
+    ptx::mbar_init(&sm.sdp_full, 1);
+    ptx::mbar_init(&sm.pds_full, kSoftmaxThreads);
+    ptx::mbar_init(&sm.mma_done, 1);
+    ptx::mbar_init(&sm.dq_full, 1);
+    ptx::mbar_init(&sm.dq_free, kSoftmaxThreads);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 4) {
+    ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  if (warp < 4) {
+    bwd_compute(sm, a, tmem, w, delta, dq_acc, j0, kv_head, batch);
+  } else if (warp == 4) {
+    if (lane == 0) bwd_producer(sm, &map_q, &map_k, &map_v, &map_g, w, j0, kv_head, batch);
+  } else {
+    if (lane == 0) bwd_mma(sm, tmem, w);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 4) ptx::tmem_dealloc(tmem, kTmemCols);
+}
