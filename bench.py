@@ -93,7 +93,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
         except OSError:
@@ -296,9 +296,10 @@ def bench_mixing(device, peaks, iters=10):
     }
 
 
-def cpu_sample(rows=2, residue=3, repeats=1):
-    """The CPU oracle on a bounded sample of the training workload: `rows` batch rows of one residue, fwd+bwd, fp32.
+def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1):
+    """The CPU oracle on a bounded sample of the training workload: `rows` batch rows, the given residues, fwd+bwd, fp32.
 
+    The default sample is one whole step (all 16 rows, all 8 residues).
     Returns (TFLOP/s over the sample's visible pairs, seconds per repeat, threads, description).
     """
     from oracle import attention_oracle as oracle
@@ -306,24 +307,26 @@ def cpu_sample(rows=2, residue=3, repeats=1):
 
     docs = geometric_documents(B, T, DOC_MEAN, seed=7)[:rows]
     groups = [torch.arange(r, T, STRIDE) for r in range(STRIDE)]
-    meta = prepare_feedback_metadata(docs, groups, T, use_dummy_token=False)[residue]
+    metas = prepare_feedback_metadata(docs, groups, T, use_dummy_token=False)
     gen = torch.Generator().manual_seed(0)
     q = torch.randn(rows, H, T // STRIDE, D, generator=gen).requires_grad_()
     k = torch.randn(rows, H, T, D, generator=gen).requires_grad_()
     v = torch.randn(rows, H, T, D, generator=gen).requires_grad_()
     g = torch.randn(rows, H, T // STRIDE, D, generator=gen)
-    flops = 14 * D * visible_pairs_per_head(docs, residue, STRIDE) * H
+    flops = 14 * D * sum(visible_pairs_per_head(docs, r, STRIDE) for r in residues) * H
     best = None
-    for _ in range(repeats + 1):  # first pass warms the allocator
+    for _ in range(repeats):
         t0 = time.perf_counter()
-        out = oracle.cyclic_attention_oracle(
-            q, k, v, query_stride=STRIDE, query_offset=residue, strict_past=True, metadata=meta,
-            compute_dtype=torch.float32,
-        )
-        torch.autograd.grad(out, (q, k, v), g)
+        for r in residues:
+            out = oracle.cyclic_attention_oracle(
+                q, k, v, query_stride=STRIDE, query_offset=r, strict_past=True, metadata=metas[r],
+                compute_dtype=torch.float32,
+            )
+            torch.autograd.grad(out, (q, k, v), g)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    what = f"{rows} of {B} batch rows, residue {residue} of {STRIDE}, fwd+bwd fp32, oracle port on torch CPU"
+    what = (f"{rows} of {B} batch rows, {len(residues)} of {STRIDE} residues, fwd+bwd fp32, "
+            "oracle port on torch CPU, all host threads")
     return flops / best / 1e12, best, torch.get_num_threads(), what
 
 
@@ -334,11 +337,12 @@ def run_reference_arm(args, rank, world):
     """The upstream algorithm on the host cores (the CPU oracle port), bounded sample per step."""
     if rank != 0:
         return
-    rows = 2
-    for _ in range(args.warmup):
-        cpu_sample(rows=rows, repeats=0)
+    # one step of the reference arm = a quarter of the workload's step (4 of 16 batch rows, all residues)
+    rows = 4
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(rows=rows)
     t0 = time.perf_counter()
-    values = [cpu_sample(rows=rows, repeats=0) for _ in range(args.steps)]
+    values = [cpu_sample(rows=rows) for _ in range(args.steps)]
     wall = time.perf_counter() - t0
     tflops = statistics.median(v[0] for v in values)
     line = {
@@ -366,7 +370,7 @@ def workload_config(n_gpus):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--backend", default="sm100", help="kernel family: sm100 | sm100_simt | sm100_tcgen05")
@@ -423,13 +427,11 @@ def main():
     if per_step_launches is not None:
         launches = per_step_launches * args.steps  # kernels inside the replayed graphs
     clocks = sampler.stop()
+    from white_matter_b200.replicas import aggregate_throughput
+
     flops = sum(sets[i % 2].flops for i in range(args.steps))
-    t = torch.tensor([ms], device=device, dtype=torch.float64)
-    f = torch.tensor([float(flops)], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(f, op=dist.ReduceOp.SUM)
-    value = f.item() / (t.item() * 1e-3) / 1e12
+    step_ms, total_flops = aggregate_throughput(ms, float(flops), device)
+    value = total_flops / (step_ms * 1e-3) / 1e12
 
     # per-operator device time inside a timed pass: forward (one kernel) and backward (its kernel group)
     work = sets[0]
@@ -452,10 +454,8 @@ def main():
     e2e_step = lambda: sets[0].step_e2e(staging)
     e2e_ms = time_steps(e2e_step, max(2, args.steps // 2), 2, sync)
     e2e_steps = max(2, args.steps // 2)
-    te = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_value = sets[0].flops * e2e_steps * world / (te.item() * 1e-3) / 1e12
+    e2e_max_ms, e2e_flops = aggregate_throughput(e2e_ms, float(sets[0].flops * e2e_steps), device)
+    e2e_value = e2e_flops / (e2e_max_ms * 1e-3) / 1e12
 
     extras = {}
     if not args.skip_extras:
@@ -466,7 +466,7 @@ def main():
     if rank == 0:
         line = {
             "metric": "cyclic_attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t.item() / args.steps,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
             "backend": args.backend, "launch_mode": "eager" if args.no_graph else "cuda graph replay of one step",
@@ -481,7 +481,7 @@ def main():
         }
         line.update(extras)
         if world == 1 and not args.skip_extras:
-            tf, secs, cores, what = cpu_sample(rows=2, repeats=1)
+            tf, secs, cores, what = cpu_sample(repeats=2)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": what, "seconds": secs}
         print(json.dumps(line), flush=True)

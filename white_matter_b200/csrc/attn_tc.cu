@@ -23,6 +23,7 @@
 #include <atomic>
 #include <limits.h>
 #include <math.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -137,6 +138,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -211,7 +218,16 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
                                    cudaSharedmemCarveoutMaxShared));
       configured = true;
     }
-    attn_fwd_tc2_kernel<<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
+    static const int dbg = [&] {
+      const char* v = getenv("WM_B200_DBG");
+      if (v != nullptr) {
+        int blocks = -1;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attn_fwd_tc2_kernel, kThreadsFwd, smem);
+        fprintf(stderr, "[wm_b200] forward pipeline: %d block(s) per SM, %zu bytes of shared memory\n", blocks, smem);
+      }
+      return v ? atoi(v) : 0;
+    }();
+    attn_fwd_tc2_kernel<<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, a, next_epoch(), dbg);
   }
   count_launch();
   return cuda_check(cudaGetLastError(), "attn_fwd_tc_kernel");

@@ -243,7 +243,7 @@ __device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a
         for (int u = 0; u < 2; ++u) {
           const int col = c * 32 + 2 * e + u;
           bool vis = !none && (full || col < lim);
-          if (vis && docs && !full) vis = doc_visible(rb, j0 + col, sm.key_seg[col], sm.key_end[col]);
+          if (docs && !full) vis = vis & doc_visible_flat(rb, j0 + col, sm.key_seg[col], sm.key_end[col]);
           const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e + u]), sl2, -lse2));
           pv[u] = vis ? p : 0.f;
           dv[u] = vis ? p * (__uint_as_float(ys[2 * e + u]) - dl) : 0.f;

@@ -293,7 +293,7 @@ __device__ __forceinline__ void bwd2_compute(Bwd2Shared& sm, const wm_attn_args&
           for (int u = 0; u < 2; ++u) {
             const int col = col0 + 2 * e + u;
             bool vis_e = cls == kTileFull || (cls != kTileNone && col < lim);
-            if (cls == kTileDocs && vis_e) vis_e = doc_visible(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col]);
+            if (cls == kTileDocs) vis_e = vis_e & doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col]);
             const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e + u]), sl2, -lse2[qt]));
             pv[u] = vis_e ? p : 0.f;
             dv[u] = vis_e ? p * (__uint_as_float(ys[2 * e + u]) - dl[qt]) : 0.f;

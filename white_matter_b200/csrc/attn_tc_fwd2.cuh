@@ -105,16 +105,22 @@ __device__ __forceinline__ void mask_chunk(const uint32_t (&raw)[32], float (&x)
     for (int e = 0; e < 32; ++e) x[e] = c * 32 + e < lim ? __uint_as_float(raw[e]) : -INFINITY;
   } else {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
+    for (int e = 0; e < 32; e += 4) {
       const int col = c * 32 + e;
-      const bool vis = col < lim && doc_visible(rb, j0 + col, key_seg[col], key_end[col]);
-      x[e] = vis ? __uint_as_float(raw[e]) : -INFINITY;
+      const int4 sg = *reinterpret_cast<const int4*>(key_seg + col);
+      const int4 en = *reinterpret_cast<const int4*>(key_end + col);
+      const int segs[4] = {sg.x, sg.y, sg.z, sg.w}, ends[4] = {en.x, en.y, en.z, en.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const bool vis = (col + u < lim) & doc_visible_flat(rb, j0 + col + u, segs[u], ends[u]);
+        x[e + u] = vis ? __uint_as_float(raw[e + u]) : -INFINITY;
+      }
     }
   }
 }
 
 __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, uint32_t tmem, const TileWalk& w,
-                                         const RowBound& rb, bool live, int batch, int head) {
+                                         const RowBound& rb, bool live, int batch, int head, int dbg) {
   const int t = threadIdx.x;
   const int warp = t >> 5, lane = t & 31;
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
@@ -133,8 +139,13 @@ __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, 
       const int j = tile_first_key(n, w.first_tile, w.dummy_tile) + t;
       if (j < a.k_len) {
         const long long at = static_cast<long long>(batch) * a.k_len + j;
-        next_seg = __ldg(a.k_seg + at);
-        next_end = __ldg(a.k_query_end + at);
+        if (dbg & 1) {
+          next_seg = 0;
+          next_end = INT_MAX;
+        } else {
+          next_seg = __ldg(a.k_seg + at);
+          next_end = __ldg(a.k_query_end + at);
+        }
       }
     }
   };
@@ -157,9 +168,11 @@ __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, 
         sm.tile_summary[b][warp][1] = smax;
         sm.tile_summary[b][warp][2] = emin;
       }
-      ptx::mbar_arrive(&sm.docs_full[b]);
-      if (!wait_or_abort(sm, &sm.docs_full[b], (n >> 1) & 1, 30)) return;
-      if (cls != kTileNone) {
+      if (!(dbg & 2)) {
+        ptx::mbar_arrive(&sm.docs_full[b]);
+        if (!wait_or_abort(sm, &sm.docs_full[b], (n >> 1) & 1, 30)) return;
+      }
+      if (cls != kTileNone && !(dbg & 4)) {
         int tmin = sm.tile_summary[b][0][0], tmax = sm.tile_summary[b][0][1], tend = sm.tile_summary[b][0][2];
 #pragma unroll
         for (int q = 1; q < 4; ++q) {
@@ -180,21 +193,22 @@ __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, 
     ptx::tc_fence_after();
     // pass 1: row maximum
     float top = -INFINITY;
-    if (__any_sync(0xffffffffu, cls != kTileNone)) {
+    if (__any_sync(0xffffffffu, cls != kTileNone) && !(dbg & 8)) {
       float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kTileN / 32; ++c) {
-        uint32_t raw[32];
-        float x[32];
-        ptx::tmem_ld32(s_tmem + c * 32, raw);
-        ptx::tmem_wait_ld();
-        mask_chunk(raw, x, cls, c, lim, rb, j0, sm.key_seg[b], sm.key_end[b]);
+      uint32_t raw[2][32];
+      ptx::tmem_ld32(s_tmem, raw[0]);
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          t0 = fmaxf(t0, x[e]);
-          t1 = fmaxf(t1, x[e + 1]);
-          t2 = fmaxf(t2, x[e + 2]);
-          t3 = fmaxf(t3, x[e + 3]);
+      for (int c = 0; c < kTileN / 32; ++c) {
+        ptx::tmem_wait_ld();
+        if (c + 1 < kTileN / 32) ptx::tmem_ld32(s_tmem + (c + 1) * 32, raw[(c + 1) & 1]);  // in flight during the math
+        float x[32];
+        mask_chunk(raw[c & 1], x, cls, c, lim, rb, j0, sm.key_seg[b], sm.key_end[b]);
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          t0 = fmax3(t0, x[e], x[e + 1]);
+          t1 = fmax3(t1, x[e + 2], x[e + 3]);
+          t2 = fmax3(t2, x[e + 4], x[e + 5]);
+          t3 = fmax3(t3, x[e + 6], x[e + 7]);
         }
       }
       top = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * sl2;
@@ -212,28 +226,31 @@ __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, 
     if (n >= 1 && !wait_or_abort(sm, &sm.pv_done, (n - 1) & 1, 32)) return;
     ptx::tc_fence_after();
     // pass 2: exponentials -> P
-    {
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll 1
+    if (!(dbg & 16)) {
+      float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
+      const float2 sc = make_float2(sl2, sl2), nm = make_float2(-m_use, -m_use);
+      uint32_t raw[2][32];
+      ptx::tmem_ld32(s_tmem, raw[0]);
+#pragma unroll
       for (int c = 0; c < kTileN / 32; ++c) {
-        uint32_t raw[32];
-        float x[32];
-        ptx::tmem_ld32(s_tmem + c * 32, raw);
         ptx::tmem_wait_ld();
-        mask_chunk(raw, x, cls, c, lim, rb, j0, sm.key_seg[b], sm.key_end[b]);
+        if (c + 1 < kTileN / 32) ptx::tmem_ld32(s_tmem + (c + 1) * 32, raw[(c + 1) & 1]);
+        float x[32];
+        mask_chunk(raw[c & 1], x, cls, c, lim, rb, j0, sm.key_seg[b], sm.key_end[b]);
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
-          const float p0 = fast_exp2(fmaf(x[e], sl2, -m_use));
-          const float p1 = fast_exp2(fmaf(x[e + 1], sl2, -m_use));
-          const float p2 = fast_exp2(fmaf(x[e + 2], sl2, -m_use));
-          const float p3 = fast_exp2(fmaf(x[e + 3], sl2, -m_use));
-          s0 += p0;
-          s1 += p1;
-          s2 += p2;
-          s3 += p3;
-          pk[e / 2] = pack_bf16(p0, p1);
-          pk[e / 2 + 1] = pack_bf16(p2, p3);
+          // two scores per packed fp32x2 instruction
+          float2 a = __ffma2_rn(make_float2(x[e], x[e + 1]), sc, nm);
+          float2 d = __ffma2_rn(make_float2(x[e + 2], x[e + 3]), sc, nm);
+          a.x = fast_exp2(a.x);
+          a.y = fast_exp2(a.y);
+          d.x = fast_exp2(d.x);
+          d.y = fast_exp2(d.y);
+          s0 = __fadd2_rn(s0, a);
+          s1 = __fadd2_rn(s1, d);
+          pk[e / 2] = pack_bf16(a.x, a.y);
+          pk[e / 2 + 1] = pack_bf16(d.x, d.y);
         }
         const int sub = (c >> 1) * kTileBytes;
 #pragma unroll
@@ -241,7 +258,11 @@ __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, 
           *reinterpret_cast<uint4*>(prow + sub + ((((c & 1) * 4 + u) ^ (t & 7)) << 4)) =
               make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
       }
-      l += (s0 + s1) + (s2 + s3);
+      const float s2 = s0.x + s0.y, s3 = s1.x + s1.y;
+      const float s0s = 0.f, s1s = 0.f;
+      (void)s0s;
+      (void)s1s;
+      l += s2 + s3;
     }
     if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
@@ -298,7 +319,8 @@ __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, 
 
 __global__ void __launch_bounds__(kThreadsFwd, 2)
     attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, const wm_attn_args a, const int epoch) {
+                        const __grid_constant__ CUtensorMap map_v, const wm_attn_args a, const int epoch,
+                        const int dbg) {
   extern __shared__ unsigned char smem_raw[];
   Fwd2Shared& sm = *reinterpret_cast<Fwd2Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x;
@@ -378,7 +400,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 2)
   const uint32_t tmem = sm.tmem_base;
 
   if (warp < 4) {
-    softmax2(sm, a, tmem, w, rb, live, batch, head);
+    softmax2(sm, a, tmem, w, rb, live, batch, head, dbg);
   } else if (warp == 4) {
     if (lane == 0) producer2(sm, &map_q, &map_k, &map_v, w, q0, head, kv_head, batch);
   } else {

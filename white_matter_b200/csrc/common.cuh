@@ -170,4 +170,10 @@ __device__ __forceinline__ bool doc_visible(const RowBound& r, int j, int kseg, 
   return kseg == r.seg && j >= r.lo;
 }
 
+
+// The same rule without control flow, for unrolled per-element loops.
+__device__ __forceinline__ bool doc_visible_flat(const RowBound& r, int j, int kseg, int kend) {
+  return (r.qi < kend) & ((kseg == -1) | ((kseg == r.seg) & (j >= r.lo)));
+}
+
 }  // namespace wm
