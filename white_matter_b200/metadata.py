@@ -147,6 +147,7 @@ class StrictCausalMetadata:
         "max_keys",
         "key_extent",
         "segments",
+        "dense_documents",
         "_cache",
     )
 
@@ -173,6 +174,10 @@ class StrictCausalMetadata:
             k = cu_keys.tolist()
             segments = tuple(zip(q[:-1], q[1:], k[:-1], k[1:], strict=True))
         self.segments = segments
+        # (document ids (B,T) int32, use_dummy_token) when the schedule is plain Jacobi packing: every token is a
+        # query, no padding, no truncation.  Such a schedule equals stride-1 cyclic attention with document
+        # metadata, which the tensor-core kernels take directly.
+        self.dense_documents = None
         self._cache: dict = {}
 
     def with_key_extent(self, key_extent: int) -> "StrictCausalMetadata":
@@ -193,7 +198,22 @@ class StrictCausalMetadata:
                 key_extent,
                 self.segments,
             )
+            cached.dense_documents = self.dense_documents
             self._cache[("extent", key_extent)] = cached
+        return cached
+
+    def cyclic_equivalent(self, device: torch.device, key_length: int) -> "CyclicAttentionMetadata | None":
+        """Stride-1 cyclic metadata of a plain Jacobi schedule (None when the schedule is not of that form)."""
+        if self.dense_documents is None:
+            return None
+        key = ("cyclic", str(device), key_length)
+        cached = self._cache.get(key)
+        if cached is None:
+            docs, dummy = self.dense_documents
+            docs = docs.to(device)
+            slots = torch.arange(docs.shape[1], device=device)
+            cached = prepare_feedback_metadata(docs, [slots], key_length, use_dummy_token=dummy)[0]
+            self._cache[key] = cached
         return cached
 
     def device_tables(self, device: torch.device, q_rows: int, k_rows: int):
@@ -331,7 +351,7 @@ def prepare_strict_causal_metadata(
             at += 1
         chosen = row_slots[b][int(g_first[n]) : int(g_first[n]) + int(real[n])]
         key_indices[at : at + chosen.shape[0]] = b * width + chosen + lead
-    return StrictCausalMetadata(
+    schedule = StrictCausalMetadata(
         torch.from_numpy(query_indices).to(device),
         torch.from_numpy(key_indices).to(device),
         torch.from_numpy(cu_queries.astype(np.int32)).to(device),
@@ -340,3 +360,14 @@ def prepare_strict_causal_metadata(
         width,
         width,
     )
+    plain = (
+        limits is None
+        and not isinstance(query_start, torch.Tensor)
+        and int(query_start) == 0
+        and query_length == extent
+        and extent > 0
+        and bool((docs >= 0).all())
+    )
+    if plain:
+        schedule.dense_documents = (document_ids.detach().to(torch.int32), bool(use_dummy_token))
+    return schedule

@@ -90,6 +90,21 @@ def strict_causal_attention(
         if metadata.query_indices.numel() == 0:
             zero = (query[..., :0, :].sum() + key[..., :0, :].sum() + value[..., :0, :].sum()).to(query.dtype)
             return query.new_zeros(batch, length, heads, dim) + zero
+        # A plain Jacobi schedule (every token a query, no padding or truncation) is stride-1 cyclic attention
+        # with document metadata; that form runs on the tensor-core kernels without gathering.
+        lead_slots = int(use_dummy_token)
+        if (
+            metadata.dense_documents is not None
+            and metadata.dense_documents[1] == use_dummy_token
+            and metadata.dense_documents[0].shape == (batch, length)
+            and key.shape[-2] >= length
+            and _BACKENDS[backend] != "simt"
+        ):
+            cyc = metadata.cyclic_equivalent(query.device, length)
+            out = operators.cyclic_attn_doc_fwd(
+                query, key[..., :length, :], value[..., :length, :], *cyc, 1, lead_slots - 1, kernel
+            )[0]
+            return out.transpose(1, 2)
         fwd_q, bwd_q, bwd_k = operators.packed_tile_rows(query, key, kernel)
         if fwd_q != bwd_q:
             raise RuntimeError("forward and backward kernels disagree on the query tile height")
