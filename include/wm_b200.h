@@ -187,6 +187,23 @@ WM_API int wm_strict_packed_bwd(const wm_attn_args* args, void* stream);
 /* single-query read of a KV pool, split over the key axis; lengths stay on the device */
 WM_API int wm_strict_decode(const wm_attn_args* args, void* stream);
 
+/*
+ * wm_strict_decode for callers that have no device allocator to lend: same arguments and result, but
+ * `workspace` is ignored and the split partials go to a 16 MiB array built into the library (held on every
+ * GPU that loads it, until the process exits).  No counterpart in the upstream project.
+ * Meant for hosts that were handed their device buffers and can pass pointers but not allocate -- a serving
+ * process that carved all of HBM into its KV pool at start-up, or a thin foreign-language binding.
+ * - Problems whose partials exceed the array (wm_strict_decode_workspace_bytes > 16 MiB) are rejected with
+ *   WM_EWORKSPACE; nothing is launched.
+ * - The first call on each device looks up the array's device address (that device must be current); make
+ *   that first call outside any stream capture.
+ * - All calls share the one array and it keeps the previous call's contents.  Nothing in it has to start at
+ *   zero (every partial that is read was written by the same call), but two calls that overlap on the GPU
+ *   (different streams) race on it: keep such calls on one stream or order them yourself.
+ * - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ */
+WM_API int wm_strict_decode_no_alloc(const wm_attn_args* args, void* stream);
+
 /* KV source mixing */
 WM_API int wm_mix_sources_fwd(const wm_mix_args* args, void* stream);
 WM_API int wm_mix_sources_bwd(const wm_mix_args* args, void* stream);

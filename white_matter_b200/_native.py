@@ -107,6 +107,7 @@ ATTN_ENTRY_POINTS = (
     "wm_strict_packed_fwd",
     "wm_strict_packed_bwd",
     "wm_strict_decode",
+    "wm_strict_decode_no_alloc",
 )
 MIX_ENTRY_POINTS = ("wm_mix_sources_fwd", "wm_mix_sources_bwd")
 QUERY_ENTRY_POINTS = (

@@ -177,6 +177,26 @@ int wm_strict_decode(const wm_attn_args* a, void* stream) {
   return wm::decode_launch(*a, static_cast<cudaStream_t>(stream));
 }
 
+int wm_strict_decode_no_alloc(const wm_attn_args* a, void* stream) {
+  int status = wm::validate_attn(a, false, "wm_strict_decode_no_alloc");
+  if (status != WM_OK) return status;
+  if (a->mask != WM_MASK_STRICT || a->q_len != 1)
+    return wm::fail(WM_EINVAL, "wm_strict_decode_no_alloc: needs the strict mask family and a single query token");
+  if (!wm::decode_supported(*a))
+    return wm::fail(WM_EUNSUPPORTED,
+                    "wm_strict_decode_no_alloc: head_dim must be a multiple of 16 bytes and all rows 16-byte aligned");
+  const size_t need = wm::decode_workspace(*a);
+  if (need > wm::decode_static_capacity())
+    return wm::fail(WM_EWORKSPACE,
+                    "wm_strict_decode_no_alloc: this problem needs %zu bytes of split scratch, the built-in array holds "
+                    "%zu; use wm_strict_decode with caller scratch",
+                    need, wm::decode_static_capacity());
+  float* scratch = nullptr;
+  status = wm::decode_static_scratch(&scratch);
+  if (status != WM_OK) return status;
+  return wm::decode_launch_with_scratch(*a, scratch, static_cast<cudaStream_t>(stream));
+}
+
 int wm_mix_sources_fwd(const wm_mix_args* a, void* stream) {
   if (a == nullptr) return wm::fail(WM_EINVAL, "wm_mix_sources_fwd: null arguments");
   return wm::mix_fwd_launch(*a, static_cast<cudaStream_t>(stream));

@@ -32,6 +32,8 @@ int decode_launch(const wm_attn_args& a, cudaStream_t stream);
 size_t decode_workspace(const wm_attn_args& a);
 int decode_launch_with_scratch(const wm_attn_args& a, float* scratch, cudaStream_t stream);
 bool decode_supported(const wm_attn_args& a);
+size_t decode_static_capacity();
+int decode_static_scratch(float** out);
 int mix_fwd_launch(const wm_mix_args& a, cudaStream_t stream);
 int mix_bwd_launch(const wm_mix_args& a, cudaStream_t stream);
 size_t mix_workspace(const wm_mix_args& a);

@@ -12,6 +12,8 @@
 // Algorithmic bytes per step: sum_b 2 * kv_heads * visible_b * head_dim * sizeof(T).
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace wm {
@@ -331,6 +333,37 @@ size_t decode_workspace(const wm_attn_args& a) {
 
 int decode_launch_with_scratch(const wm_attn_args& a, float* scratch, cudaStream_t stream) {
   return a.dtype == WM_F32 ? dispatch<float>(a, scratch, stream) : dispatch<__nv_bfloat16>(a, scratch, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Variant for callers that cannot supply scratch memory: the split partials
+// live in a fixed array that is part of the library image.  Every GPU that
+// loads the library holds these 16 MiB until the process exits.
+constexpr size_t kStaticScratchFloats = size_t(4) << 20;
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_address[kMaxDevices] = {};
+std::mutex g_scratch_mutex;
+}  // namespace
+
+size_t decode_static_capacity() { return kStaticScratchFloats * sizeof(float); }
+
+// Device address of the fixed scratch array on the current device.  The array's name is only a host-side
+// handle; the address a kernel can use comes from cudaGetSymbolAddress, looked up once per device.
+int decode_static_scratch(float** out) {
+  int device = -1;
+  WM_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) return fail(WM_EUNSUPPORTED, "device ordinal %d is out of range", device);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    WM_CUDA(cudaGetSymbolAddress(&address, g_decode_scratch));
+    g_scratch_address[device] = static_cast<float*>(address);
+  }
+  *out = g_scratch_address[device];
+  return WM_OK;
 }
 
 int decode_launch(const wm_attn_args& a, cudaStream_t stream) {

@@ -579,3 +579,32 @@ def _mix_backward(ctx, dout):
 
 
 mix_sources.register_autograd(_mix_backward, setup_context=_mix_setup)
+
+
+def strict_decode_no_alloc(
+    Q: Tensor,
+    K: Tensor,
+    V: Tensor,
+    out: Tensor,
+    query_start: Optional[Tensor],
+    query_start_value: int,
+    kv_lengths: Optional[Tensor],
+    key_mask: Optional[Tensor],
+    use_dummy: bool,
+    scale: float,
+) -> Tensor:
+    """Pool read into a caller-owned ``out`` (B,1,H,D) without any allocation on the way.
+
+    For hosts that hold pre-assigned device buffers and no allocator (a serving
+    process that split the whole device into its KV pool, a thin binding from
+    another language): inputs and ``out`` are passed in, the split partials go
+    to the 16 MiB array inside the library (``wm_strict_decode_no_alloc``).
+    Larger problems raise.  Calls share that array, so keep them on one stream.
+    """
+    a, keep = _strict_args(Q, K, V, query_start, query_start_value, kv_lengths, key_mask, use_dummy, scale, 0)
+    if out.shape != (Q.shape[0], 1, Q.shape[1], Q.shape[3]) or out.dtype != Q.dtype or out.stride(-1) != 1:
+        raise ValueError("out must be (B,1,H,D) in the query dtype with unit stride in D")
+    _set_out(a, out.transpose(1, 2), None)
+    _native.call("wm_strict_decode_no_alloc", a, Q.device)
+    del keep
+    return out
