@@ -279,17 +279,17 @@ def bench_decode(device, peaks, iters=20):
 
 
 def bench_mixing(device, peaks, iters=10):
-    """25-source mixture of a per-GPU shard: sources (25, 2, 16, 2048, 64) bf16 = 210 MB, read once."""
+    """25-source mixture of a per-GPU shard: sources (25, 4, 16, 2048, 64) bf16 = 419 MB, read once."""
     from white_matter_b200 import mix_kv_sources
 
-    src = torch.randn(25, 2, 16, 2048, 64, device=device, dtype=torch.bfloat16)
+    src = torch.randn(25, 4, 16, 2048, 64, device=device, dtype=torch.bfloat16)
     logits = torch.randn(25, device=device)
     call = lambda: mix_kv_sources(src, logits)
     ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
     nbytes = src.numel() * 2 + src[0].numel() * 2
     gbs = nbytes / (ms * 1e-3) / 1e9
     return {
-        "workload": "mix 25 sources (25,2,16,2048,64) bf16, 210 MB read + 8 MB written",
+        "workload": "mix 25 sources (25,4,16,2048,64) bf16, 419 MB read + 17 MB written",
         "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs / peaks["hbm_gbs"], "traffic": None},

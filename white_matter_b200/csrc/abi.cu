@@ -115,6 +115,10 @@ int wm_abi_version(void) { return WM_B200_ABI_VERSION; }
 
 const char* wm_last_error(void) { return wm::g_error; }
 
+__attribute__((visibility("default"))) int wm_debug_trace(long long* out, int capacity, int arm_after) {
+  return wm::tc_debug_trace(out, capacity, arm_after);
+}
+
 int wm_device_status(int reset) { return wm::tc_device_status(reset != 0); }
 
 unsigned long long wm_kernel_launch_count(void) { return wm::g_launches.load(std::memory_order_relaxed); }

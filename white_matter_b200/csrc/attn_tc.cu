@@ -45,6 +45,40 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units
 __device__ int g_status = 0;       // first failure code since the last reset
 __device__ int g_abort_epoch = 0;  // launch number whose blocks should stop waiting
 
+// Bring-up trace: (tag, clock) pairs recorded by block (0,0,0) of launches whose epoch equals g_trace_epoch.
+__device__ long long g_trace[2 * 4096];
+__device__ int g_trace_count = 0;
+__device__ int g_trace_epoch = -1;
+
+constexpr int kTraceSlots = 1024;
+
+// Events go to shared memory (cheap) and are copied out when the block ends.
+template <class Shared>
+__device__ __forceinline__ void trace_event(Shared& sm, int tag) {
+  if (sm.trace_on) {
+    const int i = atomicAdd(&sm.trace_n, 1);
+    if (i < kTraceSlots) sm.trace[i] = (clock64() << 16) | static_cast<long long>(tag & 0xffff);
+  }
+}
+
+template <class Shared>
+__device__ __forceinline__ void trace_begin(Shared& sm, int epoch) {
+  sm.trace_n = 0;
+  sm.trace_on = epoch == g_trace_epoch && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+}
+
+template <class Shared>
+__device__ __forceinline__ void trace_flush(Shared& sm) {
+  if (sm.trace_on) {
+    const int n = min(sm.trace_n, kTraceSlots);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      g_trace[2 * i] = sm.trace[i] & 0xffff;
+      g_trace[2 * i + 1] = sm.trace[i] >> 16;
+    }
+    if (threadIdx.x == 0) g_trace_count = n;
+  }
+}
+
 
 template <class Shared>
 __device__ __forceinline__ void record_failure(Shared& sm, int code) {
@@ -159,8 +193,11 @@ struct TileWalk {
 
 #include "attn_tc_fwd.cuh"
 #include "attn_tc_fwd2.cuh"
+#include "attn_tc_fwd3.cuh"
+#include "attn_tc_fwd4.cuh"
 #include "attn_tc_bwd.cuh"
 #include "attn_tc_bwd2.cuh"
+#include "attn_tc_bwd3.cuh"
 
 }  // namespace
 
@@ -195,12 +232,29 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
   status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN);
   if (status != WM_OK) return status;
   dim3 grid((a.q_len + kTileM - 1) / kTileM, a.q_heads, a.batch);
-  // WM_B200_FWD_PIPELINE=1 selects the one-block-per-SM pipeline (bring-up aid); default: two blocks per SM
-  static const bool one_per_sm = [] {
+  // WM_B200_FWD_PIPELINE selects a forward pipeline (bring-up aid): 1 = one block per SM with 4 softmax warps,
+  // 2 = two blocks per SM, 3 (default) = one block per SM with the softmax split over two warpgroups
+  static const int pipeline = [] {
     const char* v = getenv("WM_B200_FWD_PIPELINE");
-    return v != nullptr && v[0] == '1';
+    return v != nullptr ? atoi(v) : 3;
   }();
-  if (one_per_sm) {
+  if (pipeline == 4) {
+    const size_t smem = sizeof(Fwd4Shared) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      configured = true;
+    }
+    attn_fwd_tc4_kernel<<<grid, kFwd4Threads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
+  } else if (pipeline == 3) {
+    const size_t smem = sizeof(Fwd3Shared) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      configured = true;
+    }
+    attn_fwd_tc3_kernel<<<grid, kFwd3Threads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
+  } else if (pipeline == 1) {
     const size_t smem = sizeof(FwdShared) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -231,6 +285,21 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
   }
   count_launch();
   return cuda_check(cudaGetLastError(), "attn_fwd_tc_kernel");
+}
+
+// Arms the trace for the launch after the next `skip` launches and fetches what was recorded so far.
+int tc_debug_trace(long long* out, int capacity, int arm_after) {
+  int count = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&count, g_trace_count, sizeof(int));
+  if (count > 4096) count = 4096;
+  if (count > capacity) count = capacity;
+  if (out != nullptr && count > 0) cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 2 * count);
+  int zero = 0;
+  cudaMemcpyToSymbol(g_trace_count, &zero, sizeof(int));
+  int target = arm_after < 0 ? -1 : next_epoch() + 1 + arm_after;
+  cudaMemcpyToSymbol(g_trace_epoch, &target, sizeof(int));
+  return count;
 }
 
 int tc_device_status(bool reset) {
@@ -264,7 +333,7 @@ bool bwd_short_queries(const wm_attn_args& a) {
     const char* v = getenv("WM_B200_BWD_PIPELINE");  // "1": always the key-stationary pipeline (bring-up aid)
     return v != nullptr && v[0] == '1';
   }();
-  return !disabled && a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads;
+  return !disabled && a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
 }
 
 size_t tc_attn_bwd_workspace(const wm_attn_args& a) {
@@ -299,8 +368,24 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
       WM_CUDA(cudaFuncSetAttribute(attn_bwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
       configured2 = true;
     }
-    attn_bwd_tc2_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem2, stream>>>(map_q, map_k, map_v, map_g, a, delta,
-                                                                                   next_epoch());
+    // WM_B200_BWD_PIPELINE=2 keeps the non-overlapped resident-query pipeline (bring-up aid)
+    static const bool overlapped = [] {
+      const char* v = getenv("WM_B200_BWD_PIPELINE");
+      return !(v != nullptr && v[0] == '2');
+    }();
+    if (overlapped) {
+      const size_t smem3 = sizeof(Bwd3Shared) + 1024;
+      static bool configured3 = false;
+      if (!configured3) {
+        WM_CUDA(cudaFuncSetAttribute(attn_bwd_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem3)));
+        configured3 = true;
+      }
+      attn_bwd_tc3_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem3, stream>>>(map_q, map_k, map_v, map_g, a, delta,
+                                                                                     next_epoch());
+    } else {
+      attn_bwd_tc2_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem2, stream>>>(map_q, map_k, map_v, map_g, a, delta,
+                                                                                     next_epoch());
+    }
     count_launch();
     return cuda_check(cudaGetLastError(), "attention backward (tcgen05, resident queries)");
   }

@@ -217,9 +217,11 @@ __device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a
     }
     bool none = !live || j0 >= rb.hi;
     bool full = live && j0 + kTileN <= rb.hi;
+    bool own_doc = !docs;  // the tile lies inside the row's own document: only the causal bound can cut it
     if (docs && !none) {
       const bool uniform = smin == smax;
-      full = full && uniform && smin == rb.seg && j0 >= rb.lo && emin > rb.qi;
+      own_doc = uniform && smin == rb.seg && j0 >= rb.lo && emin > rb.qi;
+      full = full && own_doc;
       if (uniform && smin != -1 && smin != rb.seg) none = true;
     }
     if (!wait_or_abort(sm, &sm.sdp_full, it & 1, 61)) return;
@@ -243,7 +245,7 @@ __device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a
         for (int u = 0; u < 2; ++u) {
           const int col = c * 32 + 2 * e + u;
           bool vis = !none && (full || col < lim);
-          if (docs && !full) vis = vis & doc_visible_flat(rb, j0 + col, sm.key_seg[col], sm.key_end[col]);
+          if (!own_doc) vis = vis & doc_visible_flat(rb, j0 + col, sm.key_seg[col], sm.key_end[col]);
           const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e + u]), sl2, -lse2));
           pv[u] = vis ? p : 0.f;
           dv[u] = vis ? p * (__uint_as_float(ys[2 * e + u]) - dl) : 0.f;

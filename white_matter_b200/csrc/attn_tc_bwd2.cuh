@@ -35,6 +35,8 @@ struct Bwd2Shared {
   uint32_t tmem_base;
   int abort_flag;
   int epoch;
+  int trace_on, trace_n;
+  long long trace[kTraceSlots];
 };
 
 struct Bwd2Walk {
@@ -54,7 +56,8 @@ __device__ __forceinline__ bool pair_visible(const Bwd2Walk& w, int kt, int qt) 
   return true;
 }
 
-__device__ __forceinline__ void bwd2_producer(Bwd2Shared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
+template <class Shared>
+__device__ __forceinline__ void bwd2_producer(Shared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
                                               const CUtensorMap* map_v, const CUtensorMap* map_g, const Bwd2Walk& w,
                                               int head, int batch) {
   ptx::prefetch_tmap(map_q);
@@ -92,6 +95,7 @@ __device__ __forceinline__ void bwd2_mma(Bwd2Shared& sm, uint32_t tmem, const Bw
     const int s = active & 1;
     if (!wait_or_abort(sm, &sm.kv_ready[s], (active >> 1) & 1, 81)) return;
     ptx::tc_fence_after();
+    trace_event(sm, 100 + kt);
     const uint32_t k_base = ptx::smem_u32(sm.k[s]), v_base = ptx::smem_u32(sm.v[s]);
     bool dkv_started = false;
 #pragma unroll
@@ -107,8 +111,10 @@ __device__ __forceinline__ void bwd2_mma(Bwd2Shared& sm, uint32_t tmem, const Bw
         ptx::mma_bf16_ss(tmem + kTileN, ptx::make_smem_desc_sw128(g_base + kk * 32, 16, 1024),
                          ptx::make_smem_desc_sw128(v_base + kk * 32, 16, 1024), idesc_s, kk > 0);
       ptx::mma_commit(&sm.sdp_full);
+      trace_event(sm, 200 + it);
       if (!wait_or_abort(sm, &sm.pds_full, it & 1, 82)) return;
       ptx::tc_fence_after();
+      trace_event(sm, 300 + it);
 #pragma unroll
       for (int kk = 0; kk < kTileM / 16; ++kk)
         ptx::mma_bf16_ss(tmem + 2 * kTileN, ptx::make_smem_desc_sw128(p_base + kk * 2048, kTileBytes, 1024),
@@ -127,6 +133,7 @@ __device__ __forceinline__ void bwd2_mma(Bwd2Shared& sm, uint32_t tmem, const Bw
       dkv_started = true;
       dq_started[qt] = true;
       ptx::mma_commit(&sm.mma_done);
+      trace_event(sm, 400 + it);
       ++it;
     }
     ptx::mma_commit(&sm.kv_empty[s]);
@@ -140,16 +147,19 @@ __device__ __forceinline__ void bwd2_store_dkv(const wm_attn_args& a, uint32_t t
   const int j = kt * kTileN + row;
   uint32_t packed[kHeadDim / 2];
   const float s = half ? a.scale : 1.f;
+  uint32_t raw[kHeadDim / 32][32];
+  if (!zero) {
+#pragma unroll
+    for (int c = 0; c < kHeadDim / 32; ++c)
+      ptx::tmem_ld32(tmem + 2 * kTileN + half * kHeadDim + lane_base + c * 32, raw[c]);
+    ptx::tmem_wait_ld();
+  }
 #pragma unroll
   for (int c = 0; c < kHeadDim / 32; ++c) {
-    uint32_t raw[32];
-    if (!zero) {
-      ptx::tmem_ld32(tmem + 2 * kTileN + half * kHeadDim + lane_base + c * 32, raw);
-      ptx::tmem_wait_ld();
-    }
 #pragma unroll
     for (int e = 0; e < 16; ++e)
-      packed[c * 16 + e] = zero ? 0u : pack_bf16(__uint_as_float(raw[2 * e]) * s, __uint_as_float(raw[2 * e + 1]) * s);
+      packed[c * 16 + e] =
+          zero ? 0u : pack_bf16(__uint_as_float(raw[c][2 * e]) * s, __uint_as_float(raw[c][2 * e + 1]) * s);
   }
   if (j < a.k_len) {
     const int64_t* st = half ? a.dk_strides : a.dv_strides;
@@ -241,6 +251,7 @@ __device__ __forceinline__ void bwd2_compute(Bwd2Shared& sm, const wm_attn_args&
     }
     fetch_key_docs(next_visited(kt + 1));
     // key rows at or beyond the last visible slot may hold anything: clear them before the MMAs read the tile
+    if (tid == 0) trace_event(sm, 1100 + kt);
     if (!wait_or_abort(sm, &sm.kv_full[s], (active >> 1) & 1, 90)) return;
     if (j0 + row >= w.kvis) {
       uint4* dst = reinterpret_cast<uint4*>((half ? sm.v[s] : sm.k[s]) + row * 128);
@@ -250,6 +261,7 @@ __device__ __forceinline__ void bwd2_compute(Bwd2Shared& sm, const wm_attn_args&
     ptx::fence_async_shared();
     ptx::mbar_arrive(&sm.kv_ready[s]);
     if (!wait_or_abort(sm, &sm.kv_ready[s], (active >> 1) & 1, 91)) return;  // also orders the document tables
+    if (tid == 0) trace_event(sm, 1200 + kt);
     int tmin = 0, tmax = 0, tend = 0;
     if (w.docs) {
       tmin = min(min(sm.summary[s][0][0], sm.summary[s][1][0]), min(sm.summary[s][2][0], sm.summary[s][3][0]));
@@ -264,53 +276,89 @@ __device__ __forceinline__ void bwd2_compute(Bwd2Shared& sm, const wm_attn_args&
       int cls = !live[qt] || j0 >= r.hi ? kTileNone : (j0 + kTileN <= r.hi ? kTileFull : kTileCausal);
       if (w.docs && cls != kTileNone) {
         const bool uniform = tmin == tmax;
+        const bool own_doc = uniform && tmin == r.seg && j0 >= r.lo && tend > r.qi;
         if (uniform && tmin != -1 && tmin != r.seg) {
           cls = kTileNone;
-        } else if (!(cls == kTileFull && uniform && tmin == r.seg && j0 >= r.lo && tend > r.qi)) {
+        } else if (!own_doc) {
           cls = kTileDocs;
         }
       }
       const int lim = r.hi - j0;
       if (!wait_or_abort(sm, &sm.sdp_full, it & 1, 92)) return;
+      if (tid == 0) trace_event(sm, 500 + it);
       if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;
       ptx::tc_fence_after();
+      if (tid == 0) trace_event(sm, 600 + it);
       if (pending_kt >= 0) {
         bwd2_store_dkv(a, tmem, pending_kt, row, half, lane_base, head, batch, false);
         pending_kt = -1;
+        if (tid == 0) trace_event(sm, 700 + it);
       }
-#pragma unroll 1
+      // all four TMEM loads of the iteration are in flight before the single wait (a load takes ~500 cycles)
+      uint32_t xs[2][32], ys[2][32];
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const int col0 = half * 64 + c * 32;
-        uint32_t xs[32], ys[32];
-        ptx::tmem_ld32(tmem + lane_base + col0, xs);
-        ptx::tmem_ld32(tmem + kTileN + lane_base + col0, ys);
-        ptx::tmem_wait_ld();
-        uint32_t pp[16], dd[16];
+        ptx::tmem_ld32(tmem + lane_base + half * 64 + c * 32, xs[c]);
+        ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64 + c * 32, ys[c]);
+      }
+      ptx::tmem_wait_ld();
+      if (tid == 0) trace_event(sm, 800 + it);
+      // one comparison per element on the common path; the per-element document rule is a separate, rare loop
+      const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
+      const float nl = -lse2[qt], dlt = dl[qt];
+      if (cls != kTileDocs) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float pv[2], dv[2];
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = half * 64 + c * 32;
+          uint32_t pp[16], dd[16];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = col0 + 2 * e + u;
-            bool vis_e = cls == kTileFull || (cls != kTileNone && col < lim);
-            if (cls == kTileDocs) vis_e = vis_e & doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col]);
-            const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e + u]), sl2, -lse2[qt]));
-            pv[u] = vis_e ? p : 0.f;
-            dv[u] = vis_e ? p * (__uint_as_float(ys[2 * e + u]) - dl[qt]) : 0.f;
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e]), sl2, nl));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e + 1]), sl2, nl));
+            const bool v0 = col0 + 2 * e < lim_eff, v1 = col0 + 2 * e + 1 < lim_eff;
+            pp[e] = pack_bf16(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
+            dd[e] = pack_bf16(v0 ? p0 * (__uint_as_float(ys[c][2 * e]) - dlt) : 0.f,
+                              v1 ? p1 * (__uint_as_float(ys[c][2 * e + 1]) - dlt) : 0.f);
           }
-          pp[e] = pack_bf16(pv[0], pv[1]);
-          dd[e] = pack_bf16(dv[0], dv[1]);
-        }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int off = ((c * 4 + u) ^ (row & 7)) << 4;
-          *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-          *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+          for (int u = 0; u < 4; ++u) {
+            const int off = ((c * 4 + u) ^ (row & 7)) << 4;
+            *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+            *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = half * 64 + c * 32;
+          uint32_t pp[16], dd[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = col0 + 2 * e + u;
+              const bool vis_e = (col < lim) & doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col]);
+              const float p = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e + u]), sl2, nl));
+              pv[u] = vis_e ? p : 0.f;
+              dv[u] = vis_e ? p * (__uint_as_float(ys[c][2 * e + u]) - dlt) : 0.f;
+            }
+            pp[e] = pack_bf16(pv[0], pv[1]);
+            dd[e] = pack_bf16(dv[0], dv[1]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int off = ((c * 4 + u) ^ (row & 7)) << 4;
+            *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+            *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+          }
         }
       }
+      if (tid == 0) trace_event(sm, 900 + it);
       ptx::fence_async_shared();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&sm.pds_full);
+      if (tid == 0) trace_event(sm, 1000 + it);
       ++it;
     }
     pending_kt = kt;
@@ -367,6 +415,7 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
   if (tid == 0) {
     sm.abort_flag = 0;
     sm.epoch = epoch;
+    trace_begin(sm, epoch);
     sm.lo_min[0] = sm.lo_min[1] = INT_MAX;
     sm.hi_max[0] = sm.hi_max[1] = 0;
     sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
@@ -429,5 +478,6 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
   }
   ptx::tc_fence_before();
   __syncthreads();
+  trace_flush(sm);
   if (warp == 8) ptx::tmem_dealloc(tmem, kTmemCols);
 }

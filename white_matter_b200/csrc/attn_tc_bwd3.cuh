@@ -1,0 +1,422 @@
+// Backward pipeline for short query axes with the tensor cores and the compute warps overlapped
+// (included by attn_tc.cu; same residency idea and TMEM map as attn_tc_bwd2.cuh).
+//
+// An iteration is one (key tile, query tile) pair; the list of visible pairs is built once per
+// block.  The compute warps pull S and dP of iteration i out of TMEM into registers and release
+// them at once (sdp_free), so the MMA warp issues S/dP of iteration i+1 while the exponentials of
+// iteration i are still being computed; P and dS of iteration i are written to shared memory only
+// after the dV/dK/dQ products of iteration i-1 have read the previous contents (mma_done), which by
+// then have had a whole math phase to complete.  dK/dV of a finished key tile are stored by the
+// compute warps just before they publish the first P/dS of the next key tile.
+#pragma once
+
+constexpr int kBwd3MaxIter = 256;
+
+struct Bwd3Shared {
+  unsigned char q[2][kTileBytes];
+  unsigned char g[2][kTileBytes];  // dO
+  unsigned char k[2][kTileBytes];
+  unsigned char v[2][kTileBytes];
+  unsigned char p[2 * kTileBytes];
+  unsigned char ds[2 * kTileBytes];
+  uint64_t qg_full;
+  uint64_t kv_full[2], kv_ready[2], kv_empty[2];
+  uint64_t sdp_full, sdp_free, pds_full, mma_done;
+  int key_seg[2][kTileN];
+  int key_end[2][kTileN];
+  int summary[2][4][3];
+  int lo_min[2], hi_max[2];
+  int has_dummy;
+  // iteration list: key tile | query tile << 12 | first-of-key-tile << 13 | last-of-key-tile << 14 | visited index << 16
+  uint32_t sched[kBwd3MaxIter];
+  int n_iter;
+  uint32_t tmem_base;
+  int abort_flag;
+  int epoch;
+  int trace_on, trace_n;
+  long long trace[kTraceSlots];
+};
+
+struct Bwd3Iter {
+  int kt, qt, first, last, active;
+};
+
+__device__ __forceinline__ Bwd3Iter bwd3_iter(uint32_t e) {
+  Bwd3Iter it;
+  it.kt = e & 0xfff;
+  it.qt = (e >> 12) & 1;
+  it.first = (e >> 13) & 1;
+  it.last = (e >> 14) & 1;
+  it.active = e >> 16;
+  return it;
+}
+
+__device__ __forceinline__ void bwd3_issue_sdp(Bwd3Shared& sm, uint32_t tmem, const Bwd3Iter& e) {
+  constexpr uint32_t idesc_s = ptx::make_idesc_bf16(kTileM, kTileN, 0, 0);
+  const int s = e.active & 1;
+  const uint32_t q_base = ptx::smem_u32(sm.q[e.qt]), g_base = ptx::smem_u32(sm.g[e.qt]);
+  const uint32_t k_base = ptx::smem_u32(sm.k[s]), v_base = ptx::smem_u32(sm.v[s]);
+#pragma unroll
+  for (int kk = 0; kk < kHeadDim / 16; ++kk)
+    ptx::mma_bf16_ss(tmem, ptx::make_smem_desc_sw128(q_base + kk * 32, 16, 1024),
+                     ptx::make_smem_desc_sw128(k_base + kk * 32, 16, 1024), idesc_s, kk > 0);
+#pragma unroll
+  for (int kk = 0; kk < kHeadDim / 16; ++kk)
+    ptx::mma_bf16_ss(tmem + kTileN, ptx::make_smem_desc_sw128(g_base + kk * 32, 16, 1024),
+                     ptx::make_smem_desc_sw128(v_base + kk * 32, 16, 1024), idesc_s, kk > 0);
+  ptx::mma_commit(&sm.sdp_full);
+}
+
+__device__ __forceinline__ void bwd3_mma(Bwd3Shared& sm, uint32_t tmem) {
+  const int n = sm.n_iter;
+  if (n == 0) return;
+  if (!wait_or_abort(sm, &sm.qg_full, 0, 80)) return;
+  constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, kHeadDim, 1, 1);
+  constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);
+  const uint32_t p_base = ptx::smem_u32(sm.p), ds_base = ptx::smem_u32(sm.ds);
+  bool dq_started[2] = {false, false};
+  Bwd3Iter e = bwd3_iter(sm.sched[0]);
+  if (!wait_or_abort(sm, &sm.kv_ready[e.active & 1], (e.active >> 1) & 1, 81)) return;
+  ptx::tc_fence_after();
+  bwd3_issue_sdp(sm, tmem, e);
+  for (int it = 0; it < n; ++it) {
+    // S/dP of this iteration are in the compute warps' registers: the next pair may overwrite them
+    if (!wait_or_abort(sm, &sm.sdp_free, it & 1, 83)) return;
+    ptx::tc_fence_after();
+    if (it + 1 < n) {
+      const Bwd3Iter nx = bwd3_iter(sm.sched[it + 1]);
+      if (nx.first && !wait_or_abort(sm, &sm.kv_ready[nx.active & 1], (nx.active >> 1) & 1, 81)) return;
+      ptx::tc_fence_after();
+      bwd3_issue_sdp(sm, tmem, nx);
+    }
+    if (!wait_or_abort(sm, &sm.pds_full, it & 1, 82)) return;
+    ptx::tc_fence_after();
+    const int s = e.active & 1;
+    const uint32_t q_base = ptx::smem_u32(sm.q[e.qt]), g_base = ptx::smem_u32(sm.g[e.qt]);
+    const uint32_t k_base = ptx::smem_u32(sm.k[s]);
+    const bool acc_kv = !e.first;
+    const bool acc_q = e.qt ? dq_started[1] : dq_started[0];
+#pragma unroll
+    for (int kk = 0; kk < kTileM / 16; ++kk)
+      ptx::mma_bf16_ss(tmem + 2 * kTileN, ptx::make_smem_desc_sw128(p_base + kk * 2048, kTileBytes, 1024),
+                       ptx::make_smem_desc_sw128(g_base + kk * 2048, 1024, 1024), idesc_t, acc_kv || (kk > 0));
+#pragma unroll
+    for (int kk = 0; kk < kTileM / 16; ++kk)
+      ptx::mma_bf16_ss(tmem + 2 * kTileN + kHeadDim, ptx::make_smem_desc_sw128(ds_base + kk * 2048, kTileBytes, 1024),
+                       ptx::make_smem_desc_sw128(q_base + kk * 2048, 1024, 1024), idesc_t, acc_kv || (kk > 0));
+#pragma unroll
+    for (int kk = 0; kk < kTileN / 16; ++kk)
+      ptx::mma_bf16_ss(tmem + 2 * kTileN + 2 * kHeadDim + e.qt * kHeadDim,
+                       ptx::make_smem_desc_sw128(ds_base + (kk >> 2) * kTileBytes + (kk & 3) * 32, 16, 1024),
+                       ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, acc_q || (kk > 0));
+    if (e.qt) dq_started[1] = true; else dq_started[0] = true;
+    ptx::mma_commit(&sm.mma_done);
+    if (e.last) ptx::mma_commit(&sm.kv_empty[s]);
+    if (it + 1 < n) e = bwd3_iter(sm.sched[it + 1]);
+  }
+}
+
+__device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args& a, uint32_t tmem, const Bwd2Walk& w,
+                                             const float* delta, int head, int batch) {
+  const int tid = threadIdx.x;
+  const int row = tid & 127;
+  const int half = tid >> 7;
+  const int warp = tid >> 5, lane = tid & 31;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const float sl2 = a.scale * kLog2e;
+  const GroupCtx g = group_ctx(a, 0);
+  const int n = sm.n_iter;
+
+  // this thread's row in both query tiles
+  RowBound rb0, rb1;
+  float nl0 = -INFINITY, nl1 = -INFINITY, dl0 = 0.f, dl1 = 0.f;
+  bool live0 = false, live1 = false;
+  {
+    rb0.lo = rb0.hi = rb0.seg = 0;
+    rb0.qi = row;
+    rb1 = rb0;
+    rb1.qi = kTileM + row;
+    if (row < a.q_len) {
+      live0 = true;
+      rb0 = row_bound(a, g, batch, row);
+      const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + row;
+      nl0 = -a.lse[stat] * kLog2e;
+      dl0 = delta[stat];
+    }
+    if (w.nq > 1 && kTileM + row < a.q_len) {
+      live1 = true;
+      rb1 = row_bound(a, g, batch, kTileM + row);
+      const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + kTileM + row;
+      nl1 = -a.lse[stat] * kLog2e;
+      dl1 = delta[stat];
+    }
+  }
+  unsigned char* prow = sm.p + half * kTileBytes + (row >> 3) * 1024 + (row & 7) * 128;
+  unsigned char* drow = sm.ds + half * kTileBytes + (row >> 3) * 1024 + (row & 7) * 128;
+
+  // key tiles nobody sees get exact zeros; they are not part of the iteration list
+  for (int kt = 0; kt < w.n_kt; ++kt)
+    if (!pair_visible(w, kt, 0) && !pair_visible(w, kt, 1)) bwd2_store_dkv(a, tmem, kt, row, half, lane_base, head, batch, true);
+
+  // Make a visited key tile ready for the MMAs: publish its document table, clear rows beyond the last visible
+  // slot (they may hold anything), and meet the other compute threads at kv_ready.
+  auto prepare = [&](const Bwd3Iter& e) -> bool {
+    const int s = e.active & 1;
+    const int j0 = e.kt * kTileN;
+    if (w.docs && half == 0) {
+      int seg = INT_MIN, end = 0;
+      const int j = j0 + row;
+      if (j < a.k_len) {
+        const long long at = static_cast<long long>(batch) * a.k_len + j;
+        seg = __ldg(a.k_seg + at);
+        end = __ldg(a.k_query_end + at);
+      }
+      sm.key_seg[s][row] = seg;
+      sm.key_end[s][row] = end;
+      const int smin = __reduce_min_sync(0xffffffffu, seg);
+      const int smax = __reduce_max_sync(0xffffffffu, seg);
+      const int emin = __reduce_min_sync(0xffffffffu, end);
+      if (lane == 0) {
+        sm.summary[s][warp][0] = smin;
+        sm.summary[s][warp][1] = smax;
+        sm.summary[s][warp][2] = emin;
+      }
+    }
+    if (!wait_or_abort(sm, &sm.kv_full[s], (e.active >> 1) & 1, 90)) return false;
+    if (j0 + row >= w.kvis) {
+      uint4* dst = reinterpret_cast<uint4*>((half ? sm.v[s] : sm.k[s]) + row * 128);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+    }
+    ptx::fence_async_shared();
+    ptx::mbar_arrive(&sm.kv_ready[s]);
+    return wait_or_abort(sm, &sm.kv_ready[s], (e.active >> 1) & 1, 91);
+  };
+
+  if (n > 0 && !prepare(bwd3_iter(sm.sched[0]))) return;
+  int pending_kt = -1;
+  for (int it = 0; it < n; ++it) {
+    const Bwd3Iter e = bwd3_iter(sm.sched[it]);
+    const int s = e.active & 1;
+    const int j0 = e.kt * kTileN;
+    const RowBound& r = e.qt ? rb1 : rb0;
+    const bool live = e.qt ? live1 : live0;
+    const float nl = e.qt ? nl1 : nl0;
+    const float dlt = e.qt ? dl1 : dl0;
+    int cls = !live || j0 >= r.hi ? kTileNone : (j0 + kTileN <= r.hi ? kTileFull : kTileCausal);
+    if (w.docs && cls != kTileNone) {
+      const int tmin = min(min(sm.summary[s][0][0], sm.summary[s][1][0]), min(sm.summary[s][2][0], sm.summary[s][3][0]));
+      const int tmax = max(max(sm.summary[s][0][1], sm.summary[s][1][1]), max(sm.summary[s][2][1], sm.summary[s][3][1]));
+      const int tend = min(min(sm.summary[s][0][2], sm.summary[s][1][2]), min(sm.summary[s][2][2], sm.summary[s][3][2]));
+      const bool uniform = tmin == tmax;
+      const bool own_doc = uniform && tmin == r.seg && j0 >= r.lo && tend > r.qi;
+      if (uniform && tmin != -1 && tmin != r.seg) {
+        cls = kTileNone;
+      } else if (!own_doc) {
+        cls = kTileDocs;
+      }
+    }
+    const int lim = r.hi - j0;
+    if (!wait_or_abort(sm, &sm.sdp_full, it & 1, 92)) return;
+    ptx::tc_fence_after();
+    if (tid == 0) trace_event(sm, 500 + it);
+    uint32_t xs[2][32], ys[2][32];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      ptx::tmem_ld32(tmem + lane_base + half * 64 + c * 32, xs[c]);
+      ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64 + c * 32, ys[c]);
+    }
+    ptx::tmem_wait_ld();
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(&sm.sdp_free);  // the scores are in registers: S/dP of the next pair may be issued
+    if (tid == 0) trace_event(sm, 800 + it);
+    if (e.last && it + 1 < n && !prepare(bwd3_iter(sm.sched[it + 1]))) return;
+    // P = exp2(S*scale*log2e - lse), dS = P * (dP - delta), packed to bf16 in registers
+    uint32_t pp[2][16], dd[2][16];
+    if (cls != kTileDocs) {
+      const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = half * 64 + c * 32;
+#pragma unroll
+        for (int e2 = 0; e2 < 16; ++e2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e2]), sl2, nl));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e2 + 1]), sl2, nl));
+          const bool v0 = col0 + 2 * e2 < lim_eff, v1 = col0 + 2 * e2 + 1 < lim_eff;
+          pp[c][e2] = pack_bf16(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
+          dd[c][e2] = pack_bf16(v0 ? p0 * (__uint_as_float(ys[c][2 * e2]) - dlt) : 0.f,
+                                v1 ? p1 * (__uint_as_float(ys[c][2 * e2 + 1]) - dlt) : 0.f);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = half * 64 + c * 32;
+#pragma unroll
+        for (int e2 = 0; e2 < 16; ++e2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = col0 + 2 * e2 + u;
+            const bool vis = (col < lim) & doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col]);
+            const float p = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e2 + u]), sl2, nl));
+            pv[u] = vis ? p : 0.f;
+            dv[u] = vis ? p * (__uint_as_float(ys[c][2 * e2 + u]) - dlt) : 0.f;
+          }
+          pp[c][e2] = pack_bf16(pv[0], pv[1]);
+          dd[c][e2] = pack_bf16(dv[0], dv[1]);
+        }
+      }
+    }
+    if (tid == 0) trace_event(sm, 900 + it);
+    // the shared P / dS tiles are read by the products of the previous iteration until mma_done
+    if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;
+    ptx::tc_fence_after();
+    if (pending_kt >= 0) {
+      bwd2_store_dkv(a, tmem, pending_kt, row, half, lane_base, head, batch, false);
+      pending_kt = -1;
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int off = ((c * 4 + u) ^ (row & 7)) << 4;
+        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[c][4 * u], pp[c][4 * u + 1], pp[c][4 * u + 2], pp[c][4 * u + 3]);
+        *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[c][4 * u], dd[c][4 * u + 1], dd[c][4 * u + 2], dd[c][4 * u + 3]);
+      }
+    }
+    ptx::fence_async_shared();
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(&sm.pds_full);
+    if (tid == 0) trace_event(sm, 1000 + it);
+    if (e.last) pending_kt = e.kt;
+  }
+  if (n > 0) {
+    if (!wait_or_abort(sm, &sm.mma_done, (n - 1) & 1, 94)) return;
+    ptx::tc_fence_after();
+    if (pending_kt >= 0) bwd2_store_dkv(a, tmem, pending_kt, row, half, lane_base, head, batch, false);
+  }
+  {
+    // half h writes the dQ rows of query tile h
+    const int qt = half;
+    const int i = qt * kTileM + row;
+    const bool any = true;
+    bool issued = false;  // did any iteration target this query tile?
+    for (int it = 0; it < n; ++it) issued = issued || (((sm.sched[it] >> 12) & 1) == static_cast<uint32_t>(qt));
+    const int row_hi = half ? rb1.hi : rb0.hi;
+    uint32_t packed[kHeadDim / 2];
+    uint32_t raw[2][32];
+    if (issued && any) {
+      ptx::tmem_ld32(tmem + 2 * kTileN + 2 * kHeadDim + qt * kHeadDim + lane_base, raw[0]);
+      ptx::tmem_ld32(tmem + 2 * kTileN + 2 * kHeadDim + qt * kHeadDim + lane_base + 32, raw[1]);
+      ptx::tmem_wait_ld();
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int e2 = 0; e2 < 16; ++e2)
+        packed[c * 16 + e2] = issued && any && row_hi > 0
+                                  ? pack_bf16(__uint_as_float(raw[c][2 * e2]) * a.scale, __uint_as_float(raw[c][2 * e2 + 1]) * a.scale)
+                                  : 0u;
+    }
+    if (qt < w.nq && i < a.q_len) {
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dq) + batch * a.dq_strides[0] +
+                                            head * a.dq_strides[1] + static_cast<long long>(i) * a.dq_strides[2]);
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+    }
+  }
+}
+
+
+__global__ void __launch_bounds__(kBwd2Threads, 1)
+    attn_bwd_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_g,
+                        const wm_attn_args a, const float* delta, const int epoch) {
+  extern __shared__ unsigned char smem_raw[];
+  Bwd3Shared& sm = *reinterpret_cast<Bwd3Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.x;
+  const int batch = blockIdx.y;
+  const GroupCtx g = group_ctx(a, 0);
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    sm.epoch = epoch;
+    trace_begin(sm, epoch);
+    sm.lo_min[0] = sm.lo_min[1] = INT_MAX;
+    sm.hi_max[0] = sm.hi_max[1] = 0;
+    sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
+  }
+  __syncthreads();
+  if (tid < kBwd2Compute) {
+    const int qt = tid >> 7;
+    int lo = INT_MAX, hi = 0;
+    if (tid < a.q_len) {
+      const RowBound rb = row_bound(a, g, batch, tid);
+      hi = rb.hi;
+      if (rb.hi > 0) lo = rb.lo;
+    }
+    lo = __reduce_min_sync(0xffffffffu, lo);
+    hi = __reduce_max_sync(0xffffffffu, hi);
+    if (lane == 0) {
+      atomicMin(&sm.lo_min[qt], lo);
+      atomicMax(&sm.hi_max[qt], hi);
+    }
+  }
+  __syncthreads();
+  Bwd2Walk w;
+  w.nq = (a.q_len + kTileM - 1) / kTileM;
+  w.n_kt = (a.k_len + kTileN - 1) / kTileN;
+  w.lo_min[0] = sm.lo_min[0];
+  w.lo_min[1] = sm.lo_min[1];
+  w.hi_max[0] = sm.hi_max[0];
+  w.hi_max[1] = sm.hi_max[1];
+  w.kvis = max(w.hi_max[0], w.hi_max[1]);
+  w.docs = a.q_seg != nullptr;
+  w.dummy = sm.has_dummy != 0;
+  if (tid == 0) {
+    // the list of visible (key tile, query tile) pairs, in execution order
+    int n = 0, active = 0;
+    for (int kt = 0; kt < w.n_kt; ++kt) {
+      const bool v0 = pair_visible(w, kt, 0), v1 = pair_visible(w, kt, 1);
+      if (!v0 && !v1) continue;
+      if (v0) sm.sched[n++] = kt | (0u << 12) | (1u << 13) | ((v1 ? 0u : 1u) << 14) | (static_cast<uint32_t>(active) << 16);
+      if (v1) sm.sched[n++] = kt | (1u << 12) | ((v0 ? 0u : 1u) << 13) | (1u << 14) | (static_cast<uint32_t>(active) << 16);
+      ++active;
+    }
+    sm.n_iter = n;
+    ptx::mbar_init(&sm.qg_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&sm.kv_full[s], 1);
+      ptx::mbar_init(&sm.kv_ready[s], kBwd2Compute);
+      ptx::mbar_init(&sm.kv_empty[s], 1);
+    }
+    ptx::mbar_init(&sm.sdp_full, 1);
+    ptx::mbar_init(&sm.sdp_free, kBwd2Compute);
+    ptx::mbar_init(&sm.pds_full, kBwd2Compute);
+    ptx::mbar_init(&sm.mma_done, 1);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 8) {
+    ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  if (warp < 8) {
+    bwd3_compute(sm, a, tmem, w, delta, head, batch);
+  } else if (warp == 8) {
+    if (lane == 0) bwd2_producer(sm, &map_q, &map_k, &map_v, &map_g, w, head, batch);
+  } else {
+    if (lane == 0) bwd3_mma(sm, tmem);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  trace_flush(sm);
+  if (warp == 8) ptx::tmem_dealloc(tmem, kTmemCols);
+}

@@ -17,10 +17,13 @@ struct FwdShared {
   uint32_t tmem_base;
   int abort_flag;
   int epoch;
+  int trace_on, trace_n;
+  long long trace[kTraceSlots];
 };
 
 // ------------------------------------------------------------------ producer (one lane of warp 4)
-__device__ __forceinline__ void producer_role(FwdShared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
+template <class Shared>
+__device__ __forceinline__ void producer_role(Shared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
                                               const CUtensorMap* map_v, const TileWalk& w, int q0, int head,
                                               int kv_head, int batch) {
   ptx::prefetch_tmap(map_q);
@@ -35,14 +38,17 @@ __device__ __forceinline__ void producer_role(FwdShared& sm, const CUtensorMap* 
     if (!wait_or_abort(sm, &sm.k_empty[s], parity, 11)) return;
     ptx::mbar_expect_tx(&sm.k_full[s], kTileBytes);
     ptx::tma_load_4d(sm.k[s], map_k, &sm.k_full[s], 0, j0, kv_head, batch);
+    trace_event(sm, 100 + n);
     if (!wait_or_abort(sm, &sm.v_empty[s], parity, 12)) return;
     ptx::mbar_expect_tx(&sm.v_full[s], kTileBytes);
     ptx::tma_load_4d(sm.v[s], map_v, &sm.v_full[s], 0, j0, kv_head, batch);
+    trace_event(sm, 200 + n);
   }
 }
 
 // ------------------------------------------------------------------ MMA issuer (one lane of warp 5)
-__device__ __forceinline__ bool issue_qk(FwdShared& sm, uint32_t tmem, int n) {
+template <class Shared>
+__device__ __forceinline__ bool issue_qk(Shared& sm, uint32_t tmem, int n) {
   const int s = n % kStages;
   if (!wait_or_abort(sm, &sm.k_full[s], (n / kStages) & 1, 21)) return false;
   ptx::tc_fence_after();
@@ -58,10 +64,12 @@ __device__ __forceinline__ bool issue_qk(FwdShared& sm, uint32_t tmem, int n) {
   }
   ptx::mma_commit(&sm.k_empty[s]);
   ptx::mma_commit(&sm.s_full[n & 1]);
+  trace_event(sm, 400 + n);
   return true;
 }
 
-__device__ __forceinline__ void mma_role(FwdShared& sm, uint32_t tmem, const TileWalk& w) {
+template <class Shared>
+__device__ __forceinline__ void mma_role(Shared& sm, uint32_t tmem, const TileWalk& w) {
   if (!wait_or_abort(sm, &sm.q_full, 0, 20)) return;
   if (!issue_qk(sm, tmem, 0)) return;
   constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);
@@ -71,6 +79,7 @@ __device__ __forceinline__ void mma_role(FwdShared& sm, uint32_t tmem, const Til
     const int b = n & 1;
     const int s = n % kStages;
     if (!wait_or_abort(sm, &sm.p_full[b], (n >> 1) & 1, 22)) return;
+    trace_event(sm, 300 + n);
     if (!wait_or_abort(sm, &sm.v_full[s], (n / kStages) & 1, 23)) return;
     ptx::tc_fence_after();
     const uint32_t p_base = ptx::smem_u32(sm.p[b]);
@@ -84,6 +93,7 @@ __device__ __forceinline__ void mma_role(FwdShared& sm, uint32_t tmem, const Til
     }
     ptx::mma_commit(&sm.v_empty[s]);
     ptx::mma_commit(&sm.pv_done[b]);
+    trace_event(sm, 500 + n);
   }
 }
 
@@ -140,6 +150,7 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     // classify the tile for this row
     bool none = !live || j0 >= rb.hi;
     bool full = live && j0 + kTileN <= rb.hi;
+    bool own_doc = !docs;
     if (docs && !none) {
       int smin = sm.tile_summary[b][0][0], smax = sm.tile_summary[b][0][1], emin = sm.tile_summary[b][0][2];
 #pragma unroll
@@ -149,7 +160,8 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
         emin = min(emin, sm.tile_summary[b][q][2]);
       }
       const bool uniform = smin == smax;
-      full = full && uniform && smin == rb.seg && j0 >= rb.lo && emin > rb.qi;
+      own_doc = uniform && smin == rb.seg && j0 >= rb.lo && emin > rb.qi;
+      full = full && own_doc;
       if (uniform && smin != -1 && smin != rb.seg) none = true;
     }
     if (!wait_or_abort(sm, &sm.s_full[b], (n >> 1) & 1, 31)) return;
@@ -174,7 +186,7 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     } else if (full) {
 #pragma unroll
       for (int c = 0; c < kTileN; ++c) top = fmaxf(top, x[c]);
-    } else if (!docs) {
+    } else if (own_doc) {
       const int lim = rb.hi - j0;
 #pragma unroll
       for (int c = 0; c < kTileN; ++c) {
@@ -303,6 +315,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1)
     sm.red_max_hi = 0;
     sm.abort_flag = 0;
     sm.epoch = epoch;
+    trace_begin(sm, epoch);
     sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
   }
   __syncthreads();
@@ -376,6 +389,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1)
   }
   ptx::tc_fence_before();
   __syncthreads();
+  trace_flush(sm);
   if (warp == 4) ptx::tmem_dealloc(tmem, kTmemCols);
 }
 

@@ -180,10 +180,12 @@ __device__ __forceinline__ void softmax2(Fwd2Shared& sm, const wm_attn_args& a, 
           tmax = max(tmax, sm.tile_summary[b][q][1]);
           tend = min(tend, sm.tile_summary[b][q][2]);
         }
+        // a tile that lies inside the row's own document needs the causal bound at most
         const bool uniform = tmin == tmax;
+        const bool own_doc = uniform && tmin == rb.seg && j0 >= rb.lo && tend > rb.qi;
         if (uniform && tmin != -1 && tmin != rb.seg) {
           cls = kTileNone;
-        } else if (!(cls == kTileFull && uniform && tmin == rb.seg && j0 >= rb.lo && tend > rb.qi)) {
+        } else if (!own_doc) {
           cls = kTileDocs;
         }
       }

@@ -43,6 +43,7 @@ bool tc_bwd_supported(const wm_attn_args& a);
 int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream);
 size_t tc_attn_bwd_workspace(const wm_attn_args& a);
 int tc_device_status(bool reset);
+int tc_debug_trace(long long* out, int capacity, int arm_after);
 
 // ---------------------------------------------------------------- device side
 constexpr float kLog2e = 1.4426950408889634f;
