@@ -317,6 +317,8 @@ bool tc_bwd_supported(const wm_attn_args& a) {
   if (!tc_fwd_supported(a)) return false;
   if (a.dout == nullptr) return true;  // shape query before the tensors exist
   if (!tma_ok(a.dout, a.dout_strides, a.batch, a.q_heads, a.q_len)) return false;
+  if (!tma_ok(a.dk, a.dk_strides, a.batch, a.kv_heads, a.k_len)) return false;
+  if (!tma_ok(a.dv, a.dv_strides, a.batch, a.kv_heads, a.k_len)) return false;
   const void* ptrs[3] = {a.dq, a.dk, a.dv};
   const int64_t* strides[3] = {a.dq_strides, a.dk_strides, a.dv_strides};
   for (int n = 0; n < 3; ++n) {
@@ -380,8 +382,13 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
         WM_CUDA(cudaFuncSetAttribute(attn_bwd_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem3)));
         configured3 = true;
       }
-      attn_bwd_tc3_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem3, stream>>>(map_q, map_k, map_v, map_g, a, delta,
-                                                                                     next_epoch());
+      CUtensorMap map_dk, map_dv;
+      status = make_map(&map_dk, a.dk, a.batch, a.kv_heads, a.k_len, a.dk_strides, kTileN);
+      if (status != WM_OK) return status;
+      status = make_map(&map_dv, a.dv, a.batch, a.kv_heads, a.k_len, a.dv_strides, kTileN);
+      if (status != WM_OK) return status;
+      attn_bwd_tc3_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem3, stream>>>(map_q, map_k, map_v, map_g, map_dk,
+                                                                                     map_dv, a, delta, next_epoch());
     } else {
       attn_bwd_tc2_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem2, stream>>>(map_q, map_k, map_v, map_g, a, delta,
                                                                                      next_epoch());

@@ -22,6 +22,7 @@ struct Bwd3Shared {
   uint64_t qg_full;
   uint64_t kv_full[2], kv_ready[2], kv_empty[2];
   uint64_t sdp_full, sdp_free, pds_full, mma_done;
+  uint64_t out_full[2];  // dV (half 0) / dK (half 1) rows of a finished key tile are staged in shared memory
   int key_seg[2][kTileN];
   int key_end[2][kTileN];
   int summary[2][4][3];
@@ -111,13 +112,13 @@ __device__ __forceinline__ void bwd3_mma(Bwd3Shared& sm, uint32_t tmem) {
                        ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, acc_q || (kk > 0));
     if (e.qt) dq_started[1] = true; else dq_started[0] = true;
     ptx::mma_commit(&sm.mma_done);
-    if (e.last) ptx::mma_commit(&sm.kv_empty[s]);
     if (it + 1 < n) e = bwd3_iter(sm.sched[it + 1]);
   }
 }
 
 __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args& a, uint32_t tmem, const Bwd2Walk& w,
-                                             const float* delta, int head, int batch) {
+                                             const float* delta, int head, int batch, const CUtensorMap* map_dk,
+                                             const CUtensorMap* map_dv) {
   const int tid = threadIdx.x;
   const int row = tid & 127;
   const int half = tid >> 7;
@@ -193,8 +194,50 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
     return wait_or_abort(sm, &sm.kv_ready[s], (e.active >> 1) & 1, 91);
   };
 
+  // dV / dK of a finished key tile: TMEM -> bf16 -> the tile's own (now idle) V / K stage in shared memory, in
+  // the 128B-swizzled row layout of the output tensor map -> one TMA store per half.  The stage goes back to the
+  // producer once the store has read it.
+  int outs = 0;  // staged stores so far (parity of out_full)
+  int release_stage = -1;  // stage whose staged gradients still have to be read before the producer may refill it
+  auto release = [&]() {
+    if (release_stage >= 0 && row == 0) {
+      ptx::tma_store_wait_read();
+      ptx::mbar_arrive(&sm.kv_empty[release_stage]);
+    }
+    release_stage = -1;
+  };
+  auto stage_out = [&](int kt, int stage, bool release_now) -> bool {
+    const float sc = half ? a.scale : 1.f;
+    unsigned char* dst = (half ? sm.k[stage] : sm.v[stage]) + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {  // 32 columns at a time keeps the register footprint small
+      uint32_t raw[32];
+      ptx::tmem_ld32(tmem + 2 * kTileN + half * kHeadDim + lane_base + h2 * 32, raw);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2)
+          pk[e2] = pack_bf16(__uint_as_float(raw[c * 8 + 2 * e2]) * sc, __uint_as_float(raw[c * 8 + 2 * e2 + 1]) * sc);
+        *reinterpret_cast<uint4*>(dst + (((h2 * 4 + c) ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+    }
+    ptx::fence_async_shared();
+    ptx::mbar_arrive(&sm.out_full[half]);
+    if (!wait_or_abort(sm, &sm.out_full[half], outs & 1, 95)) return false;
+    if (row == 0) {
+      ptx::tma_store_4d(half ? map_dk : map_dv, half ? sm.k[stage] : sm.v[stage], 0, kt * kTileN, head, batch);
+      ptx::tma_store_commit();
+    }
+    release_stage = stage;
+    if (release_now) release();
+    ++outs;
+    return true;
+  };
+
   if (n > 0 && !prepare(bwd3_iter(sm.sched[0]))) return;
-  int pending_kt = -1;
+  int pending_kt = -1, pending_stage = 0;
   for (int it = 0; it < n; ++it) {
     const Bwd3Iter e = bwd3_iter(sm.sched[it]);
     const int s = e.active & 1;
@@ -220,38 +263,21 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
     if (!wait_or_abort(sm, &sm.sdp_full, it & 1, 92)) return;
     ptx::tc_fence_after();
     if (tid == 0) trace_event(sm, 500 + it);
-    uint32_t xs[2][32], ys[2][32];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      ptx::tmem_ld32(tmem + lane_base + half * 64 + c * 32, xs[c]);
-      ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64 + c * 32, ys[c]);
-    }
-    ptx::tmem_wait_ld();
-    ptx::tc_fence_before();
-    ptx::mbar_arrive(&sm.sdp_free);  // the scores are in registers: S/dP of the next pair may be issued
-    if (tid == 0) trace_event(sm, 800 + it);
-    if (e.last && it + 1 < n && !prepare(bwd3_iter(sm.sched[it + 1]))) return;
-    // P = exp2(S*scale*log2e - lse), dS = P * (dP - delta), packed to bf16 in registers
-    uint32_t pp[2][16], dd[2][16];
-    if (cls != kTileDocs) {
-      const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = half * 64 + c * 32;
+    // Two rounds of 32 columns keep the register footprint small: scores of round 0 are turned into P / dS
+    // while the loads of round 1 are in flight; S/dP are released to the MMA warp as soon as round 1 has landed.
+    const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
+    auto math = [&](const uint32_t (&xs)[32], const uint32_t (&ys)[32], int col0, uint32_t (&pp)[16], uint32_t (&dd)[16]) {
+      if (cls != kTileDocs) {
 #pragma unroll
         for (int e2 = 0; e2 < 16; ++e2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e2]), sl2, nl));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e2 + 1]), sl2, nl));
+          const float p0 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2]), sl2, nl));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2 + 1]), sl2, nl));
           const bool v0 = col0 + 2 * e2 < lim_eff, v1 = col0 + 2 * e2 + 1 < lim_eff;
-          pp[c][e2] = pack_bf16(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
-          dd[c][e2] = pack_bf16(v0 ? p0 * (__uint_as_float(ys[c][2 * e2]) - dlt) : 0.f,
-                                v1 ? p1 * (__uint_as_float(ys[c][2 * e2 + 1]) - dlt) : 0.f);
+          pp[e2] = pack_bf16(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
+          dd[e2] = pack_bf16(v0 ? p0 * (__uint_as_float(ys[2 * e2]) - dlt) : 0.f,
+                             v1 ? p1 * (__uint_as_float(ys[2 * e2 + 1]) - dlt) : 0.f);
         }
-      }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = half * 64 + c * 32;
+      } else {
 #pragma unroll
         for (int e2 = 0; e2 < 16; ++e2) {
           float pv[2], dv[2];
@@ -259,42 +285,64 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
           for (int u = 0; u < 2; ++u) {
             const int col = col0 + 2 * e2 + u;
             const bool vis = (col < lim) & doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col]);
-            const float p = fast_exp2(fmaf(__uint_as_float(xs[c][2 * e2 + u]), sl2, nl));
+            const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e2 + u]), sl2, nl));
             pv[u] = vis ? p : 0.f;
-            dv[u] = vis ? p * (__uint_as_float(ys[c][2 * e2 + u]) - dlt) : 0.f;
+            dv[u] = vis ? p * (__uint_as_float(ys[2 * e2 + u]) - dlt) : 0.f;
           }
-          pp[c][e2] = pack_bf16(pv[0], pv[1]);
-          dd[c][e2] = pack_bf16(dv[0], dv[1]);
+          pp[e2] = pack_bf16(pv[0], pv[1]);
+          dd[e2] = pack_bf16(dv[0], dv[1]);
         }
       }
-    }
-    if (tid == 0) trace_event(sm, 900 + it);
-    // the shared P / dS tiles are read by the products of the previous iteration until mma_done
-    if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;
-    ptx::tc_fence_after();
-    if (pending_kt >= 0) {
-      bwd2_store_dkv(a, tmem, pending_kt, row, half, lane_base, head, batch, false);
-      pending_kt = -1;
-    }
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
+    };
+    auto store = [&](int c, const uint32_t (&pp)[16], const uint32_t (&dd)[16]) {
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int off = ((c * 4 + u) ^ (row & 7)) << 4;
-        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[c][4 * u], pp[c][4 * u + 1], pp[c][4 * u + 2], pp[c][4 * u + 3]);
-        *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[c][4 * u], dd[c][4 * u + 1], dd[c][4 * u + 2], dd[c][4 * u + 3]);
+        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+        *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
       }
+    };
+    {
+      uint32_t xs[32], ys[32], pp[16], dd[16];
+      ptx::tmem_ld32(tmem + lane_base + half * 64, xs);
+      ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64, ys);
+      ptx::tmem_wait_ld();
+      math(xs, ys, half * 64, pp, dd);
+      // round 1 loads go out now; they land while round 0 is stored
+      ptx::tmem_ld32(tmem + lane_base + half * 64 + 32, xs);
+      ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64 + 32, ys);
+      if (tid == 0) trace_event(sm, 900 + it);
+      // the shared P / dS tiles are read by the products of the previous iteration until mma_done
+      if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;
+      ptx::tc_fence_after();
+      store(0, pp, dd);
+      ptx::tmem_wait_ld();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&sm.sdp_free);  // all scores are in registers: S/dP of the next pair may be issued
+      if (tid == 0) trace_event(sm, 800 + it);
+      // hand over a finished key tile (gradients and shared-memory stage), then prepare the next one
+      if (pending_kt >= 0) {
+        if (!stage_out(pending_kt, pending_stage, e.last)) return;
+        pending_kt = -1;
+      }
+      if (e.last && it + 1 < n && !prepare(bwd3_iter(sm.sched[it + 1]))) return;
+      math(xs, ys, half * 64 + 32, pp, dd);
+      store(1, pp, dd);
     }
     ptx::fence_async_shared();
     ptx::tc_fence_before();
     ptx::mbar_arrive(&sm.pds_full);
     if (tid == 0) trace_event(sm, 1000 + it);
-    if (e.last) pending_kt = e.kt;
+    release();
+    if (e.last) {
+      pending_kt = e.kt;
+      pending_stage = s;
+    }
   }
   if (n > 0) {
     if (!wait_or_abort(sm, &sm.mma_done, (n - 1) & 1, 94)) return;
     ptx::tc_fence_after();
-    if (pending_kt >= 0) bwd2_store_dkv(a, tmem, pending_kt, row, half, lane_base, head, batch, false);
+    if (pending_kt >= 0 && !stage_out(pending_kt, pending_stage, true)) return;
   }
   {
     // half h writes the dQ rows of query tile h
@@ -333,6 +381,7 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
 __global__ void __launch_bounds__(kBwd2Threads, 1)
     attn_bwd_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_g,
+                        const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
                         const wm_attn_args a, const float* delta, const int epoch) {
   extern __shared__ unsigned char smem_raw[];
   Bwd3Shared& sm = *reinterpret_cast<Bwd3Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -392,7 +441,8 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&sm.kv_full[s], 1);
       ptx::mbar_init(&sm.kv_ready[s], kBwd2Compute);
-      ptx::mbar_init(&sm.kv_empty[s], 1);
+      ptx::mbar_init(&sm.kv_empty[s], 2);  // the two halves' store threads release a stage
+      ptx::mbar_init(&sm.out_full[s], kTileM);
     }
     ptx::mbar_init(&sm.sdp_full, 1);
     ptx::mbar_init(&sm.sdp_free, kBwd2Compute);
@@ -409,12 +459,13 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
   ptx::tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   if (warp < 8) {
-    bwd3_compute(sm, a, tmem, w, delta, head, batch);
+    bwd3_compute(sm, a, tmem, w, delta, head, batch, &map_dk, &map_dv);
   } else if (warp == 8) {
     if (lane == 0) bwd2_producer(sm, &map_q, &map_k, &map_v, &map_g, w, head, batch);
   } else {
     if (lane == 0) bwd3_mma(sm, tmem);
   }
+  ptx::tma_store_wait_all();
   ptx::tc_fence_before();
   __syncthreads();
   trace_flush(sm);
