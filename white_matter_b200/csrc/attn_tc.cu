@@ -37,7 +37,7 @@ constexpr int kTileN = 128;
 constexpr int kHeadDim = 64;
 constexpr int kStages = 3;
 constexpr int kSoftmaxThreads = 128;
-constexpr int kThreadsFwd = 192;
+constexpr int kThreadsFwd = 192;  // key-stationary backward: 4 compute warps + producer + MMA
 constexpr uint32_t kTileBytes = kTileN * kHeadDim * 2;  // 16 KB: one Q, K or V tile
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
@@ -184,6 +184,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// How a key tile relates to one query row.
+enum TileClass { kTileNone = 0, kTileFull = 1, kTileCausal = 2, kTileDocs = 3 };
+
 struct TileWalk {
   int first_tile;
   int dummy_tile;
@@ -192,12 +195,8 @@ struct TileWalk {
 };
 
 #include "attn_tc_fwd.cuh"
-#include "attn_tc_fwd2.cuh"
-#include "attn_tc_fwd3.cuh"
-#include "attn_tc_fwd4.cuh"
 #include "attn_tc_bwd.cuh"
-#include "attn_tc_bwd2.cuh"
-#include "attn_tc_bwd3.cuh"
+#include "attn_tc_bwd_resident.cuh"
 
 }  // namespace
 
@@ -232,57 +231,13 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
   status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN);
   if (status != WM_OK) return status;
   dim3 grid((a.q_len + kTileM - 1) / kTileM, a.q_heads, a.batch);
-  // WM_B200_FWD_PIPELINE selects a forward pipeline (bring-up aid): 1 = one block per SM with 4 softmax warps,
-  // 2 = two blocks per SM, 3 (default) = one block per SM with the softmax split over two warpgroups
-  static const int pipeline = [] {
-    const char* v = getenv("WM_B200_FWD_PIPELINE");
-    return v != nullptr ? atoi(v) : 3;
-  }();
-  if (pipeline == 4) {
-    const size_t smem = sizeof(Fwd4Shared) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      configured = true;
-    }
-    attn_fwd_tc4_kernel<<<grid, kFwd4Threads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
-  } else if (pipeline == 3) {
-    const size_t smem = sizeof(Fwd3Shared) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      configured = true;
-    }
-    attn_fwd_tc3_kernel<<<grid, kFwd3Threads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
-  } else if (pipeline == 1) {
-    const size_t smem = sizeof(FwdShared) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      configured = true;
-    }
-    attn_fwd_tc_kernel<<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
-  } else {
-    const size_t smem = sizeof(Fwd2Shared) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      // two blocks per SM need the largest shared-memory carveout
-      WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc2_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                   cudaSharedmemCarveoutMaxShared));
-      configured = true;
-    }
-    static const int dbg = [&] {
-      const char* v = getenv("WM_B200_DBG");
-      if (v != nullptr) {
-        int blocks = -1;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attn_fwd_tc2_kernel, kThreadsFwd, smem);
-        fprintf(stderr, "[wm_b200] forward pipeline: %d block(s) per SM, %zu bytes of shared memory\n", blocks, smem);
-      }
-      return v ? atoi(v) : 0;
-    }();
-    attn_fwd_tc2_kernel<<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, a, next_epoch(), dbg);
+  const size_t smem = sizeof(FwdShared) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    configured = true;
   }
+  attn_fwd_tc_kernel<<<grid, kFwdThreads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
   count_launch();
   return cuda_check(cudaGetLastError(), "attn_fwd_tc_kernel");
 }
@@ -331,11 +286,7 @@ bool tc_bwd_supported(const wm_attn_args& a) {
 
 // The short-query pipeline keeps both query tiles of a (batch, head) resident.
 bool bwd_short_queries(const wm_attn_args& a) {
-  static const bool disabled = [] {
-    const char* v = getenv("WM_B200_BWD_PIPELINE");  // "1": always the key-stationary pipeline (bring-up aid)
-    return v != nullptr && v[0] == '1';
-  }();
-  return !disabled && a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
+  return a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
 }
 
 size_t tc_attn_bwd_workspace(const wm_attn_args& a) {
@@ -364,35 +315,19 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
   count_launch();
   WM_CUDA(cudaGetLastError());
   if (bwd_short_queries(a)) {
-    const size_t smem2 = sizeof(Bwd2Shared) + 1024;
-    static bool configured2 = false;
-    if (!configured2) {
-      WM_CUDA(cudaFuncSetAttribute(attn_bwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
-      configured2 = true;
+    const size_t smem_r = sizeof(ResidentShared) + 1024;
+    static bool configured_r = false;
+    if (!configured_r) {
+      WM_CUDA(cudaFuncSetAttribute(attn_bwd_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_r)));
+      configured_r = true;
     }
-    // WM_B200_BWD_PIPELINE=2 keeps the non-overlapped resident-query pipeline (bring-up aid)
-    static const bool overlapped = [] {
-      const char* v = getenv("WM_B200_BWD_PIPELINE");
-      return !(v != nullptr && v[0] == '2');
-    }();
-    if (overlapped) {
-      const size_t smem3 = sizeof(Bwd3Shared) + 1024;
-      static bool configured3 = false;
-      if (!configured3) {
-        WM_CUDA(cudaFuncSetAttribute(attn_bwd_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem3)));
-        configured3 = true;
-      }
-      CUtensorMap map_dk, map_dv;
-      status = make_map(&map_dk, a.dk, a.batch, a.kv_heads, a.k_len, a.dk_strides, kTileN);
-      if (status != WM_OK) return status;
-      status = make_map(&map_dv, a.dv, a.batch, a.kv_heads, a.k_len, a.dv_strides, kTileN);
-      if (status != WM_OK) return status;
-      attn_bwd_tc3_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem3, stream>>>(map_q, map_k, map_v, map_g, map_dk,
-                                                                                     map_dv, a, delta, next_epoch());
-    } else {
-      attn_bwd_tc2_kernel<<<dim3(a.q_heads, a.batch), kBwd2Threads, smem2, stream>>>(map_q, map_k, map_v, map_g, a, delta,
-                                                                                     next_epoch());
-    }
+    CUtensorMap map_dk, map_dv;
+    status = make_map(&map_dk, a.dk, a.batch, a.kv_heads, a.k_len, a.dk_strides, kTileN);
+    if (status != WM_OK) return status;
+    status = make_map(&map_dv, a.dv, a.batch, a.kv_heads, a.k_len, a.dv_strides, kTileN);
+    if (status != WM_OK) return status;
+    attn_bwd_resident_kernel<<<dim3(a.q_heads, a.batch), kResidentThreads, smem_r, stream>>>(map_q, map_k, map_v, map_g, map_dk,
+                                                                                   map_dv, a, delta, next_epoch());
     count_launch();
     return cuda_check(cudaGetLastError(), "attention backward (tcgen05, resident queries)");
   }

@@ -1,18 +1,103 @@
-// Backward pipeline for short query axes with the tensor cores and the compute warps overlapped
-// (included by attn_tc.cu; same residency idea and TMEM map as attn_tc_bwd2.cuh).
+// Backward pipeline for short query axes (included by attn_tc.cu).
+//
+// Cyclic attention with stride S has S times fewer queries than keys.  When a (batch, head) has
+// at most 256 queries and query heads are not grouped, one block keeps both query tiles (Q, dO:
+// 64 KB) and their dQ accumulators (TMEM) resident and walks over the key tiles: dK and dV of a
+// key tile are complete inside the block and leave through one TMA store each, dQ is written
+// once at the end -- no atomics, no fp32 scratch, no conversion pass.  K and V tiles stream
+// through a two-stage TMA ring.
+//
+// 320 threads: warps 0-7 compute (thread = query row (tid & 127), column half (tid >> 7) of the
+// 128-key tile), warp 8 TMA producer, warp 9 MMA issuer.
+// TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ0 [384,448) dQ1 [448,512).
 //
 // An iteration is one (key tile, query tile) pair; the list of visible pairs is built once per
 // block.  The compute warps pull S and dP of iteration i out of TMEM into registers and release
 // them at once (sdp_free), so the MMA warp issues S/dP of iteration i+1 while the exponentials of
 // iteration i are still being computed; P and dS of iteration i are written to shared memory only
-// after the dV/dK/dQ products of iteration i-1 have read the previous contents (mma_done), which by
-// then have had a whole math phase to complete.  dK/dV of a finished key tile are stored by the
-// compute warps just before they publish the first P/dS of the next key tile.
+// after the dV/dK/dQ products of iteration i-1 have read the previous contents (mma_done).
 #pragma once
 
-constexpr int kBwd3MaxIter = 256;
+constexpr int kResidentThreads = 320;
+constexpr int kResidentCompute = 256;
 
-struct Bwd3Shared {
+
+struct ResidentWalk {
+  int nq;      // query tiles (1 or 2)
+  int n_kt;    // key tiles of the tensor
+  int lo_min[2], hi_max[2];
+  int kvis;    // exclusive bound of the key slots any query can see
+  bool docs;
+  bool dummy;
+};
+
+__device__ __forceinline__ bool pair_visible(const ResidentWalk& w, int kt, int qt) {
+  if (qt >= w.nq) return false;
+  const int j0 = kt * kTileN;
+  if (j0 >= w.hi_max[qt]) return false;
+  if (w.docs && j0 + kTileN - 1 < w.lo_min[qt] && !(w.dummy && kt == 0)) return false;
+  return true;
+}
+
+template <class Shared>
+__device__ __forceinline__ void resident_producer(Shared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
+                                              const CUtensorMap* map_v, const CUtensorMap* map_g, const ResidentWalk& w,
+                                              int head, int batch) {
+  ptx::prefetch_tmap(map_q);
+  ptx::prefetch_tmap(map_k);
+  ptx::prefetch_tmap(map_v);
+  ptx::prefetch_tmap(map_g);
+  ptx::mbar_expect_tx(&sm.qg_full, 2 * w.nq * kTileBytes);
+  for (int qt = 0; qt < w.nq; ++qt) {
+    ptx::tma_load_4d(sm.q[qt], map_q, &sm.qg_full, 0, qt * kTileM, head, batch);
+    ptx::tma_load_4d(sm.g[qt], map_g, &sm.qg_full, 0, qt * kTileM, head, batch);
+  }
+  int active = 0;
+  for (int kt = 0; kt < w.n_kt; ++kt) {
+    if (!pair_visible(w, kt, 0) && !pair_visible(w, kt, 1)) continue;
+    const int s = active & 1;
+    if (!wait_or_abort(sm, &sm.kv_empty[s], ((active >> 1) & 1) ^ 1, 71)) return;
+    ptx::mbar_expect_tx(&sm.kv_full[s], 2 * kTileBytes);
+    ptx::tma_load_4d(sm.k[s], map_k, &sm.kv_full[s], 0, kt * kTileN, head, batch);
+    ptx::tma_load_4d(sm.v[s], map_v, &sm.kv_full[s], 0, kt * kTileN, head, batch);
+    ++active;
+  }
+}
+
+// dV (half 0) or dK (half 1) rows of key tile `kt`: TMEM -> bf16 -> global, one key row per thread
+__device__ __forceinline__ void resident_store_dkv(const wm_attn_args& a, uint32_t tmem, int kt, int row, int half,
+                                               uint32_t lane_base, int head, int batch, bool zero) {
+  const int j = kt * kTileN + row;
+  uint32_t packed[kHeadDim / 2];
+  const float s = half ? a.scale : 1.f;
+  uint32_t raw[kHeadDim / 32][32];
+  if (!zero) {
+#pragma unroll
+    for (int c = 0; c < kHeadDim / 32; ++c)
+      ptx::tmem_ld32(tmem + 2 * kTileN + half * kHeadDim + lane_base + c * 32, raw[c]);
+    ptx::tmem_wait_ld();
+  }
+#pragma unroll
+  for (int c = 0; c < kHeadDim / 32; ++c) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e)
+      packed[c * 16 + e] =
+          zero ? 0u : pack_bf16(__uint_as_float(raw[c][2 * e]) * s, __uint_as_float(raw[c][2 * e + 1]) * s);
+  }
+  if (j < a.k_len) {
+    const int64_t* st = half ? a.dk_strides : a.dv_strides;
+    __nv_bfloat16* base = static_cast<__nv_bfloat16*>(half ? a.dk : a.dv);
+    uint4* dst = reinterpret_cast<uint4*>(base + batch * st[0] + head * st[1] + static_cast<long long>(j) * st[2]);
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+  }
+}
+
+
+constexpr int kResidentMaxIter = 256;
+
+struct ResidentShared {
   unsigned char q[2][kTileBytes];
   unsigned char g[2][kTileBytes];  // dO
   unsigned char k[2][kTileBytes];
@@ -29,7 +114,7 @@ struct Bwd3Shared {
   int lo_min[2], hi_max[2];
   int has_dummy;
   // iteration list: key tile | query tile << 12 | first-of-key-tile << 13 | last-of-key-tile << 14 | visited index << 16
-  uint32_t sched[kBwd3MaxIter];
+  uint32_t sched[kResidentMaxIter];
   int n_iter;
   uint32_t tmem_base;
   int abort_flag;
@@ -38,12 +123,12 @@ struct Bwd3Shared {
   long long trace[kTraceSlots];
 };
 
-struct Bwd3Iter {
+struct ResidentIter {
   int kt, qt, first, last, active;
 };
 
-__device__ __forceinline__ Bwd3Iter bwd3_iter(uint32_t e) {
-  Bwd3Iter it;
+__device__ __forceinline__ ResidentIter resident_iter(uint32_t e) {
+  ResidentIter it;
   it.kt = e & 0xfff;
   it.qt = (e >> 12) & 1;
   it.first = (e >> 13) & 1;
@@ -52,7 +137,7 @@ __device__ __forceinline__ Bwd3Iter bwd3_iter(uint32_t e) {
   return it;
 }
 
-__device__ __forceinline__ void bwd3_issue_sdp(Bwd3Shared& sm, uint32_t tmem, const Bwd3Iter& e) {
+__device__ __forceinline__ void resident_issue_sdp(ResidentShared& sm, uint32_t tmem, const ResidentIter& e) {
   constexpr uint32_t idesc_s = ptx::make_idesc_bf16(kTileM, kTileN, 0, 0);
   const int s = e.active & 1;
   const uint32_t q_base = ptx::smem_u32(sm.q[e.qt]), g_base = ptx::smem_u32(sm.g[e.qt]);
@@ -68,7 +153,7 @@ __device__ __forceinline__ void bwd3_issue_sdp(Bwd3Shared& sm, uint32_t tmem, co
   ptx::mma_commit(&sm.sdp_full);
 }
 
-__device__ __forceinline__ void bwd3_mma(Bwd3Shared& sm, uint32_t tmem) {
+__device__ __forceinline__ void resident_mma(ResidentShared& sm, uint32_t tmem) {
   const int n = sm.n_iter;
   if (n == 0) return;
   if (!wait_or_abort(sm, &sm.qg_full, 0, 80)) return;
@@ -76,19 +161,19 @@ __device__ __forceinline__ void bwd3_mma(Bwd3Shared& sm, uint32_t tmem) {
   constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);
   const uint32_t p_base = ptx::smem_u32(sm.p), ds_base = ptx::smem_u32(sm.ds);
   bool dq_started[2] = {false, false};
-  Bwd3Iter e = bwd3_iter(sm.sched[0]);
+  ResidentIter e = resident_iter(sm.sched[0]);
   if (!wait_or_abort(sm, &sm.kv_ready[e.active & 1], (e.active >> 1) & 1, 81)) return;
   ptx::tc_fence_after();
-  bwd3_issue_sdp(sm, tmem, e);
+  resident_issue_sdp(sm, tmem, e);
   for (int it = 0; it < n; ++it) {
     // S/dP of this iteration are in the compute warps' registers: the next pair may overwrite them
     if (!wait_or_abort(sm, &sm.sdp_free, it & 1, 83)) return;
     ptx::tc_fence_after();
     if (it + 1 < n) {
-      const Bwd3Iter nx = bwd3_iter(sm.sched[it + 1]);
+      const ResidentIter nx = resident_iter(sm.sched[it + 1]);
       if (nx.first && !wait_or_abort(sm, &sm.kv_ready[nx.active & 1], (nx.active >> 1) & 1, 81)) return;
       ptx::tc_fence_after();
-      bwd3_issue_sdp(sm, tmem, nx);
+      resident_issue_sdp(sm, tmem, nx);
     }
     if (!wait_or_abort(sm, &sm.pds_full, it & 1, 82)) return;
     ptx::tc_fence_after();
@@ -112,11 +197,11 @@ __device__ __forceinline__ void bwd3_mma(Bwd3Shared& sm, uint32_t tmem) {
                        ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, acc_q || (kk > 0));
     if (e.qt) dq_started[1] = true; else dq_started[0] = true;
     ptx::mma_commit(&sm.mma_done);
-    if (it + 1 < n) e = bwd3_iter(sm.sched[it + 1]);
+    if (it + 1 < n) e = resident_iter(sm.sched[it + 1]);
   }
 }
 
-__device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args& a, uint32_t tmem, const Bwd2Walk& w,
+__device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_attn_args& a, uint32_t tmem, const ResidentWalk& w,
                                              const float* delta, int head, int batch, const CUtensorMap* map_dk,
                                              const CUtensorMap* map_dv) {
   const int tid = threadIdx.x;
@@ -157,11 +242,11 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
 
   // key tiles nobody sees get exact zeros; they are not part of the iteration list
   for (int kt = 0; kt < w.n_kt; ++kt)
-    if (!pair_visible(w, kt, 0) && !pair_visible(w, kt, 1)) bwd2_store_dkv(a, tmem, kt, row, half, lane_base, head, batch, true);
+    if (!pair_visible(w, kt, 0) && !pair_visible(w, kt, 1)) resident_store_dkv(a, tmem, kt, row, half, lane_base, head, batch, true);
 
   // Make a visited key tile ready for the MMAs: publish its document table, clear rows beyond the last visible
   // slot (they may hold anything), and meet the other compute threads at kv_ready.
-  auto prepare = [&](const Bwd3Iter& e) -> bool {
+  auto prepare = [&](const ResidentIter& e) -> bool {
     const int s = e.active & 1;
     const int j0 = e.kt * kTileN;
     if (w.docs && half == 0) {
@@ -236,10 +321,10 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
     return true;
   };
 
-  if (n > 0 && !prepare(bwd3_iter(sm.sched[0]))) return;
+  if (n > 0 && !prepare(resident_iter(sm.sched[0]))) return;
   int pending_kt = -1, pending_stage = 0;
   for (int it = 0; it < n; ++it) {
-    const Bwd3Iter e = bwd3_iter(sm.sched[it]);
+    const ResidentIter e = resident_iter(sm.sched[it]);
     const int s = e.active & 1;
     const int j0 = e.kt * kTileN;
     const RowBound& r = e.qt ? rb1 : rb0;
@@ -265,33 +350,33 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
     if (tid == 0) trace_event(sm, 500 + it);
     // Two rounds of 32 columns keep the register footprint small: scores of round 0 are turned into P / dS
     // while the loads of round 1 are in flight; S/dP are released to the MMA warp as soon as round 1 has landed.
+    // Visibility of 32 columns as one bit mask: arithmetic for the causal bound, a short loop over the key table
+    // for tiles that contain a document boundary.  One copy of the math serves every tile class.
     const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
-    auto math = [&](const uint32_t (&xs)[32], const uint32_t (&ys)[32], int col0, uint32_t (&pp)[16], uint32_t (&dd)[16]) {
-      if (cls != kTileDocs) {
-#pragma unroll
-        for (int e2 = 0; e2 < 16; ++e2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2]), sl2, nl));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2 + 1]), sl2, nl));
-          const bool v0 = col0 + 2 * e2 < lim_eff, v1 = col0 + 2 * e2 + 1 < lim_eff;
-          pp[e2] = pack_bf16(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
-          dd[e2] = pack_bf16(v0 ? p0 * (__uint_as_float(ys[2 * e2]) - dlt) : 0.f,
-                             v1 ? p1 * (__uint_as_float(ys[2 * e2 + 1]) - dlt) : 0.f);
+    auto visible_mask = [&](int col0) -> uint32_t {
+      const int left = lim_eff - col0;
+      uint32_t mask = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
+      if (cls == kTileDocs && mask != 0u) {
+        uint32_t docs_mask = 0u;
+#pragma unroll 1
+        for (int e2 = 0; e2 < 32; ++e2) {
+          const int col = col0 + e2;
+          docs_mask |= static_cast<uint32_t>(doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col])) << e2;
         }
-      } else {
+        mask &= docs_mask;
+      }
+      return mask;
+    };
+    auto math = [&](const uint32_t (&xs)[32], const uint32_t (&ys)[32], uint32_t mask, uint32_t (&pp)[16],
+                    uint32_t (&dd)[16]) {
 #pragma unroll
-        for (int e2 = 0; e2 < 16; ++e2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = col0 + 2 * e2 + u;
-            const bool vis = (col < lim) & doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col]);
-            const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e2 + u]), sl2, nl));
-            pv[u] = vis ? p : 0.f;
-            dv[u] = vis ? p * (__uint_as_float(ys[2 * e2 + u]) - dlt) : 0.f;
-          }
-          pp[e2] = pack_bf16(pv[0], pv[1]);
-          dd[e2] = pack_bf16(dv[0], dv[1]);
-        }
+      for (int e2 = 0; e2 < 16; ++e2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2]), sl2, nl));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2 + 1]), sl2, nl));
+        const bool v0 = (mask >> (2 * e2)) & 1u, v1 = (mask >> (2 * e2 + 1)) & 1u;
+        pp[e2] = pack_bf16(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
+        dd[e2] = pack_bf16(v0 ? p0 * (__uint_as_float(ys[2 * e2]) - dlt) : 0.f,
+                           v1 ? p1 * (__uint_as_float(ys[2 * e2 + 1]) - dlt) : 0.f);
       }
     };
     auto store = [&](int c, const uint32_t (&pp)[16], const uint32_t (&dd)[16]) {
@@ -303,37 +388,37 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
       }
     };
     {
-      uint32_t xs[32], ys[32], pp[16], dd[16];
+      uint32_t xs[32], ys[32], pp0[16], dd0[16], pp1[16], dd1[16];
       ptx::tmem_ld32(tmem + lane_base + half * 64, xs);
       ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64, ys);
       ptx::tmem_wait_ld();
-      math(xs, ys, half * 64, pp, dd);
-      // round 1 loads go out now; they land while round 0 is stored
+      math(xs, ys, visible_mask(half * 64), pp0, dd0);
       ptx::tmem_ld32(tmem + lane_base + half * 64 + 32, xs);
       ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64 + 32, ys);
-      if (tid == 0) trace_event(sm, 900 + it);
-      // the shared P / dS tiles are read by the products of the previous iteration until mma_done
-      if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;
-      ptx::tc_fence_after();
-      store(0, pp, dd);
       ptx::tmem_wait_ld();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&sm.sdp_free);  // all scores are in registers: S/dP of the next pair may be issued
       if (tid == 0) trace_event(sm, 800 + it);
-      // hand over a finished key tile (gradients and shared-memory stage), then prepare the next one
-      if (pending_kt >= 0) {
-        if (!stage_out(pending_kt, pending_stage, e.last)) return;
-        pending_kt = -1;
-      }
-      if (e.last && it + 1 < n && !prepare(bwd3_iter(sm.sched[it + 1]))) return;
-      math(xs, ys, half * 64 + 32, pp, dd);
-      store(1, pp, dd);
+      math(xs, ys, visible_mask(half * 64 + 32), pp1, dd1);
+      if (tid == 0) trace_event(sm, 900 + it);
+      // the shared P / dS tiles are read by the products of the previous iteration until mma_done
+      if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;
+      ptx::tc_fence_after();
+      store(0, pp0, dd0);
+      store(1, pp1, dd1);
+    }
+    // dV / dK of a finished key tile leave TMEM before this iteration's products (which restart the accumulators)
+    // can be issued, i.e. before pds_full; the shared-memory stage is released and the next tile prepared after it
+    if (pending_kt >= 0) {
+      if (!stage_out(pending_kt, pending_stage, false)) return;
+      pending_kt = -1;
     }
     ptx::fence_async_shared();
     ptx::tc_fence_before();
     ptx::mbar_arrive(&sm.pds_full);
     if (tid == 0) trace_event(sm, 1000 + it);
     release();
+    if (e.last && it + 1 < n && !prepare(resident_iter(sm.sched[it + 1]))) return;
     if (e.last) {
       pending_kt = e.kt;
       pending_stage = s;
@@ -378,13 +463,13 @@ __device__ __forceinline__ void bwd3_compute(Bwd3Shared& sm, const wm_attn_args&
 }
 
 
-__global__ void __launch_bounds__(kBwd2Threads, 1)
-    attn_bwd_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(kResidentThreads, 1)
+    attn_bwd_resident_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_g,
                         const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
                         const wm_attn_args a, const float* delta, const int epoch) {
   extern __shared__ unsigned char smem_raw[];
-  Bwd3Shared& sm = *reinterpret_cast<Bwd3Shared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  ResidentShared& sm = *reinterpret_cast<ResidentShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.x;
@@ -400,7 +485,7 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
     sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
   }
   __syncthreads();
-  if (tid < kBwd2Compute) {
+  if (tid < kResidentCompute) {
     const int qt = tid >> 7;
     int lo = INT_MAX, hi = 0;
     if (tid < a.q_len) {
@@ -416,7 +501,7 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
     }
   }
   __syncthreads();
-  Bwd2Walk w;
+  ResidentWalk w;
   w.nq = (a.q_len + kTileM - 1) / kTileM;
   w.n_kt = (a.k_len + kTileN - 1) / kTileN;
   w.lo_min[0] = sm.lo_min[0];
@@ -440,13 +525,13 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
     ptx::mbar_init(&sm.qg_full, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&sm.kv_full[s], 1);
-      ptx::mbar_init(&sm.kv_ready[s], kBwd2Compute);
+      ptx::mbar_init(&sm.kv_ready[s], kResidentCompute);
       ptx::mbar_init(&sm.kv_empty[s], 2);  // the two halves' store threads release a stage
       ptx::mbar_init(&sm.out_full[s], kTileM);
     }
     ptx::mbar_init(&sm.sdp_full, 1);
-    ptx::mbar_init(&sm.sdp_free, kBwd2Compute);
-    ptx::mbar_init(&sm.pds_full, kBwd2Compute);
+    ptx::mbar_init(&sm.sdp_free, kResidentCompute);
+    ptx::mbar_init(&sm.pds_full, kResidentCompute);
     ptx::mbar_init(&sm.mma_done, 1);
     ptx::mbar_fence_init();
   }
@@ -459,11 +544,11 @@ __global__ void __launch_bounds__(kBwd2Threads, 1)
   ptx::tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   if (warp < 8) {
-    bwd3_compute(sm, a, tmem, w, delta, head, batch, &map_dk, &map_dv);
+    resident_compute(sm, a, tmem, w, delta, head, batch, &map_dk, &map_dv);
   } else if (warp == 8) {
-    if (lane == 0) bwd2_producer(sm, &map_q, &map_k, &map_v, &map_g, w, head, batch);
+    if (lane == 0) resident_producer(sm, &map_q, &map_k, &map_v, &map_g, w, head, batch);
   } else {
-    if (lane == 0) bwd3_mma(sm, tmem);
+    if (lane == 0) resident_mma(sm, tmem);
   }
   ptx::tma_store_wait_all();
   ptx::tc_fence_before();
