@@ -52,30 +52,37 @@ __device__ int g_trace_epoch = -1;
 
 constexpr int kTraceSlots = 1024;
 
-// Events go to shared memory (cheap) and are copied out when the block ends.
+// Events go to shared memory and are copied out when the block ends.  Every warp has its own region of 64 slots
+// (one thread per warp records), so that recording needs no atomic.
 template <class Shared>
 __device__ __forceinline__ void trace_event(Shared& sm, int tag) {
   if (sm.trace_on) {
-    const int i = atomicAdd(&sm.trace_n, 1);
-    if (i < kTraceSlots) sm.trace[i] = (clock64() << 16) | static_cast<long long>(tag & 0xffff);
+    const int r = (threadIdx.x >> 5) & 15;
+    const int i = sm.trace_cnt[r];
+    if (i < 64) {
+      sm.trace[r * 64 + i] = (clock64() << 16) | static_cast<long long>(tag & 0xffff);
+      sm.trace_cnt[r] = i + 1;
+    }
   }
 }
 
 template <class Shared>
 __device__ __forceinline__ void trace_begin(Shared& sm, int epoch) {
-  sm.trace_n = 0;
+  for (int r = 0; r < 16; ++r) sm.trace_cnt[r] = 0;
   sm.trace_on = epoch == g_trace_epoch && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 }
 
 template <class Shared>
 __device__ __forceinline__ void trace_flush(Shared& sm) {
-  if (sm.trace_on) {
-    const int n = min(sm.trace_n, kTraceSlots);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      g_trace[2 * i] = sm.trace[i] & 0xffff;
-      g_trace[2 * i + 1] = sm.trace[i] >> 16;
-    }
-    if (threadIdx.x == 0) g_trace_count = n;
+  if (sm.trace_on && threadIdx.x == 0) {
+    int n = 0;
+    for (int r = 0; r < 16; ++r)
+      for (int i = 0; i < sm.trace_cnt[r] && i < 64; ++i) {
+        g_trace[2 * n] = sm.trace[r * 64 + i] & 0xffff;
+        g_trace[2 * n + 1] = sm.trace[r * 64 + i] >> 16;
+        ++n;
+      }
+    g_trace_count = n;
   }
 }
 
@@ -230,7 +237,7 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
   if (status != WM_OK) return status;
   status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN);
   if (status != WM_OK) return status;
-  dim3 grid((a.q_len + kTileM - 1) / kTileM, a.q_heads, a.batch);
+  dim3 grid(a.q_heads, a.batch, (a.q_len + kTileM - 1) / kTileM);
   const size_t smem = sizeof(FwdShared) + 1024;
   static bool configured = false;
   if (!configured) {

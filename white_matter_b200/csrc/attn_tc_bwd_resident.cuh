@@ -119,7 +119,7 @@ struct ResidentShared {
   uint32_t tmem_base;
   int abort_flag;
   int epoch;
-  int trace_on, trace_n;
+  int trace_on, trace_cnt[16];
   long long trace[kTraceSlots];
 };
 
