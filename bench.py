@@ -37,6 +37,14 @@ if str(ROOT) not in sys.path:
 B, H, T, D, STRIDE = 16, 16, 2048, 64, 8
 DOC_MEAN = 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels on exactly these
+# workloads, from the ncu captures summarised under profiles/ (one capture each; the bench cannot run ncu itself).
+NCU_TRAFFIC_BYTES = {
+    "attn_bwd_resident_kernel": 249.7e6,
+    "attn_fwd_tc_kernel": 186.0e6,
+    "decode_split_kernel": 1086.4e6,
+    "mix_fwd_kernel": 432.8e6,
+}
 
 
 def load_peaks():
@@ -297,7 +305,7 @@ def bench_decode(device, peaks, iters=20):
         "workload": "strict decode B=64 H=16 D=64 lengths~U[1,8192] bf16 (pool 2.15 GB > L2)",
         "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["decode_split_kernel"]},
     }
 
 
@@ -315,7 +323,7 @@ def bench_mixing(device, peaks, iters=10):
         "workload": "mix 25 sources (25,4,16,2048,64) bf16, 419 MB read + 17 MB written",
         "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["mix_fwd_kernel"]},
     }
 
 
@@ -491,10 +499,12 @@ def main():
                     "d2h_bytes_per_step": sets[0].staging_bytes()[1]},
             "roofline": {"bound": "tensor", "kernel": "backward kernels of one residue call (attn_bwd_resident_kernel + bwd_delta_kernel)",
                          "achieved": bwd_tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": bwd_tf / tensor_peak,
-                         "traffic": None, "peak_kind": f"{peak_kind} bf16_tflops_sustained", "ms": bwd_ms},
+                         "traffic": NCU_TRAFFIC_BYTES["attn_bwd_resident_kernel"] if args.backend != "sm100_simt" else None, "peak_kind": f"{peak_kind} bf16_tflops_sustained", "ms": bwd_ms},
             "roofline_forward": {"bound": "tensor", "kernel": "attn_fwd_tc_kernel, one residue call",
                                  "achieved": fwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
-                                 "frac": fwd_tf / tensor_peak, "traffic": None, "ms": fwd_ms},
+                                 "frac": fwd_tf / tensor_peak,
+                                 "traffic": NCU_TRAFFIC_BYTES["attn_fwd_tc_kernel"] if args.backend != "sm100_simt" else None,
+                                 "ms": fwd_ms},
         }
         line.update(extras)
         if world == 1 and not args.skip_extras:

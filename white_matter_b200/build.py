@@ -2,7 +2,9 @@
 
 ``python -m white_matter_b200.build`` compiles every ``csrc/*.cu`` to an object
 file (in parallel) and links them into ``white_matter_b200/libwm_b200.so``.
-Objects are rebuilt only when their source or a header is newer.
+Objects are rebuilt only when their source or a header is newer.  ``--trace``
+adds the pipeline event trace of the tcgen05 kernels (a developer build; rebuild
+without the flag and with ``-f`` afterwards).
 """
 
 from __future__ import annotations
@@ -48,8 +50,9 @@ def _newest_header() -> float:
     return max(h.stat().st_mtime for h in headers)
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile and link; returns the library path."""
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, trace: bool = False) -> Path:
+    """Compile and link; returns the library path.  ``trace`` builds the pipeline event trace in (see wm_debug_trace)."""
+    force = force or trace
     nvcc = _nvcc()
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
@@ -62,6 +65,8 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
             cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
+            if trace:
+                cmd[1:1] = ["-DWM_B200_TRACE"]
             jobs.append(cmd)
 
     def run(cmd):
@@ -87,5 +92,5 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
 
 
 if __name__ == "__main__":
-    path = build(verbose="-v" in sys.argv, force="-f" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    path = build(verbose="-v" in sys.argv, force="-f" in sys.argv, ptxas_info="--ptxas" in sys.argv, trace="--trace" in sys.argv)
     print(path)

@@ -115,7 +115,7 @@ int wm_abi_version(void) { return WM_B200_ABI_VERSION; }
 
 const char* wm_last_error(void) { return wm::g_error; }
 
-__attribute__((visibility("default"))) int wm_debug_trace(long long* out, int capacity, int arm_after) {
+int wm_debug_trace(long long* out, int capacity, int arm_after) {
   return wm::tc_debug_trace(out, capacity, arm_after);
 }
 

@@ -45,22 +45,25 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units
 __device__ int g_status = 0;       // first failure code since the last reset
 __device__ int g_abort_epoch = 0;  // launch number whose blocks should stop waiting
 
-// Bring-up trace: (tag, clock) pairs recorded by block (0,0,0) of launches whose epoch equals g_trace_epoch.
+// Pipeline trace (builds with -DWM_B200_TRACE only): block (0,0,0) of the launch whose number equals g_trace_epoch
+// records (tag, clock) pairs in shared memory and copies them out when it ends.  Every warp has its own region of
+// 128 slots (one thread per warp records), so that recording needs no atomic.
+#ifdef WM_B200_TRACE
 __device__ long long g_trace[2 * 4096];
 __device__ int g_trace_count = 0;
 __device__ int g_trace_epoch = -1;
+constexpr int kTraceSlots = 2048;
+#define WM_TRACE_FIELDS \
+  int trace_on, trace_cnt[16]; \
+  long long trace[kTraceSlots];
 
-constexpr int kTraceSlots = 1024;
-
-// Events go to shared memory and are copied out when the block ends.  Every warp has its own region of 64 slots
-// (one thread per warp records), so that recording needs no atomic.
 template <class Shared>
 __device__ __forceinline__ void trace_event(Shared& sm, int tag) {
   if (sm.trace_on) {
     const int r = (threadIdx.x >> 5) & 15;
     const int i = sm.trace_cnt[r];
-    if (i < 64) {
-      sm.trace[r * 64 + i] = (clock64() << 16) | static_cast<long long>(tag & 0xffff);
+    if (i < 128) {
+      sm.trace[r * 128 + i] = (clock64() << 16) | static_cast<long long>(tag & 0xffff);
       sm.trace_cnt[r] = i + 1;
     }
   }
@@ -77,15 +80,23 @@ __device__ __forceinline__ void trace_flush(Shared& sm) {
   if (sm.trace_on && threadIdx.x == 0) {
     int n = 0;
     for (int r = 0; r < 16; ++r)
-      for (int i = 0; i < sm.trace_cnt[r] && i < 64; ++i) {
-        g_trace[2 * n] = sm.trace[r * 64 + i] & 0xffff;
-        g_trace[2 * n + 1] = sm.trace[r * 64 + i] >> 16;
+      for (int i = 0; i < sm.trace_cnt[r] && i < 128; ++i) {
+        g_trace[2 * n] = sm.trace[r * 128 + i] & 0xffff;
+        g_trace[2 * n + 1] = sm.trace[r * 128 + i] >> 16;
         ++n;
       }
     g_trace_count = n;
   }
 }
-
+#else
+#define WM_TRACE_FIELDS
+template <class Shared>
+__device__ __forceinline__ void trace_event(Shared&, int) {}
+template <class Shared>
+__device__ __forceinline__ void trace_begin(Shared&, int) {}
+template <class Shared>
+__device__ __forceinline__ void trace_flush(Shared&) {}
+#endif
 
 template <class Shared>
 __device__ __forceinline__ void record_failure(Shared& sm, int code) {
@@ -249,8 +260,10 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
   return cuda_check(cudaGetLastError(), "attn_fwd_tc_kernel");
 }
 
-// Arms the trace for the launch after the next `skip` launches and fetches what was recorded so far.
+// Arms the trace for the launch after the next `arm_after` launches (negative: disarm) and fetches what was
+// recorded so far as (tag, clock) pairs; 0 in builds without -DWM_B200_TRACE.
 int tc_debug_trace(long long* out, int capacity, int arm_after) {
+#ifdef WM_B200_TRACE
   int count = 0;
   cudaDeviceSynchronize();
   cudaMemcpyFromSymbol(&count, g_trace_count, sizeof(int));
@@ -262,6 +275,12 @@ int tc_debug_trace(long long* out, int capacity, int arm_after) {
   int target = arm_after < 0 ? -1 : next_epoch() + 1 + arm_after;
   cudaMemcpyToSymbol(g_trace_epoch, &target, sizeof(int));
   return count;
+#else
+  (void)out;
+  (void)capacity;
+  (void)arm_after;
+  return 0;
+#endif
 }
 
 int tc_device_status(bool reset) {

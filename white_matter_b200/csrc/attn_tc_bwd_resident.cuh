@@ -119,8 +119,7 @@ struct ResidentShared {
   uint32_t tmem_base;
   int abort_flag;
   int epoch;
-  int trace_on, trace_cnt[16];
-  long long trace[kTraceSlots];
+  WM_TRACE_FIELDS
 };
 
 struct ResidentIter {
@@ -169,14 +168,17 @@ __device__ __forceinline__ void resident_mma(ResidentShared& sm, uint32_t tmem) 
     // S/dP of this iteration are in the compute warps' registers: the next pair may overwrite them
     if (!wait_or_abort(sm, &sm.sdp_free, it & 1, 83)) return;
     ptx::tc_fence_after();
+    trace_event(sm, 100 + it);
     if (it + 1 < n) {
       const ResidentIter nx = resident_iter(sm.sched[it + 1]);
       if (nx.first && !wait_or_abort(sm, &sm.kv_ready[nx.active & 1], (nx.active >> 1) & 1, 81)) return;
       ptx::tc_fence_after();
       resident_issue_sdp(sm, tmem, nx);
+      trace_event(sm, 200 + it);
     }
     if (!wait_or_abort(sm, &sm.pds_full, it & 1, 82)) return;
     ptx::tc_fence_after();
+    trace_event(sm, 300 + it);
     const int s = e.active & 1;
     const uint32_t q_base = ptx::smem_u32(sm.q[e.qt]), g_base = ptx::smem_u32(sm.g[e.qt]);
     const uint32_t k_base = ptx::smem_u32(sm.k[s]);
@@ -197,6 +199,7 @@ __device__ __forceinline__ void resident_mma(ResidentShared& sm, uint32_t tmem) 
                        ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, acc_q || (kk > 0));
     if (e.qt) dq_started[1] = true; else dq_started[0] = true;
     ptx::mma_commit(&sm.mma_done);
+    trace_event(sm, 400 + it);
     if (it + 1 < n) e = resident_iter(sm.sched[it + 1]);
   }
 }
@@ -404,6 +407,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
       // the shared P / dS tiles are read by the products of the previous iteration until mma_done
       if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;
       ptx::tc_fence_after();
+      if (tid == 0) trace_event(sm, 600 + it);
       store(0, pp0, dd0);
       store(1, pp1, dd1);
     }

@@ -121,8 +121,7 @@ struct FwdShared {
   uint32_t tmem_base;
   int abort_flag;
   int epoch;
-  int trace_on, trace_cnt[16];
-  long long trace[kTraceSlots];
+  WM_TRACE_FIELDS
 };
 
 // One softmax group (128 threads, thread = query row = TMEM lane) owns the key tiles of one parity: it keeps its
