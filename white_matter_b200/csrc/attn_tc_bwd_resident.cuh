@@ -7,8 +7,8 @@
 // once at the end -- no atomics, no fp32 scratch, no conversion pass.  K and V tiles stream
 // through a two-stage TMA ring.
 //
-// 320 threads: warps 0-7 compute (thread = query row (tid & 127), column half (tid >> 7) of the
-// 128-key tile), warp 8 TMA producer, warp 9 MMA issuer.
+// 352 threads: warps 0-7 compute (thread = query row (tid & 127), column half (tid >> 7) of the
+// 128-key tile), warp 8 TMA producer, warps 9 and 10 MMA issuers (S/dP products, gradient products).
 // TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ0 [384,448) dQ1 [448,512).
 //
 // An iteration is one (key tile, query tile) pair; the list of visible pairs is built once per
@@ -18,7 +18,7 @@
 // after the dV/dK/dQ products of iteration i-1 have read the previous contents (mma_done).
 #pragma once
 
-constexpr int kResidentThreads = 320;
+constexpr int kResidentThreads = 352;
 constexpr int kResidentCompute = 256;
 
 
@@ -152,30 +152,36 @@ __device__ __forceinline__ void resident_issue_sdp(ResidentShared& sm, uint32_t 
   ptx::mma_commit(&sm.sdp_full);
 }
 
-__device__ __forceinline__ void resident_mma(ResidentShared& sm, uint32_t tmem) {
+// Two issuing threads, because the tensor pipe takes an instruction only when it has started the previous one and
+// the issuing thread is busy for as long as its products run: one thread issues the S / dP products as soon as
+// the compute warps hold the previous pair in registers, the other the three gradient products of a pair as soon
+// as its P / dS are in shared memory; the waits of one never sit in front of the other's issue.
+__device__ __forceinline__ void resident_mma_scores(ResidentShared& sm, uint32_t tmem) {
   const int n = sm.n_iter;
   if (n == 0) return;
   if (!wait_or_abort(sm, &sm.qg_full, 0, 80)) return;
+  for (int it = 0; it < n; ++it) {
+    const ResidentIter e = resident_iter(sm.sched[it]);
+    // S/dP of the previous pair are in the compute warps' registers: this pair may overwrite them
+    if (it > 0 && !wait_or_abort(sm, &sm.sdp_free, (it - 1) & 1, 83)) return;
+    if (e.first && !wait_or_abort(sm, &sm.kv_ready[e.active & 1], (e.active >> 1) & 1, 81)) return;
+    ptx::tc_fence_after();
+    trace_event(sm, 100 + it);
+    resident_issue_sdp(sm, tmem, e);
+    trace_event(sm, 200 + it);
+  }
+}
+
+__device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t tmem) {
+  const int n = sm.n_iter;
+  if (n == 0) return;
+  if (!wait_or_abort(sm, &sm.qg_full, 0, 84)) return;
   constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, kHeadDim, 1, 1);
   constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);
   const uint32_t p_base = ptx::smem_u32(sm.p), ds_base = ptx::smem_u32(sm.ds);
   bool dq_started[2] = {false, false};
-  ResidentIter e = resident_iter(sm.sched[0]);
-  if (!wait_or_abort(sm, &sm.kv_ready[e.active & 1], (e.active >> 1) & 1, 81)) return;
-  ptx::tc_fence_after();
-  resident_issue_sdp(sm, tmem, e);
   for (int it = 0; it < n; ++it) {
-    // S/dP of this iteration are in the compute warps' registers: the next pair may overwrite them
-    if (!wait_or_abort(sm, &sm.sdp_free, it & 1, 83)) return;
-    ptx::tc_fence_after();
-    trace_event(sm, 100 + it);
-    if (it + 1 < n) {
-      const ResidentIter nx = resident_iter(sm.sched[it + 1]);
-      if (nx.first && !wait_or_abort(sm, &sm.kv_ready[nx.active & 1], (nx.active >> 1) & 1, 81)) return;
-      ptx::tc_fence_after();
-      resident_issue_sdp(sm, tmem, nx);
-      trace_event(sm, 200 + it);
-    }
+    const ResidentIter e = resident_iter(sm.sched[it]);
     if (!wait_or_abort(sm, &sm.pds_full, it & 1, 82)) return;
     ptx::tc_fence_after();
     trace_event(sm, 300 + it);
@@ -200,7 +206,6 @@ __device__ __forceinline__ void resident_mma(ResidentShared& sm, uint32_t tmem) 
     if (e.qt) dq_started[1] = true; else dq_started[0] = true;
     ptx::mma_commit(&sm.mma_done);
     trace_event(sm, 400 + it);
-    if (it + 1 < n) e = resident_iter(sm.sched[it + 1]);
   }
 }
 
@@ -551,8 +556,10 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
     resident_compute(sm, a, tmem, w, delta, head, batch, &map_dk, &map_dv);
   } else if (warp == 8) {
     if (lane == 0) resident_producer(sm, &map_q, &map_k, &map_v, &map_g, w, head, batch);
+  } else if (warp == 9) {
+    if (lane == 0) resident_mma_scores(sm, tmem);
   } else {
-    if (lane == 0) resident_mma(sm, tmem);
+    if (lane == 0) resident_mma_grads(sm, tmem);
   }
   ptx::tma_store_wait_all();
   ptx::tc_fence_before();
