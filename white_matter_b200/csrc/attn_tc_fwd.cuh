@@ -9,8 +9,9 @@
 // owns the key tiles of parity g with its own running reference, row sum, P buffer and output
 // accumulator, so the groups exchange nothing per tile and run out of phase; their partial
 // results are merged in the epilogue like the splits of a split-KV reduction.
-// P is written as bf16 into the K-major 128B-swizzled shared layout that the MMA reads.
-// TMEM: S0..S2 [0,384), O0 [384,448), O1 [448,512) columns; 512 allocated.
+// P never touches shared memory: it is written as packed bf16 over the first 64 columns of its own
+// score buffer and the PV product takes it from there as its A operand.
+// TMEM: S0..S2 [0,384) (P aliases the tile's S), O0 [384,448), O1 [448,512) columns; 512 allocated.
 #pragma once
 
 constexpr int kFwdThreads = 352;
@@ -58,8 +59,8 @@ __device__ __forceinline__ void score_mma_role(Shared& sm, uint32_t tmem, const 
   const uint32_t a_base = ptx::smem_u32(sm.q);
   for (int n = 0; n < w.n_tiles; ++n) {
     const int s = n % kStages;
-    // the softmax of tile n-3 has read this score buffer
-    if (n >= kScoreBuffers && !wait_or_abort(sm, &sm.s_free[s], ((n / kScoreBuffers) & 1) ^ 1, 24)) return;
+    // P of tile n-3 lives in this score buffer until its PV product has read it
+    if (n >= kScoreBuffers && !wait_or_abort(sm, &sm.pv_done[s], ((n / kScoreBuffers) & 1) ^ 1, 24)) return;
     if (!wait_or_abort(sm, &sm.k_full[s], (n / kStages) & 1, 21)) return;
     ptx::tc_fence_after();
     trace_event(sm, 1100 + n);
@@ -88,14 +89,13 @@ __device__ __forceinline__ void value_mma_role(Shared& sm, uint32_t tmem, const 
     ptx::tc_fence_after();
     trace_event(sm, 1200 + n);
     const uint32_t o_tmem = tmem + kOutCol + static_cast<uint32_t>(b) * kHeadDim;
-    const uint32_t p_base = ptx::smem_u32(sm.p[b]);
+    const uint32_t p_tmem = tmem + static_cast<uint32_t>(s) * kTileN;  // P overwrote the first 64 columns of S
     const uint32_t v_base = ptx::smem_u32(sm.v[s]);
 #pragma unroll
     for (int kk = 0; kk < kTileN / 16; ++kk) {
-      // A = P: K-major, 64-key sub-tiles of 16 KB; B = V: head_dim contiguous (MN-major), 16 keys = 2048 bytes
-      const uint64_t a_desc = ptx::make_smem_desc_sw128(p_base + (kk >> 2) * kTileBytes + (kk & 3) * 32, 16, 1024);
+      // A = P from tensor memory, 16 keys = 8 columns; B = V: head_dim contiguous (MN-major), 16 keys = 2048 bytes
       const uint64_t b_desc = ptx::make_smem_desc_sw128(v_base + kk * 2048, 1024, 1024);
-      ptx::mma_bf16_ss(o_tmem, a_desc, b_desc, idesc_pv, (n > 1) || (kk > 0));
+      ptx::mma_bf16_ts(o_tmem, p_tmem + kk * 8, b_desc, idesc_pv, (n > 1) || (kk > 0));
     }
     ptx::mma_commit(&sm.pv_done[s]);
     trace_event(sm, 500 + n);
@@ -107,11 +107,10 @@ struct FwdShared {
   unsigned char q[kTileBytes];
   unsigned char k[kStages][kTileBytes];
   unsigned char v[kStages][kTileBytes];
-  unsigned char p[2][2 * kTileBytes];
   uint64_t q_full;
   // s_full[i] and pv_done[i] also release K and V stage i (score buffers and stages share the ring size)
   uint64_t k_full[kStages], v_full[kStages];
-  uint64_t s_full[kScoreBuffers], s_free[kScoreBuffers], pv_done[kStages], p_full[2], docs_full[2], sum_full;
+  uint64_t s_full[kScoreBuffers], pv_done[kStages], p_full[2], docs_full[2], sum_full;
   int key_seg[2][2][kTileN];  // [group][tile of the group & 1]
   int key_end[2][2][kTileN];
   int tile_summary[2][2][4][3];
@@ -292,9 +291,9 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       l *= corr;
     }
     const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-    // the P buffer and the accumulator were last touched by the PV product of this group's previous tile
-    if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return;
     if (__any_sync(0xffffffffu, moved)) {
+      // the accumulator was last written by the PV product of this group's previous tile
+      if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return;
       ptx::tc_fence_after();
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -308,15 +307,14 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       ptx::tmem_wait_st();
     }
     WM_TRACE(800 + n);
-    // second reading: exponentials, row sum, P as bf16 into the swizzled K-major layout
+    // second reading: exponentials, row sum, P as packed bf16 over the first 64 columns of the score buffer
+    // (piece c of 64 keys goes to columns [32c, 32c+32), all of which have been read by then)
     if (warp_none) {
-      ptx::mbar_arrive(&sm.s_free[sb]);
+      uint32_t zeros[32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint4* prow = reinterpret_cast<uint4*>(sm.p[b] + c * kTileBytes + (row >> 3) * 1024 + (row & 7) * 128);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) prow[u] = make_uint4(0, 0, 0, 0);
-      }
+      for (int e = 0; e < 32; ++e) zeros[e] = 0u;
+      ptx::tmem_st32(s_tmem, zeros);
+      ptx::tmem_st32(s_tmem + 32, zeros);
     } else {
       float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
       const float2 sc = make_float2(sl2, sl2), nm = make_float2(-m_use, -m_use);
@@ -324,11 +322,7 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       for (int c = 0; c < 2; ++c) {
         float x[64];
         load_scores(c, x);
-        if (c == 1) {
-          ptx::tc_fence_before();
-          ptx::mbar_arrive(&sm.s_free[sb]);
-        }
-        unsigned char* prow = sm.p[b] + c * kTileBytes + (row >> 3) * 1024 + (row & 7) * 128;
+        uint32_t pk[32];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           float2 u0 = __ffma2_rn(make_float2(x[8 * u], x[8 * u + 1]), sc, nm);
@@ -345,12 +339,16 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
           u3.y = fast_exp2(u3.y);
           s0 = __fadd2_rn(s0, __fadd2_rn(u0, u1));
           s1 = __fadd2_rn(s1, __fadd2_rn(u2, u3));
-          *reinterpret_cast<uint4*>(prow + ((u ^ (row & 7)) << 4)) =
-              make_uint4(pack_bf16(u0.x, u0.y), pack_bf16(u1.x, u1.y), pack_bf16(u2.x, u2.y), pack_bf16(u3.x, u3.y));
+          pk[4 * u] = pack_bf16(u0.x, u0.y);
+          pk[4 * u + 1] = pack_bf16(u1.x, u1.y);
+          pk[4 * u + 2] = pack_bf16(u2.x, u2.y);
+          pk[4 * u + 3] = pack_bf16(u3.x, u3.y);
         }
+        ptx::tmem_st32(s_tmem + 32 * c, pk);
       }
       l += (s0.x + s0.y) + (s1.x + s1.y);
     }
+    ptx::tmem_wait_st();
     WM_TRACE(900 + n);
     // last tile: value rows at or beyond the largest visible slot may hold anything (unused cache capacity)
     if (n == w.n_tiles - 1 && w.kmax < j0 + kTileN) {
@@ -361,8 +359,8 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
 #pragma unroll
         for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
       }
+      ptx::fence_async_shared();
     }
-    ptx::fence_async_shared();
     ptx::tc_fence_before();
     ptx::mbar_arrive(&sm.p_full[b]);
     WM_TRACE(1000 + n);
@@ -442,7 +440,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
     for (int b = 0; b < kScoreBuffers; ++b) {
       ptx::mbar_init(&sm.s_full[b], 1);
-      ptx::mbar_init(&sm.s_free[b], kFwdGroup);
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&sm.p_full[b], kFwdGroup);
