@@ -208,3 +208,39 @@ def test_training_shape_properties_at_full_size(backend):
     assert out.transpose(1, 2)[first_rows].abs().max().item() == 0
     out2 = cyclic_attention(q, k, 2 * v, backend=backend, **opts)
     assert_parity(out2.float(), 2 * out.float(), what="linearity in V", max_abs_tol=4e-2, rel_l2_tol=1e-2)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("boost", [6.0, 40.0, 400.0])
+def test_scores_that_outgrow_the_running_reference(boost, backend):
+    """Later key tiles whose scores exceed everything seen before by a little, a lot, and by far more than fp32
+    exponentials can hold: the soft-max reference has to follow (deferred rescale, and the re-exponentiation of a
+    tile that outgrew its reference by more than 2^64)."""
+    torch.manual_seed(5)
+    T, S = 1024, 2
+    q = torch.randn(1, 2, T // S, 64)
+    k = torch.randn(1, 2, T, 64)
+    v = torch.randn(1, 2, T, 64)
+    # a few keys in the 4th, 6th and 7th key tile point along the mean query direction with a growing norm
+    direction = q[0, 0].mean(0) / q[0, 0].mean(0).norm()
+    q = q + 2.0 * direction
+    for slot, gain in ((400, boost), (700, 2 * boost), (801, 4 * boost)):
+        k[:, :, slot] = gain * direction
+    q, k, v = (t.bfloat16() for t in (q, k, v))
+    probe = torch.randn(1, 2, T // S, 64).bfloat16()
+    c = dict(stride=S, offset=0, strict_past=False)
+    out, grads = run(q, k, v, probe, None, c, torch.bfloat16, backend)
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp = oracle.cyclic_attention_oracle(qo, ko, vo, query_stride=S, query_offset=0)
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    # The gradients multiply bf16-rounded P and dS by keys whose norm is up to 4*boost, which amplifies the
+    # rounding of any bf16 tensor-core backward: the usual bound is asked for the moderate case only, the extreme
+    # ones must stay finite and keep the direction of the exact gradient.
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        if boost <= 6.0:
+            assert_parity(g.float(), e, what=name, **BF16_TOL)
+        else:
+            assert torch.isfinite(g).all(), name
+            cos = torch.nn.functional.cosine_similarity(g.double().flatten().cpu(), e.flatten(), dim=0).item()
+            assert cos > 0.995, f"{name}: cosine {cos}"

@@ -138,6 +138,8 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
   const float sl2 = a.scale * kLog2e;
   const bool docs = a.q_seg != nullptr;
   float m_ref = -INFINITY, l = 0.f;
+  float pending = 1.f;  // factor the accumulator still has to be multiplied by
+  constexpr float kGuard = 64.f;  // log2 units a tile may exceed its reference by before it is read twice
   const uint32_t o_mine = tmem + kOutCol + grp * kHeadDim + lane_base;
   const int b = grp;  // P buffer, output accumulator and document tables of this group
 
@@ -161,6 +163,10 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
 
   for (int n = grp; n < w.n_tiles; n += 2) {
     const int it = n >> 1;  // tiles this group has finished
+    // A warp that needs nothing from a tile (nothing visible) could finish it before a slower warp of the group
+    // has arrived for the previous one, and its second arrival would complete that phase early: the previous
+    // phase of p_full has to be over before anybody works towards the next arrival.
+    if (it >= 1 && !wait_or_abort(sm, &sm.p_full[b], (it - 1) & 1, 40)) return;
     const int sb = n % kScoreBuffers;
     const int j0 = tile_first_key(n, w.first_tile, w.dummy_tile);
     int cls = !live || j0 >= rb.hi ? kTileNone : (j0 + kTileN <= rb.hi ? kTileFull : kTileCausal);
@@ -225,75 +231,13 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       vis3 = visible_mask(96);
     }
     const uint32_t s_tmem = tmem + static_cast<uint32_t>(sb) * kTileN + lane_base;
-    // 64 scores of this row starting at column 64*c, masked unless the whole warp sees the whole tile
-    auto load_scores = [&](int c, float (&x)[64]) {
-      uint32_t raw0[32], raw1[32];
-      ptx::tmem_ld32(s_tmem + 64 * c, raw0);
-      ptx::tmem_ld32(s_tmem + 64 * c + 32, raw1);
-      ptx::tmem_wait_ld();
-      if (warp_full) {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          x[e] = __uint_as_float(raw0[e]);
-          x[32 + e] = __uint_as_float(raw1[e]);
-        }
-      } else {
-        const uint32_t m0 = c ? vis2 : vis0, m1 = c ? vis3 : vis1;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          x[e] = (m0 >> e) & 1u ? __uint_as_float(raw0[e]) : -INFINITY;
-          x[32 + e] = (m1 >> e) & 1u ? __uint_as_float(raw1[e]) : -INFINITY;
-        }
-      }
-    };
-
     if (!wait_or_abort(sm, &sm.s_full[sb], (n / kScoreBuffers) & 1, 31)) return;
     ptx::tc_fence_after();
     WM_TRACE(600 + n);
-    // first reading: the row maximum, all 128 columns in flight at once
-    float mine = -INFINITY;
-    if (!warp_none) {
-      uint32_t r0[32], r1[32], r2[32], r3[32];
-      ptx::tmem_ld32(s_tmem, r0);
-      ptx::tmem_ld32(s_tmem + 32, r1);
-      ptx::tmem_ld32(s_tmem + 64, r2);
-      ptx::tmem_ld32(s_tmem + 96, r3);
-      ptx::tmem_wait_ld();
-      auto max32 = [&](const uint32_t (&raw)[32], uint32_t mask) -> float {
-        float t0 = -INFINITY, t1 = -INFINITY;
-        if (warp_full) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            t0 = fmax3(t0, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
-            t1 = fmax3(t1, __uint_as_float(raw[e + 2]), __uint_as_float(raw[e + 3]));
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            t0 = fmax3(t0, (mask >> e) & 1u ? __uint_as_float(raw[e]) : -INFINITY,
-                       (mask >> (e + 1)) & 1u ? __uint_as_float(raw[e + 1]) : -INFINITY);
-            t1 = fmax3(t1, (mask >> (e + 2)) & 1u ? __uint_as_float(raw[e + 2]) : -INFINITY,
-                       (mask >> (e + 3)) & 1u ? __uint_as_float(raw[e + 3]) : -INFINITY);
-          }
-        }
-        return fmaxf(t0, t1);
-      };
-      mine = fmaxf(fmaxf(max32(r0, vis0), max32(r1, vis1)), fmaxf(max32(r2, vis2), max32(r3, vis3)));
-    }
-    WM_TRACE(700 + n);
-    const float top = mine * sl2;
-    float corr = 1.f;
-    bool moved = false;
-    if (top > m_ref + kRescaleThreshold || (m_ref == -INFINITY && top > -INFINITY)) {
-      moved = m_ref != -INFINITY;
-      corr = moved ? fast_exp2(m_ref - top) : 1.f;
-      m_ref = top;
-      l *= corr;
-    }
-    const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-    if (__any_sync(0xffffffffu, moved)) {
-      // the accumulator was last written by the PV product of this group's previous tile
-      if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return;
+    // multiply this group's accumulator by `factor` (1 for rows that did not move); the accumulator was last
+    // written by the PV product of the group's previous tile
+    auto rescale_output = [&](float factor) -> bool {
+      if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return false;
       ptx::tc_fence_after();
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -301,14 +245,24 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
         ptx::tmem_ld32(o_mine + 32 * c, raw);
         ptx::tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) raw[e] = __float_as_uint(__uint_as_float(raw[e]) * corr);
+        for (int e = 0; e < 32; ++e) raw[e] = __float_as_uint(__uint_as_float(raw[e]) * factor);
         ptx::tmem_st32(o_mine + 32 * c, raw);
       }
       ptx::tmem_wait_st();
+      return true;
+    };
+    // a reference that moved while the previous tile of this group was exponentiated: the row sum was corrected
+    // then, the accumulator (which had to take that tile's product first) is corrected now
+    if (__any_sync(0xffffffffu, pending != 1.f)) {
+      if (!rescale_output(pending)) return;
+      pending = 1.f;
     }
-    WM_TRACE(800 + n);
-    // second reading: exponentials, row sum, P as packed bf16 over the first 64 columns of the score buffer
-    // (piece c of 64 keys goes to columns [32c, 32c+32), all of which have been read by then)
+    // Rows normally exponentiate against the reference they already have and look at the maximum afterwards
+    // (one reading of the scores).  A warp with a row that has no reference yet, or whose scores turn out to
+    // exceed the reference by more than 2^kGuard, reads the tile twice: maximum first, exponentials second.
+    bool exact = __any_sync(0xffffffffu, cls != kTileNone && m_ref == -INFINITY);
+    float tile_sum = 0.f, tmax = -INFINITY;
+    // P as packed bf16 over the first 64 columns of the score buffer, all of which have been read by then
     if (warp_none) {
       uint32_t zeros[32];
 #pragma unroll
@@ -316,37 +270,123 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       ptx::tmem_st32(s_tmem, zeros);
       ptx::tmem_st32(s_tmem + 32, zeros);
     } else {
-      float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
-      const float2 sc = make_float2(sl2, sl2), nm = make_float2(-m_use, -m_use);
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float x[64];
-        load_scores(c, x);
-        uint32_t pk[32];
+      if (exact) {
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        ptx::tmem_ld32(s_tmem, r0);
+        ptx::tmem_ld32(s_tmem + 32, r1);
+        ptx::tmem_ld32(s_tmem + 64, r2);
+        ptx::tmem_ld32(s_tmem + 96, r3);
+        ptx::tmem_wait_ld();
+        auto max32 = [&](const uint32_t (&raw)[32], uint32_t mask) -> float {
+          float t0 = -INFINITY, t1 = -INFINITY;
+          if (warp_full) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          float2 u0 = __ffma2_rn(make_float2(x[8 * u], x[8 * u + 1]), sc, nm);
-          float2 u1 = __ffma2_rn(make_float2(x[8 * u + 2], x[8 * u + 3]), sc, nm);
-          float2 u2 = __ffma2_rn(make_float2(x[8 * u + 4], x[8 * u + 5]), sc, nm);
-          float2 u3 = __ffma2_rn(make_float2(x[8 * u + 6], x[8 * u + 7]), sc, nm);
-          u0.x = fast_exp2(u0.x);
-          u0.y = fast_exp2(u0.y);
-          u1.x = fast_exp2(u1.x);
-          u1.y = fast_exp2(u1.y);
-          u2.x = fast_exp2(u2.x);
-          u2.y = fast_exp2(u2.y);
-          u3.x = fast_exp2(u3.x);
-          u3.y = fast_exp2(u3.y);
-          s0 = __fadd2_rn(s0, __fadd2_rn(u0, u1));
-          s1 = __fadd2_rn(s1, __fadd2_rn(u2, u3));
-          pk[4 * u] = pack_bf16(u0.x, u0.y);
-          pk[4 * u + 1] = pack_bf16(u1.x, u1.y);
-          pk[4 * u + 2] = pack_bf16(u2.x, u2.y);
-          pk[4 * u + 3] = pack_bf16(u3.x, u3.y);
+            for (int e = 0; e < 32; e += 4) {
+              t0 = fmax3(t0, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
+              t1 = fmax3(t1, __uint_as_float(raw[e + 2]), __uint_as_float(raw[e + 3]));
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              t0 = fmax3(t0, (mask >> e) & 1u ? __uint_as_float(raw[e]) : -INFINITY,
+                         (mask >> (e + 1)) & 1u ? __uint_as_float(raw[e + 1]) : -INFINITY);
+              t1 = fmax3(t1, (mask >> (e + 2)) & 1u ? __uint_as_float(raw[e + 2]) : -INFINITY,
+                         (mask >> (e + 3)) & 1u ? __uint_as_float(raw[e + 3]) : -INFINITY);
+            }
+          }
+          return fmaxf(t0, t1);
+        };
+        const float top =
+            fmaxf(fmaxf(max32(r0, vis0), max32(r1, vis1)), fmaxf(max32(r2, vis2), max32(r3, vis3))) * sl2;
+        float corr = 1.f;
+        if (top > m_ref + kRescaleThreshold || (m_ref == -INFINITY && top > -INFINITY)) {
+          corr = m_ref != -INFINITY ? fast_exp2(m_ref - top) : 1.f;
+          m_ref = top;
+          l *= corr;
         }
-        ptx::tmem_st32(s_tmem + 32 * c, pk);
+        if (__any_sync(0xffffffffu, corr != 1.f) && !rescale_output(corr)) return;
       }
-      l += (s0.x + s0.y) + (s1.x + s1.y);
+      uint32_t pk0[16], pk1[16], pk2[16], pk3[16];
+      // all 128 columns against the current reference: packed P, row sum and the largest exponent
+      auto exponentiate = [&]() {
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        const float2 sc = make_float2(sl2, sl2), nm = make_float2(-m_use, -m_use);
+        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
+        float g0 = -INFINITY, g1 = -INFINITY;
+        // 32 columns at a time keep the live registers (scores + packed P of the whole tile) under the limit
+        auto piece = [&](int q, uint32_t mask, uint32_t (&pk)[16]) {
+          uint32_t raw[32];
+          ptx::tmem_ld32(s_tmem + 32 * q, raw);
+          ptx::tmem_wait_ld();
+          float x[32];
+          if (warp_full) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) x[e] = __uint_as_float(raw[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) x[e] = (mask >> e) & 1u ? __uint_as_float(raw[e]) : -INFINITY;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float2 u0 = __ffma2_rn(make_float2(x[8 * u], x[8 * u + 1]), sc, nm);
+            float2 u1 = __ffma2_rn(make_float2(x[8 * u + 2], x[8 * u + 3]), sc, nm);
+            float2 u2 = __ffma2_rn(make_float2(x[8 * u + 4], x[8 * u + 5]), sc, nm);
+            float2 u3 = __ffma2_rn(make_float2(x[8 * u + 6], x[8 * u + 7]), sc, nm);
+            g0 = fmax3(g0, fmaxf(u0.x, u0.y), fmaxf(u1.x, u1.y));
+            g1 = fmax3(g1, fmaxf(u2.x, u2.y), fmaxf(u3.x, u3.y));
+            u0.x = fast_exp2(u0.x);
+            u0.y = fast_exp2(u0.y);
+            u1.x = fast_exp2(u1.x);
+            u1.y = fast_exp2(u1.y);
+            u2.x = fast_exp2(u2.x);
+            u2.y = fast_exp2(u2.y);
+            u3.x = fast_exp2(u3.x);
+            u3.y = fast_exp2(u3.y);
+            s0 = __fadd2_rn(s0, __fadd2_rn(u0, u1));
+            s1 = __fadd2_rn(s1, __fadd2_rn(u2, u3));
+            pk[4 * u] = pack_bf16(u0.x, u0.y);
+            pk[4 * u + 1] = pack_bf16(u1.x, u1.y);
+            pk[4 * u + 2] = pack_bf16(u2.x, u2.y);
+            pk[4 * u + 3] = pack_bf16(u3.x, u3.y);
+          }
+        };
+        piece(0, vis0, pk0);
+        piece(1, vis1, pk1);
+        piece(2, vis2, pk2);
+        piece(3, vis3, pk3);
+        tile_sum = (s0.x + s0.y) + (s1.x + s1.y);
+        tmax = fmaxf(g0, g1);
+      };
+      exponentiate();
+      if (!exact && __any_sync(0xffffffffu, tmax > kGuard)) {
+        // the tile outgrew its reference by so much that the exponentials may have overflowed: move the
+        // reference of those rows to the tile maximum and exponentiate once more (the scores are still there)
+        float corr = 1.f;
+        if (tmax > kGuard) {
+          m_ref += tmax;
+          corr = fast_exp2(-tmax);
+          l *= corr;
+        }
+        if (!rescale_output(corr)) return;
+        exponentiate();
+      }
+      uint32_t lo[32], hi[32];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        lo[e] = pk0[e];
+        lo[16 + e] = pk1[e];
+        hi[e] = pk2[e];
+        hi[16 + e] = pk3[e];
+      }
+      ptx::tmem_st32(s_tmem, lo);
+      ptx::tmem_st32(s_tmem + 32, hi);
+    }
+    l += tile_sum;
+    if (tmax > kRescaleThreshold && n + 2 < w.n_tiles) {
+      // the tile outgrew the reference: move it for the tiles to come
+      m_ref += tmax;
+      pending = fast_exp2(-tmax);
+      l *= pending;
     }
     ptx::tmem_wait_st();
     WM_TRACE(900 + n);
