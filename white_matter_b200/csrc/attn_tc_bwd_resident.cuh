@@ -108,6 +108,7 @@ struct ResidentShared {
   uint64_t kv_full[2], kv_ready[2], kv_empty[2];
   uint64_t sdp_full, sdp_free, pds_full, mma_done;
   uint64_t out_full[2];  // dV (half 0) / dK (half 1) rows of a finished key tile are staged in shared memory
+  uint64_t stage_free[2];  // the store out of the spare staging room has read it
   int key_seg[2][kTileN];
   int key_end[2][kTileN];
   int summary[2][4][3];
@@ -116,6 +117,7 @@ struct ResidentShared {
   // iteration list: key tile | query tile << 12 | first-of-key-tile << 13 | last-of-key-tile << 14 | visited index << 16
   uint32_t sched[kResidentMaxIter];
   int n_iter;
+  int q0_last_iter;  // last iteration that uses query tile 0 (-1: none)
   uint32_t tmem_base;
   int abort_flag;
   int epoch;
@@ -172,9 +174,10 @@ __device__ __forceinline__ void resident_mma_scores(ResidentShared& sm, uint32_t
   }
 }
 
-__device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t tmem) {
+__device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t tmem, int nq) {
   const int n = sm.n_iter;
   if (n == 0) return;
+  const int spare_from = nq == 1 ? 0 : sm.q0_last_iter + 1;  // same rule as the compute warps' staging
   if (!wait_or_abort(sm, &sm.qg_full, 0, 84)) return;
   constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, kHeadDim, 1, 1);
   constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);
@@ -205,6 +208,12 @@ __device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t 
                        ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, acc_q || (kk > 0));
     if (e.qt) dq_started[1] = true; else dq_started[0] = true;
     ptx::mma_commit(&sm.mma_done);
+    if (e.last && it + 1 >= spare_from) {
+      // the gradients of this key tile will be staged in spare room: its K/V stage is free as soon as these
+      // products are complete (two arrivals, as many as the staging threads give when they release a stage)
+      ptx::mma_commit(&sm.kv_empty[s]);
+      ptx::mma_commit(&sm.kv_empty[s]);
+    }
     trace_event(sm, 400 + it);
   }
 }
@@ -284,24 +293,45 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     }
     ptx::fence_async_shared();
     ptx::mbar_arrive(&sm.kv_ready[s]);
-    return wait_or_abort(sm, &sm.kv_ready[s], (e.active >> 1) & 1, 91);
+    return true;
+  };
+  // every compute thread has prepared the tile: its document table is complete
+  auto prepared = [&](const ResidentIter& e) -> bool {
+    return wait_or_abort(sm, &sm.kv_ready[e.active & 1], (e.active >> 1) & 1, 91);
   };
 
   // dV / dK of a finished key tile: TMEM -> bf16 -> the tile's own (now idle) V / K stage in shared memory, in
   // the 128B-swizzled row layout of the output tensor map -> one TMA store per half.  The stage goes back to the
   // producer once the store has read it.
+  // Once the first query tile has no pair left (or when there is only one query tile), the Q / dO tiles of an
+  // idle query tile are spare staging room: the K/V stage then goes back to the producer at once, which hides
+  // the load of the next key tile behind the current pair (key tiles seen by one query tile only would otherwise
+  // expose it every time).
   int outs = 0;  // staged stores so far (parity of out_full)
+  int spare_outs = 0;  // of those, through the spare room (parity of stage_free)
   int release_stage = -1;  // stage whose staged gradients still have to be read before the producer may refill it
+  bool release_spare = false;
+  const int spare_tile = w.nq == 1 ? 1 : 0;
+  const int spare_from = w.nq == 1 ? 0 : sm.q0_last_iter + 1;  // first iteration index at which it is free
   auto release = [&]() {
-    if (release_stage >= 0 && row == 0) {
+    if (row == 0 && (release_stage >= 0 || release_spare)) {
       ptx::tma_store_wait_read();
-      ptx::mbar_arrive(&sm.kv_empty[release_stage]);
+      if (release_stage >= 0) ptx::mbar_arrive(&sm.kv_empty[release_stage]);
+      if (release_spare) ptx::mbar_arrive(&sm.stage_free[half]);
     }
     release_stage = -1;
+    release_spare = false;
   };
-  auto stage_out = [&](int kt, int stage, bool release_now) -> bool {
+  auto stage_out = [&](int kt, int stage, int it_now, bool release_now) -> bool {
     const float sc = half ? a.scale : 1.f;
-    unsigned char* dst = (half ? sm.k[stage] : sm.v[stage]) + (row >> 3) * 1024 + (row & 7) * 128;
+    const bool spare = it_now >= spare_from;
+    unsigned char* tile = spare ? (half ? sm.q[spare_tile] : sm.g[spare_tile]) : (half ? sm.k[stage] : sm.v[stage]);
+    if (spare) {
+      // (the K/V stage of this key tile was handed back by the gradient issuer's commit)
+      // the previous store out of the spare room has to have read it
+      if (spare_outs > 0 && !wait_or_abort(sm, &sm.stage_free[half], (spare_outs - 1) & 1, 96)) return false;
+    }
+    unsigned char* dst = tile + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {  // 32 columns at a time keeps the register footprint small
       uint32_t raw[32];
@@ -320,10 +350,15 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     ptx::mbar_arrive(&sm.out_full[half]);
     if (!wait_or_abort(sm, &sm.out_full[half], outs & 1, 95)) return false;
     if (row == 0) {
-      ptx::tma_store_4d(half ? map_dk : map_dv, half ? sm.k[stage] : sm.v[stage], 0, kt * kTileN, head, batch);
+      ptx::tma_store_4d(half ? map_dk : map_dv, tile, 0, kt * kTileN, head, batch);
       ptx::tma_store_commit();
     }
-    release_stage = stage;
+    if (spare) {
+      release_spare = true;
+      ++spare_outs;
+    } else {
+      release_stage = stage;
+    }
     if (release_now) release();
     ++outs;
     return true;
@@ -333,6 +368,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
   int pending_kt = -1, pending_stage = 0;
   for (int it = 0; it < n; ++it) {
     const ResidentIter e = resident_iter(sm.sched[it]);
+    if (e.first && !prepared(e)) return;
     const int s = e.active & 1;
     const int j0 = e.kt * kTileN;
     const RowBound& r = e.qt ? rb1 : rb0;
@@ -419,7 +455,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     // dV / dK of a finished key tile leave TMEM before this iteration's products (which restart the accumulators)
     // can be issued, i.e. before pds_full; the shared-memory stage is released and the next tile prepared after it
     if (pending_kt >= 0) {
-      if (!stage_out(pending_kt, pending_stage, false)) return;
+      if (!stage_out(pending_kt, pending_stage, it, false)) return;
       pending_kt = -1;
     }
     ptx::fence_async_shared();
@@ -436,7 +472,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
   if (n > 0) {
     if (!wait_or_abort(sm, &sm.mma_done, (n - 1) & 1, 94)) return;
     ptx::tc_fence_after();
-    if (pending_kt >= 0 && !stage_out(pending_kt, pending_stage, true)) return;
+    if (pending_kt >= 0 && !stage_out(pending_kt, pending_stage, n, true)) return;
   }
   {
     // half h writes the dQ rows of query tile h
@@ -531,12 +567,17 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
       ++active;
     }
     sm.n_iter = n;
+    int q0_last = -1;
+    for (int i = 0; i < n; ++i)
+      if (((sm.sched[i] >> 12) & 1) == 0) q0_last = i;
+    sm.q0_last_iter = q0_last;
     ptx::mbar_init(&sm.qg_full, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&sm.kv_full[s], 1);
       ptx::mbar_init(&sm.kv_ready[s], kResidentCompute);
       ptx::mbar_init(&sm.kv_empty[s], 2);  // the two halves' store threads release a stage
       ptx::mbar_init(&sm.out_full[s], kTileM);
+      ptx::mbar_init(&sm.stage_free[s], 1);
     }
     ptx::mbar_init(&sm.sdp_full, 1);
     ptx::mbar_init(&sm.sdp_free, kResidentCompute);
@@ -559,7 +600,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
   } else if (warp == 9) {
     if (lane == 0) resident_mma_scores(sm, tmem);
   } else {
-    if (lane == 0) resident_mma_grads(sm, tmem);
+    if (lane == 0) resident_mma_grads(sm, tmem, w.nq);
   }
   ptx::tma_store_wait_all();
   ptx::tc_fence_before();
