@@ -411,16 +411,27 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
       }
       return mask;
     };
+    // P = exp2(S * scale * log2e - lse * log2e), dS = P * (dP - delta), two elements per instruction where the
+    // hardware has packed fp32 forms.  A masked score becomes -inf before the exponential, so its P and dS are
+    // exact zeros; a warp whose rows all see the whole tile skips the masking.
+    const bool warp_full = __all_sync(0xffffffffu, cls == kTileFull);
     auto math = [&](const uint32_t (&xs)[32], const uint32_t (&ys)[32], uint32_t mask, uint32_t (&pp)[16],
                     uint32_t (&dd)[16]) {
+      const float2 sc2 = make_float2(sl2, sl2), nl2 = make_float2(nl, nl), nd2 = make_float2(-dlt, -dlt);
 #pragma unroll
       for (int e2 = 0; e2 < 16; ++e2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2]), sl2, nl));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(xs[2 * e2 + 1]), sl2, nl));
-        const bool v0 = (mask >> (2 * e2)) & 1u, v1 = (mask >> (2 * e2 + 1)) & 1u;
-        pp[e2] = pack_bf16(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
-        dd[e2] = pack_bf16(v0 ? p0 * (__uint_as_float(ys[2 * e2]) - dlt) : 0.f,
-                           v1 ? p1 * (__uint_as_float(ys[2 * e2 + 1]) - dlt) : 0.f);
+        float2 x = make_float2(__uint_as_float(xs[2 * e2]), __uint_as_float(xs[2 * e2 + 1]));
+        if (!warp_full) {
+          x.x = (mask >> (2 * e2)) & 1u ? x.x : -INFINITY;
+          x.y = (mask >> (2 * e2 + 1)) & 1u ? x.y : -INFINITY;
+        }
+        float2 pr = __ffma2_rn(x, sc2, nl2);
+        pr.x = fast_exp2(pr.x);
+        pr.y = fast_exp2(pr.y);
+        const float2 ds = __fmul2_rn(
+            pr, __fadd2_rn(make_float2(__uint_as_float(ys[2 * e2]), __uint_as_float(ys[2 * e2 + 1])), nd2));
+        pp[e2] = pack_bf16(pr.x, pr.y);
+        dd[e2] = pack_bf16(ds.x, ds.y);
       }
     };
     auto store = [&](int c, const uint32_t (&pp)[16], const uint32_t (&dd)[16]) {

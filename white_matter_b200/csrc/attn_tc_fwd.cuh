@@ -313,11 +313,9 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
         const float2 sc = make_float2(sl2, sl2), nm = make_float2(-m_use, -m_use);
         float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
         float g0 = -INFINITY, g1 = -INFINITY;
-        // 32 columns at a time keep the live registers (scores + packed P of the whole tile) under the limit
-        auto piece = [&](int q, uint32_t mask, uint32_t (&pk)[16]) {
-          uint32_t raw[32];
-          ptx::tmem_ld32(s_tmem + 32 * q, raw);
-          ptx::tmem_wait_ld();
+        // 32 columns at a time keep the live registers (scores + packed P of the whole tile) under the limit;
+        // the load of the next piece is in flight while this one is exponentiated
+        auto piece = [&](uint32_t (&raw)[32], uint32_t mask, uint32_t (&pk)[16]) {
           float x[32];
           if (warp_full) {
 #pragma unroll
@@ -326,34 +324,42 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
 #pragma unroll
             for (int e = 0; e < 32; ++e) x[e] = (mask >> e) & 1u ? __uint_as_float(raw[e]) : -INFINITY;
           }
+          // one kind of instruction at a time: 32 independent exponentials in a row keep the special-function
+          // unit busy from a single warp
+          float2 t[16];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float2 u0 = __ffma2_rn(make_float2(x[8 * u], x[8 * u + 1]), sc, nm);
-            float2 u1 = __ffma2_rn(make_float2(x[8 * u + 2], x[8 * u + 3]), sc, nm);
-            float2 u2 = __ffma2_rn(make_float2(x[8 * u + 4], x[8 * u + 5]), sc, nm);
-            float2 u3 = __ffma2_rn(make_float2(x[8 * u + 6], x[8 * u + 7]), sc, nm);
-            g0 = fmax3(g0, fmaxf(u0.x, u0.y), fmaxf(u1.x, u1.y));
-            g1 = fmax3(g1, fmaxf(u2.x, u2.y), fmaxf(u3.x, u3.y));
-            u0.x = fast_exp2(u0.x);
-            u0.y = fast_exp2(u0.y);
-            u1.x = fast_exp2(u1.x);
-            u1.y = fast_exp2(u1.y);
-            u2.x = fast_exp2(u2.x);
-            u2.y = fast_exp2(u2.y);
-            u3.x = fast_exp2(u3.x);
-            u3.y = fast_exp2(u3.y);
-            s0 = __fadd2_rn(s0, __fadd2_rn(u0, u1));
-            s1 = __fadd2_rn(s1, __fadd2_rn(u2, u3));
-            pk[4 * u] = pack_bf16(u0.x, u0.y);
-            pk[4 * u + 1] = pack_bf16(u1.x, u1.y);
-            pk[4 * u + 2] = pack_bf16(u2.x, u2.y);
-            pk[4 * u + 3] = pack_bf16(u3.x, u3.y);
+          for (int u = 0; u < 16; ++u) t[u] = __ffma2_rn(make_float2(x[2 * u], x[2 * u + 1]), sc, nm);
+#pragma unroll
+          for (int u = 0; u < 16; u += 4) {
+            g0 = fmax3(g0, fmaxf(t[u].x, t[u].y), fmaxf(t[u + 1].x, t[u + 1].y));
+            g1 = fmax3(g1, fmaxf(t[u + 2].x, t[u + 2].y), fmaxf(t[u + 3].x, t[u + 3].y));
           }
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            t[u].x = fast_exp2(t[u].x);
+            t[u].y = fast_exp2(t[u].y);
+          }
+#pragma unroll
+          for (int u = 0; u < 16; u += 4) {
+            s0 = __fadd2_rn(s0, __fadd2_rn(t[u], t[u + 1]));
+            s1 = __fadd2_rn(s1, __fadd2_rn(t[u + 2], t[u + 3]));
+          }
+#pragma unroll
+          for (int u = 0; u < 16; ++u) pk[u] = pack_bf16(t[u].x, t[u].y);
         };
-        piece(0, vis0, pk0);
-        piece(1, vis1, pk1);
-        piece(2, vis2, pk2);
-        piece(3, vis3, pk3);
+        uint32_t even[32], odd[32];
+        ptx::tmem_ld32(s_tmem, even);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld32(s_tmem + 32, odd);
+        piece(even, vis0, pk0);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld32(s_tmem + 64, even);
+        piece(odd, vis1, pk1);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld32(s_tmem + 96, odd);
+        piece(even, vis2, pk2);
+        ptx::tmem_wait_ld();
+        piece(odd, vis3, pk3);
         tile_sum = (s0.x + s0.y) + (s1.x + s1.y);
         tmax = fmaxf(g0, g1);
       };
