@@ -202,6 +202,35 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Document visibility of the 128 key columns of a tile for the rows of one warp (row = lane), as four 32-column
+// bit masks per row.  Lane c holds the table entries of columns c, c+32, c+64 and c+96 in registers; the rows
+// that need a mask are visited in turn, their parameters broadcast, and four ballots give the row's masks --
+// no shared-memory access and no per-element loop in the row's own thread.
+__device__ __forceinline__ void warp_doc_masks(const RowBound& rb, bool wanted, int j0, const int* key_seg,
+                                               const int* key_end, uint32_t (&out)[4]) {
+  const int lane = threadIdx.x & 31;
+  int seg[4], end[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    seg[c] = key_seg[32 * c + lane];
+    end[c] = key_end[32 * c + lane];
+    out[c] = 0xffffffffu;
+  }
+  for (uint32_t left = __ballot_sync(0xffffffffu, wanted); left != 0u; left &= left - 1u) {
+    const int r = __ffs(left) - 1;
+    const int rseg = __shfl_sync(0xffffffffu, rb.seg, r);
+    const int rqi = __shfl_sync(0xffffffffu, rb.qi, r);
+    const int rlo = __shfl_sync(0xffffffffu, rb.lo, r);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int j = j0 + 32 * c + lane;
+      const bool vis = (rqi < end[c]) & ((seg[c] == -1) | ((seg[c] == rseg) & (j >= rlo)));
+      const uint32_t m = __ballot_sync(0xffffffffu, vis);
+      if (lane == r) out[c] = m;
+    }
+  }
+}
+
 // How a key tile relates to one query row.
 enum TileClass { kTileNone = 0, kTileFull = 1, kTileCausal = 2, kTileDocs = 3 };
 

@@ -397,19 +397,13 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     // Visibility of 32 columns as one bit mask: arithmetic for the causal bound, a short loop over the key table
     // for tiles that contain a document boundary.  One copy of the math serves every tile class.
     const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
-    auto visible_mask = [&](int col0) -> uint32_t {
+    uint32_t dm[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+    if (__any_sync(0xffffffffu, cls == kTileDocs))
+      warp_doc_masks(r, cls == kTileDocs, j0, sm.key_seg[s], sm.key_end[s], dm);
+    const uint32_t dm_lo = half ? dm[2] : dm[0], dm_hi = half ? dm[3] : dm[1];  // this thread's 64 columns
+    auto causal_mask = [&](int col0) -> uint32_t {
       const int left = lim_eff - col0;
-      uint32_t mask = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
-      if (cls == kTileDocs && mask != 0u) {
-        uint32_t docs_mask = 0u;
-#pragma unroll 1
-        for (int e2 = 0; e2 < 32; ++e2) {
-          const int col = col0 + e2;
-          docs_mask |= static_cast<uint32_t>(doc_visible_flat(r, j0 + col, sm.key_seg[s][col], sm.key_end[s][col])) << e2;
-        }
-        mask &= docs_mask;
-      }
-      return mask;
+      return left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
     };
     // P = exp2(S * scale * log2e - lse * log2e), dS = P * (dP - delta), two elements per instruction where the
     // hardware has packed fp32 forms.  A masked score becomes -inf before the exponential, so its P and dS are
@@ -447,14 +441,14 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
       ptx::tmem_ld32(tmem + lane_base + half * 64, xs);
       ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64, ys);
       ptx::tmem_wait_ld();
-      math(xs, ys, visible_mask(half * 64), pp0, dd0);
+      math(xs, ys, causal_mask(half * 64) & dm_lo, pp0, dd0);
       ptx::tmem_ld32(tmem + lane_base + half * 64 + 32, xs);
       ptx::tmem_ld32(tmem + kTileN + lane_base + half * 64 + 32, ys);
       ptx::tmem_wait_ld();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&sm.sdp_free);  // all scores are in registers: S/dP of the next pair may be issued
       if (tid == 0) trace_event(sm, 800 + it);
-      math(xs, ys, visible_mask(half * 64 + 32), pp1, dd1);
+      math(xs, ys, causal_mask(half * 64 + 32) & dm_hi, pp1, dd1);
       if (tid == 0) trace_event(sm, 900 + it);
       // the shared P / dS tiles are read by the products of the previous iteration until mma_done
       if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 93)) return;

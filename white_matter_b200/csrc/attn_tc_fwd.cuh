@@ -207,28 +207,21 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     const bool warp_none = __all_sync(0xffffffffu, cls == kTileNone);
     const int lim = rb.hi - j0;
     const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
-    // visibility of 32 columns as a bit mask: arithmetic for the causal bound, a short loop over the key table
-    // for tiles that contain a document boundary
-    auto visible_mask = [&](int col0) -> uint32_t {
-      const int left = lim_eff - col0;
-      uint32_t mask = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
-      if (cls == kTileDocs && mask != 0u) {
-        uint32_t docs_mask = 0u;
-#pragma unroll 1
-        for (int e = 0; e < 32; ++e) {
-          const int col = col0 + e;
-          docs_mask |= static_cast<uint32_t>(doc_visible_flat(rb, j0 + col, sm.key_seg[b][it & 1][col], sm.key_end[b][it & 1][col])) << e;
-        }
-        mask &= docs_mask;
-      }
-      return mask;
-    };
+    // visibility of 32 columns as a bit mask: arithmetic for the causal bound, and the key tile's document table
+    // (looked at by the whole warp together) for rows whose tile contains a document boundary
     uint32_t vis0 = 0xffffffffu, vis1 = 0xffffffffu, vis2 = 0xffffffffu, vis3 = 0xffffffffu;
     if (!warp_full && !warp_none) {
-      vis0 = visible_mask(0);
-      vis1 = visible_mask(32);
-      vis2 = visible_mask(64);
-      vis3 = visible_mask(96);
+      uint32_t dm[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+      if (__any_sync(0xffffffffu, cls == kTileDocs))
+        warp_doc_masks(rb, cls == kTileDocs, j0, sm.key_seg[b][it & 1], sm.key_end[b][it & 1], dm);
+      auto causal_mask = [&](int col0) -> uint32_t {
+        const int left = lim_eff - col0;
+        return left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
+      };
+      vis0 = causal_mask(0) & dm[0];
+      vis1 = causal_mask(32) & dm[1];
+      vis2 = causal_mask(64) & dm[2];
+      vis3 = causal_mask(96) & dm[3];
     }
     const uint32_t s_tmem = tmem + static_cast<uint32_t>(sb) * kTileN + lane_base;
     if (!wait_or_abort(sm, &sm.s_full[sb], (n / kScoreBuffers) & 1, 31)) return;
