@@ -263,17 +263,27 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
 
   // Make a visited key tile ready for the MMAs: publish its document table, clear rows beyond the last visible
   // slot (they may hold anything), and meet the other compute threads at kv_ready.
+  // the table entries of a key tile are fetched one pair ahead of the tile's preparation
+  int pf_seg = INT_MIN, pf_end = 0, pf_kt = -1;
+  auto fetch_table = [&](int kt) {
+    if (w.docs && half == 0) {
+      pf_seg = INT_MIN;
+      pf_end = 0;
+      pf_kt = kt;
+      const int j = kt * kTileN + row;
+      if (j < a.k_len) {
+        const long long at = static_cast<long long>(batch) * a.k_len + j;
+        pf_seg = __ldg(a.k_seg + at);
+        pf_end = __ldg(a.k_query_end + at);
+      }
+    }
+  };
   auto prepare = [&](const ResidentIter& e) -> bool {
     const int s = e.active & 1;
     const int j0 = e.kt * kTileN;
     if (w.docs && half == 0) {
-      int seg = INT_MIN, end = 0;
-      const int j = j0 + row;
-      if (j < a.k_len) {
-        const long long at = static_cast<long long>(batch) * a.k_len + j;
-        seg = __ldg(a.k_seg + at);
-        end = __ldg(a.k_query_end + at);
-      }
+      if (pf_kt != e.kt) fetch_table(e.kt);
+      const int seg = pf_seg, end = pf_end;
       sm.key_seg[s][row] = seg;
       sm.key_end[s][row] = end;
       const int smin = __reduce_min_sync(0xffffffffu, seg);
@@ -369,6 +379,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
   for (int it = 0; it < n; ++it) {
     const ResidentIter e = resident_iter(sm.sched[it]);
     if (e.first && !prepared(e)) return;
+    if (e.last && it + 1 < n) fetch_table(resident_iter(sm.sched[it + 1]).kt);
     const int s = e.active & 1;
     const int j0 = e.kt * kTileN;
     const RowBound& r = e.qt ? rb1 : rb0;
