@@ -494,7 +494,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
-            "backend": args.backend, "launch_mode": "eager" if args.no_graph else "cuda graph replay of one step",
+            "device_status": int(lib.wm_device_status(0)), "backend": args.backend, "launch_mode": "eager" if args.no_graph else "cuda graph replay of one step",
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": sets[0].staging_bytes()[0],
                     "d2h_bytes_per_step": sets[0].staging_bytes()[1]},
             "roofline": {"bound": "tensor", "kernel": "backward kernels of one residue call (attn_bwd_resident_kernel + bwd_delta_kernel)",

@@ -156,8 +156,9 @@ typedef struct wm_mix_args {
 WM_API int wm_abi_version(void);
 WM_API const char* wm_last_error(void);
 /* Status word of the pipelined kernels on the current device: 0 when every bounded
- * wait inside them completed, else the code of the first wait that gave up.
- * Synchronises the device; reset != 0 clears the word. */
+ * wait inside them completed, else the first wait that gave up: its code in the low byte,
+ * the linear index of its block in the bits above.  Synchronises the device; reset != 0
+ * clears the word. */
 WM_API int wm_device_status(int reset);
 /* Number of kernels this library has launched in the process so far (diagnostic). */
 WM_API unsigned long long wm_kernel_launch_count(void);

@@ -100,7 +100,9 @@ __device__ __forceinline__ void trace_flush(Shared&) {}
 
 template <class Shared>
 __device__ __forceinline__ void record_failure(Shared& sm, int code) {
-  atomicCAS(&g_status, 0, code);
+  // low byte: which wait gave up; above it: the linear index of the block
+  const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  atomicCAS(&g_status, 0, code | static_cast<int>((block & 0x7fffffu) << 8));
   atomicExch(&g_abort_epoch, sm.epoch);
   atomicExch(&sm.abort_flag, 1);
 }

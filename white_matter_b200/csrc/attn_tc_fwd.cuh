@@ -167,6 +167,11 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     // has arrived for the previous one, and its second arrival would complete that phase early: the previous
     // phase of p_full has to be over before anybody works towards the next arrival.
     if (it >= 1 && !wait_or_abort(sm, &sm.p_full[b], (it - 1) & 1, 40)) return;
+    // The PV issuer reads p_full by parity: the group must not complete the phase of this tile before the issuer
+    // has consumed the phase of the group's previous tile, or the issuer, late by whatever the scheduler does to
+    // a single-lane role, would see an unfinished phase of the same parity and wait for ever.  The PV product of
+    // the previous tile being complete proves that it has.
+    if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return;
     const int sb = n % kScoreBuffers;
     const int j0 = tile_first_key(n, w.first_tile, w.dummy_tile);
     int cls = !live || j0 >= rb.hi ? kTileNone : (j0 + kTileN <= rb.hi ? kTileFull : kTileCausal);
@@ -230,8 +235,7 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     // multiply this group's accumulator by `factor` (1 for rows that did not move); the accumulator was last
     // written by the PV product of the group's previous tile
     auto rescale_output = [&](float factor) -> bool {
-      if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return false;
-      ptx::tc_fence_after();
+      ptx::tc_fence_after();  // (the PV product of the group's previous tile is complete: waited for at the top of the tile)
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t raw[32];
