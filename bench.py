@@ -327,6 +327,14 @@ def bench_mixing(device, peaks, iters=10):
     }
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU legs are meant to use every core the process may run on."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if torch.get_num_threads() < cores:
+        torch.set_num_threads(cores)
+    return torch.get_num_threads()
+
+
 def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1):
     """The CPU oracle on a bounded sample of the training workload: `rows` batch rows, the given residues, fwd+bwd, fp32.
 
@@ -335,6 +343,8 @@ def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1):
     """
     from oracle import attention_oracle as oracle
     from white_matter_b200 import prepare_feedback_metadata
+
+    use_all_host_threads()
 
     docs = geometric_documents(B, T, DOC_MEAN, seed=7)[:rows]
     groups = [torch.arange(r, T, STRIDE) for r in range(STRIDE)]
