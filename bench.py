@@ -13,8 +13,9 @@ The headline ``value`` is TFLOP/s on the visible (query,key) pairs only,
 14*head_dim FLOP per pair (4 forward, 10 backward), with inputs resident in
 HBM.  ``e2e`` is the same metric with pinned host buffers copied in and the
 results copied back inside the timed region.  The same line also reports the
-pool-read (decode) bandwidth and the source-mixing bandwidth, each with its
-roofline fraction, and the CPU oracle timed on a bounded sample.
+pool-read (decode) bandwidth, the cached-prefix prefill over the same pool,
+the Jacobi prefill and the source-mixing bandwidth, each with its roofline
+fraction, and the CPU oracle timed on a bounded sample.
 """
 
 from __future__ import annotations
@@ -101,7 +102,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "25", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
         except OSError:
@@ -301,11 +302,53 @@ def bench_decode(device, peaks, iters=20):
     ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
     nbytes = int(lengths.sum().item()) * 2 * heads * dim * 2
     gbs = nbytes / (ms * 1e-3) / 1e9
-    return {
+    result = {
         "workload": "strict decode B=64 H=16 D=64 lengths~U[1,8192] bf16 (pool 2.15 GB > L2)",
         "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["decode_split_kernel"]},
+    }
+    # cached-prefix prefill over the same pool: 128 new tokens per sequence, query_start = kv_length - 128 (>= 0)
+    q128 = torch.randn(batch, heads, 128, dim, device=device, dtype=torch.bfloat16)
+    starts = (lengths - 128).clamp_min(0)
+    call = lambda: strict_causal_attention(q128, k, v, query_start=starts, kv_lengths=lengths)
+    ms128 = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+    pos = starts.cpu()[:, None] + torch.arange(128)[None, :]
+    pairs = int(torch.minimum(pos, lengths.cpu()[:, None]).sum().item()) * heads
+    gbs128 = nbytes / (ms128 * 1e-3) / 1e9
+    prefill = {
+        "workload": "strict cached-prefix prefill: 128 new tokens per sequence over the same pool",
+        "ms": ms128, "bytes": nbytes, "value": gbs128, "unit": "GB/s", "tflops": 4 * dim * pairs / (ms128 * 1e-3) / 1e12,
+        "roofline": {"bound": "hbm", "achieved": gbs128, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs128 / peaks["hbm_gbs"], "traffic": None},
+    }
+    return result, prefill
+
+
+def bench_jacobi(device, peaks, iters=10):
+    """Jacobi prefill: B=8, H=16, T=2048, D=64 bf16, packed documents (geometric, mean 512), schedule built once."""
+    from white_matter_b200 import prepare_strict_causal_metadata, strict_causal_attention
+
+    batch, heads, length, dim = 8, 16, 2048, 64
+    docs = geometric_documents(batch, length, 512, seed=7)
+    metadata = prepare_strict_causal_metadata(docs.to(device), length)
+    gen = torch.Generator().manual_seed(100)
+    mk = lambda scale: (torch.randn(batch, heads, length, dim, generator=gen) * scale).to(device, torch.bfloat16)
+    q, k, v = mk(dim ** -0.5), mk(1.0), mk(1.0)
+    call = lambda: strict_causal_attention(q, k, v, metadata=metadata)
+    ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+    pairs = 0
+    for row in docs.tolist():
+        run = 0
+        for t in range(length):
+            run = run + 1 if t and row[t] == row[t - 1] else 1
+            pairs += run - 1  # strictly earlier tokens of the same document
+    tf = 4 * dim * pairs * heads / (ms * 1e-3) / 1e12
+    return {
+        "workload": "strict Jacobi prefill forward B=8 H=16 T=2048 D=64 bf16, packed documents (geometric, mean 512)",
+        "ms": ms, "value": tf, "unit": "TFLOP/s",
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_kind": "bf16_tflops (kernel timed alone)"},
     }
 
 
@@ -496,7 +539,8 @@ def main():
     if not args.skip_extras:
         del staging
         torch.cuda.empty_cache()
-        extras["decode"] = bench_decode(device, peaks)
+        extras["decode"], extras["prefill128"] = bench_decode(device, peaks)
+        extras["jacobi"] = bench_jacobi(device, peaks)
         extras["mixing"] = bench_mixing(device, peaks)
     if rank == 0:
         line = {
