@@ -244,3 +244,32 @@ def test_scores_that_outgrow_the_running_reference(boost, backend):
             assert torch.isfinite(g).all(), name
             cos = torch.nn.functional.cosine_similarity(g.double().flatten().cpu(), e.flatten(), dim=0).item()
             assert cos > 0.995, f"{name}: cosine {cos}"
+
+
+def test_many_launches_leave_the_status_word_clean():
+    """The pipelined kernels synchronise their roles through parity barriers with bounded waits: a protocol slip
+    shows as a wait that gives up (status word != 0), typically once in hundreds of launches.  Several hundred
+    forward and backward launches over the shapes that exercise the different walks must leave the word clean."""
+    from white_matter_b200 import _native
+
+    _native.device_status(True)
+    torch.manual_seed(3)
+    shapes = [  # batch, heads, keys, stride, documents
+        (16, 16, 2048, 8, True), (16, 16, 2048, 8, False), (4, 8, 1024, 4, True), (2, 4, 260, 4, False), (2, 4, 4096, 1, False),
+    ]
+    for batch, heads, keys, stride, documents in shapes:
+        q = torch.randn(batch, heads, keys // stride, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        k = torch.randn(batch, heads, keys, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        v = torch.randn_like(k, requires_grad=True)
+        probe = torch.randn_like(q)
+        metas = [None] * stride
+        if documents:
+            docs = geometric_documents(batch, keys, keys // 2, seed=11)
+            groups = [torch.arange(r, keys, stride) for r in range(stride)]
+            metas = [tuple(t.cuda() for t in m) for m in prepare_feedback_metadata(docs, groups, keys, use_dummy_token=False)]
+        for launch in range(60):
+            r = launch % stride
+            out = cyclic_attention(q, k, v, query_stride=stride, query_offset=r, strict_past=True, metadata=metas[r], backend="sm100")
+            torch.autograd.grad(out, (q, k, v), probe)
+        status = _native.device_status(True)
+        assert status == 0, f"shape {(batch, heads, keys, stride, documents)}: wait {status & 255} gave up in block {status >> 8}"
