@@ -437,6 +437,39 @@ def bench_mixing(device, peaks, iters=10):
     }
 
 
+def bench_query_prepare(device, peaks, iters=20):
+    """q_norm + rotary embedding + layout change of the query projection: B=32, T=2048, H=16, D=64 bf16 (134 MB in, 134 MB out: larger than L2)."""
+    from white_matter_b200 import prepare_queries
+
+    batch, tokens, heads, dim = 32, 2048, 16, 64
+    x = torch.randn(batch, tokens, heads * dim, device=device, dtype=torch.bfloat16)
+    weight = torch.ones(dim, device=device, dtype=torch.bfloat16)
+    angles = torch.rand(1, tokens, dim, device=device) * 6.0
+    cos, sin = angles.cos().bfloat16(), angles.sin().bfloat16()
+    call = lambda: prepare_queries(x, weight, cos, sin)
+    # a 40 us kernel: replayed from a CUDA graph so that the operator's host cost does not enter
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            call()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            call()
+    ms = time_steps(graph.replay, 3, 1, torch.cuda.synchronize) / (3 * iters)
+    nbytes = 2 * x.numel() * 2 + 2 * cos.numel() * 2
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {
+        "workload": "query preparation (rms_norm * gain, rotary embedding, BTHD -> BHTD) B=32 T=2048 H=16 D=64 bf16, 268 MB > L2",
+        "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+    }
+
+
 def use_all_host_threads():
     """torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU legs are meant to use every core the process may run on."""
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
@@ -616,6 +649,7 @@ def main():
         extras["decode"], extras["prefill128"] = bench_decode(device, peaks)
         extras["jacobi"] = bench_jacobi(device, peaks)
         extras["mixing"] = bench_mixing(device, peaks)
+        extras["query_prepare"] = bench_query_prepare(device, peaks)
     if rank == 0:
         line = {
             "metric": "cyclic_attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,

@@ -153,6 +153,30 @@ typedef struct wm_mix_args {
   int32_t dtype;
 } wm_mix_args;
 
+/* Query preparation of the attention layer (layers/white_matter.py:105-111 of the reference: q_norm, transpose,
+ * rotary embedding): q[b,h,t,:] = rope(rms_norm(x[b,t,h,:]) * weight).  x has element strides x_strides for
+ * (batch, token, head) and unit stride in head_dim; q is contiguous (batch, heads, tokens, head_dim); cos / sin are
+ * (batch, tokens, head_dim) with element strides cs_strides (a batch stride of 0 broadcasts one table).  weight, cos
+ * and sin have the dtype of x.  The backward call reads dq (layout of q) and writes dx (strides of x) and dweight. */
+typedef struct wm_qprep_args {
+  const void* x;
+  const void* weight; /* (head_dim,) */
+  const void* cos;
+  const void* sin;
+  void* q;            /* forward result */
+  const void* dq;     /* backward input */
+  void* dx;           /* backward result */
+  void* dweight;      /* backward result, (head_dim,) in the dtype of x */
+  void* workspace;    /* backward only: wm_query_prepare_workspace_bytes */
+  size_t workspace_bytes;
+  int64_t x_strides[3];
+  int64_t cs_strides[2];
+  int32_t dtype;   /* of x, weight, cos, sin, dx, dweight */
+  int32_t q_dtype; /* of q and dq: WM_BF16, or WM_F32 when dtype is WM_F32 */
+  int32_t batch, tokens, heads, head_dim; /* head_dim 64 or 128 */
+  float eps;
+} wm_qprep_args;
+
 WM_API int wm_abi_version(void);
 WM_API const char* wm_last_error(void);
 /* Status word of the pipelined kernels on the current device: 0 when every bounded
@@ -177,6 +201,7 @@ WM_API size_t wm_attn_fwd_workspace_bytes(const wm_attn_args* args);
 WM_API size_t wm_attn_bwd_workspace_bytes(const wm_attn_args* args);
 WM_API size_t wm_strict_decode_workspace_bytes(const wm_attn_args* args);
 WM_API size_t wm_mix_workspace_bytes(const wm_mix_args* args);
+WM_API size_t wm_query_prepare_workspace_bytes(const wm_qprep_args* args);
 
 /* cyclic attention without / with document metadata */
 WM_API int wm_cyclic_attn_fwd(const wm_attn_args* args, void* stream);
@@ -213,6 +238,10 @@ WM_API int wm_strict_decode_no_alloc(const wm_attn_args* args, void* stream);
 /* KV source mixing */
 WM_API int wm_mix_sources_fwd(const wm_mix_args* args, void* stream);
 WM_API int wm_mix_sources_bwd(const wm_mix_args* args, void* stream);
+
+/* the step in front of the attention operators inside the attention layer (first of the "next" components) */
+WM_API int wm_query_prepare_fwd(const wm_qprep_args* args, void* stream);
+WM_API int wm_query_prepare_bwd(const wm_qprep_args* args, void* stream);
 
 #ifdef __cplusplus
 }

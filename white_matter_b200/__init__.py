@@ -12,10 +12,13 @@ from .metadata import (
     prepare_feedback_metadata,
     prepare_strict_causal_metadata,
 )
+from .layer import cyclic_attention_layer, prepare_queries
 from .mixing import mix_kv_sources
 from .strict import strict_causal_attention
 
 __all__ = [
+    "prepare_queries",
+    "cyclic_attention_layer",
     "StrictCausalMetadata",
     "prepare_strict_causal_metadata",
     "strict_causal_attention",

@@ -97,6 +97,32 @@ class MixArgs(ctypes.Structure):
     ]
 
 
+class QueryPrepArgs(ctypes.Structure):
+    """Mirror of ``wm_qprep_args``."""
+
+    _fields_ = [
+        ("x", ctypes.c_void_p),
+        ("weight", ctypes.c_void_p),
+        ("cos", ctypes.c_void_p),
+        ("sin", ctypes.c_void_p),
+        ("q", ctypes.c_void_p),
+        ("dq", ctypes.c_void_p),
+        ("dx", ctypes.c_void_p),
+        ("dweight", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+        ("x_strides", ctypes.c_int64 * 3),
+        ("cs_strides", ctypes.c_int64 * 2),
+        ("dtype", ctypes.c_int32),
+        ("q_dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("tokens", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("eps", ctypes.c_float),
+    ]
+
+
 ATTN_ENTRY_POINTS = (
     "wm_cyclic_attn_fwd",
     "wm_cyclic_attn_bwd",
@@ -110,6 +136,7 @@ ATTN_ENTRY_POINTS = (
     "wm_strict_decode_no_alloc",
 )
 MIX_ENTRY_POINTS = ("wm_mix_sources_fwd", "wm_mix_sources_bwd")
+QUERY_PREP_ENTRY_POINTS = ("wm_query_prepare_fwd", "wm_query_prepare_bwd")
 QUERY_ENTRY_POINTS = (
     "wm_abi_version",
     "wm_last_error",
@@ -120,6 +147,7 @@ QUERY_ENTRY_POINTS = (
     "wm_attn_bwd_workspace_bytes",
     "wm_strict_decode_workspace_bytes",
     "wm_mix_workspace_bytes",
+    "wm_query_prepare_workspace_bytes",
 )
 
 _lock = threading.Lock()
@@ -148,6 +176,12 @@ def load_library() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.argtypes = [ctypes.POINTER(MixArgs), ctypes.c_void_p]
             fn.restype = ctypes.c_int
+        for name in QUERY_PREP_ENTRY_POINTS:
+            fn = getattr(lib, name)
+            fn.argtypes = [ctypes.POINTER(QueryPrepArgs), ctypes.c_void_p]
+            fn.restype = ctypes.c_int
+        lib.wm_query_prepare_workspace_bytes.argtypes = [ctypes.POINTER(QueryPrepArgs)]
+        lib.wm_query_prepare_workspace_bytes.restype = ctypes.c_size_t
         lib.wm_abi_version.argtypes = []
         lib.wm_abi_version.restype = ctypes.c_int
         lib.wm_last_error.argtypes = []

@@ -145,6 +145,8 @@ size_t wm_strict_decode_workspace_bytes(const wm_attn_args* a) { return a ? wm::
 
 size_t wm_mix_workspace_bytes(const wm_mix_args* a) { return a ? wm::mix_workspace(*a) : 0; }
 
+size_t wm_query_prepare_workspace_bytes(const wm_qprep_args* a) { return a ? wm::query_prepare_workspace(*a) : 0; }
+
 int wm_cyclic_attn_fwd(const wm_attn_args* a, void* stream) {
   return wm::run_fwd(a, stream, WM_MASK_CYCLIC, false, "wm_cyclic_attn_fwd");
 }
@@ -209,6 +211,16 @@ int wm_mix_sources_fwd(const wm_mix_args* a, void* stream) {
 int wm_mix_sources_bwd(const wm_mix_args* a, void* stream) {
   if (a == nullptr) return wm::fail(WM_EINVAL, "wm_mix_sources_bwd: null arguments");
   return wm::mix_bwd_launch(*a, static_cast<cudaStream_t>(stream));
+}
+
+int wm_query_prepare_fwd(const wm_qprep_args* a, void* stream) {
+  if (a == nullptr) return wm::fail(WM_EINVAL, "wm_query_prepare_fwd: null arguments");
+  return wm::query_prepare(*a, false, static_cast<cudaStream_t>(stream));
+}
+
+int wm_query_prepare_bwd(const wm_qprep_args* a, void* stream) {
+  if (a == nullptr) return wm::fail(WM_EINVAL, "wm_query_prepare_bwd: null arguments");
+  return wm::query_prepare(*a, true, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -44,6 +44,8 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream);
 size_t tc_attn_bwd_workspace(const wm_attn_args& a);
 int tc_device_status(bool reset);
 int tc_debug_trace(long long* out, int capacity, int arm_after);
+int query_prepare(const wm_qprep_args& a, bool backward, cudaStream_t stream);
+size_t query_prepare_workspace(const wm_qprep_args& a);
 
 // ---------------------------------------------------------------- device side
 constexpr float kLog2e = 1.4426950408889634f;

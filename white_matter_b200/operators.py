@@ -581,6 +581,99 @@ def _mix_backward(ctx, dout):
 mix_sources.register_autograd(_mix_backward, setup_context=_mix_setup)
 
 
+# ---------------------------------------------------------------------------
+# query preparation of the attention layer: rms_norm * gain, rotary embedding, (B,T,H,D) -> (B,H,T,D)
+
+
+def _qprep_args(x: Tensor, weight: Tensor, cos: Tensor, sin: Tensor, eps: float, q_dtype: torch.dtype) -> "_native.QueryPrepArgs":
+    a = _native.QueryPrepArgs()
+    a.x = x.data_ptr()
+    a.weight = weight.data_ptr()
+    a.cos = cos.data_ptr()
+    a.sin = sin.data_ptr()
+    a.x_strides = (ctypes.c_int64 * 3)(x.stride(0), x.stride(1), x.stride(2))
+    a.cs_strides = (ctypes.c_int64 * 2)(cos.stride(0) if cos.shape[0] > 1 else 0, cos.stride(1))
+    a.dtype = _native.dtype_code(x.dtype)
+    a.q_dtype = _native.dtype_code(q_dtype)
+    a.batch, a.tokens, a.heads, a.head_dim = x.shape
+    a.eps = float(eps)
+    return a
+
+
+def _qprep_inputs(x: Tensor, weight: Tensor, cos: Tensor, sin: Tensor):
+    if x.stride(-1) != 1 or any(st % 2 for st in x.stride()[:3]):
+        x = x.contiguous()
+    weight = weight.to(x.dtype).contiguous()
+    cos = cos.to(x.dtype)
+    sin = sin.to(x.dtype)
+    if cos.stride(-1) != 1 or cos.stride(1) % 2 or cos.stride(0) % 2:
+        cos = cos.contiguous()
+    if sin.stride() != cos.stride():
+        sin = sin.contiguous()
+        cos = cos.contiguous()
+    return x, weight, cos, sin
+
+
+@torch.library.custom_op("wm_b200::query_prepare", mutates_args=())
+def query_prepare(x: Tensor, weight: Tensor, cos: Tensor, sin: Tensor, eps: float, to_bf16: bool) -> Tensor:
+    """x (B,T,H,D), weight (D,), cos/sin (B|1,T,D) -> q (B,H,T,D) = rope(rms_norm(x) * weight)."""
+    x, weight, cos, sin = _qprep_inputs(x, weight, cos, sin)
+    q_dtype = torch.bfloat16 if to_bf16 else x.dtype
+    b, t, h, d = x.shape
+    q = torch.empty((b, h, t, d), dtype=q_dtype, device=x.device)
+    a = _qprep_args(x, weight, cos, sin, eps, q_dtype)
+    a.q = q.data_ptr()
+    _native.call("wm_query_prepare_fwd", a, x.device)
+    return q
+
+
+@query_prepare.register_fake
+def _(x, weight, cos, sin, eps, to_bf16):
+    b, t, h, d = x.shape
+    return torch.empty((b, h, t, d), dtype=torch.bfloat16 if to_bf16 else x.dtype, device=x.device)
+
+
+@torch.library.custom_op("wm_b200::query_prepare_bwd", mutates_args=())
+def query_prepare_bwd(x: Tensor, weight: Tensor, cos: Tensor, sin: Tensor, dq: Tensor, eps: float) -> tuple[Tensor, Tensor]:
+    x, weight, cos, sin = _qprep_inputs(x, weight, cos, sin)
+    dq = dq.contiguous()
+    dx = torch.empty_like(x)
+    if dx.stride() != x.stride():
+        x = x.contiguous()
+        dx = torch.empty_like(x)
+    dweight = torch.empty_like(weight)
+    a = _qprep_args(x, weight, cos, sin, eps, dq.dtype)
+    a.dq = dq.data_ptr()
+    a.dx = dx.data_ptr()
+    a.dweight = dweight.data_ptr()
+    nbytes = _native.load_library().wm_query_prepare_workspace_bytes(ctypes.byref(a))
+    ws = _attach_workspace(a, nbytes, x.device)
+    _native.call("wm_query_prepare_bwd", a, x.device)
+    del ws
+    return dx, dweight
+
+
+@query_prepare_bwd.register_fake
+def _(x, weight, cos, sin, dq, eps):
+    return torch.empty_like(x), torch.empty_like(weight, dtype=x.dtype)
+
+
+def _qprep_setup(ctx, inputs, output):
+    x, weight, cos, sin, eps, _ = inputs
+    ctx.save_for_backward(x, weight, cos, sin)
+    ctx.eps = eps
+    ctx.weight_dtype = weight.dtype
+
+
+def _qprep_backward(ctx, dq):
+    x, weight, cos, sin = ctx.saved_tensors
+    dx, dweight = query_prepare_bwd(x, weight, cos, sin, dq, ctx.eps)
+    return dx, dweight.to(ctx.weight_dtype), None, None, None, None
+
+
+query_prepare.register_autograd(_qprep_backward, setup_context=_qprep_setup)
+
+
 def strict_decode_no_alloc(
     Q: Tensor,
     K: Tensor,
