@@ -47,6 +47,7 @@ NCU_TRAFFIC_BYTES = {
     "attn_fwd_tc_kernel": 185.2e6,
     "decode_split_kernel": 1086.4e6,
     "mix_fwd_kernel": 432.8e6,
+    "query_prepare_fwd_bf16_kernel": 226.7e6,
 }
 
 
@@ -466,7 +467,7 @@ def bench_query_prepare(device, peaks, iters=20):
         "workload": "query preparation (rms_norm * gain, rotary embedding, BTHD -> BHTD) B=32 T=2048 H=16 D=64 bf16, 268 MB > L2",
         "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": gbs / peaks["hbm_gbs"], "traffic": None},
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["query_prepare_fwd_bf16_kernel"]},
     }
 
 

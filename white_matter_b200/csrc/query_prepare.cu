@@ -57,6 +57,84 @@ __device__ __forceinline__ bool low_half(int lane, int g) {
   return G == 1 ? lane < 16 : g == 0;
 }
 
+// Forward for bf16 input and output: a lane holds 8 adjacent elements (one 16-byte access), a head takes D/8 lanes
+// and a warp 32/(D/8) heads of its token at a time; the rotary partner is the lane D/16 further on.  Four times
+// fewer memory instructions and shuffles per element than the two-element mapping below, which it replaces
+// whenever the strides allow 16-byte accesses (the kernel is bound by instruction issue otherwise).
+template <int D>
+__global__ void __launch_bounds__(kThreads) query_prepare_fwd_bf16_kernel(const wm_qprep_args a) {
+  constexpr int kLanes = D / 8;        // lanes per head
+  constexpr int kHeads = 32 / kLanes;  // heads per warp pass
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % kLanes, slot = lane / kLanes;
+  const int t = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int b = blockIdx.y;
+  if (t >= a.tokens) return;
+  auto unpack8 = [](const uint4& r, float (&x)[8]) {
+    const unsigned w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[2 * i] = __uint_as_float(w[i] << 16);
+      x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  };
+  const __nv_bfloat16* cs = static_cast<const __nv_bfloat16*>(a.cos) + b * a.cs_strides[0] + static_cast<long long>(t) * a.cs_strides[1];
+  const __nv_bfloat16* sn = static_cast<const __nv_bfloat16*>(a.sin) + b * a.cs_strides[0] + static_cast<long long>(t) * a.cs_strides[1];
+  const __nv_bfloat16* wt = static_cast<const __nv_bfloat16*>(a.weight);
+  const int partner_sub = sub ^ (kLanes / 2);
+  float c[8], s[8], w[8], wp[8];
+  unpack8(*reinterpret_cast<const uint4*>(cs + 8 * sub), c);
+  unpack8(*reinterpret_cast<const uint4*>(sn + 8 * sub), s);
+  unpack8(*reinterpret_cast<const uint4*>(wt + 8 * sub), w);
+  unpack8(*reinterpret_cast<const uint4*>(wt + 8 * partner_sub), wp);
+  const float sign = sub < kLanes / 2 ? -1.f : 1.f;  // rot(y)[d] = -y[d + D/2] in the first half
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    s[i] *= sign;
+    wp[i] *= s[i];  // partner gain and (signed) sine in one factor
+    w[i] *= c[i];   // own gain and cosine in one factor
+  }
+  const __nv_bfloat16* x_tok = static_cast<const __nv_bfloat16*>(a.x) + b * a.x_strides[0] + static_cast<long long>(t) * a.x_strides[1];
+  __nv_bfloat16* q_tok = static_cast<__nv_bfloat16*>(a.q) + (static_cast<long long>(b) * a.heads * a.tokens + t) * D;
+  constexpr int kBatch = 2;  // warp passes whose loads are issued together
+  for (int h0 = 0; h0 < a.heads; h0 += kBatch * kHeads) {
+    uint4 raw[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int h = h0 + i * kHeads + slot;
+      raw[i] = h < a.heads ? *reinterpret_cast<const uint4*>(x_tok + h * a.x_strides[2] + 8 * sub) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int h = h0 + i * kHeads + slot;
+      float x[8], xp[8];
+      unpack8(raw[i], x);
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+#pragma unroll
+      for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float r = rsqrtf(ss * (1.f / D) + a.eps);
+      uint4 other;
+      other.x = __shfl_xor_sync(0xffffffffu, raw[i].x, kLanes / 2);
+      other.y = __shfl_xor_sync(0xffffffffu, raw[i].y, kLanes / 2);
+      other.z = __shfl_xor_sync(0xffffffffu, raw[i].z, kLanes / 2);
+      other.w = __shfl_xor_sync(0xffffffffu, raw[i].w, kLanes / 2);
+      unpack8(other, xp);
+      unsigned out[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = r * fmaf(x[2 * e], w[2 * e], xp[2 * e] * wp[2 * e]);
+        const float hi = r * fmaf(x[2 * e + 1], w[2 * e + 1], xp[2 * e + 1] * wp[2 * e + 1]);
+        __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+        out[e] = *reinterpret_cast<unsigned*>(&pk);
+      }
+      if (h < a.heads)
+        *reinterpret_cast<uint4*>(q_tok + static_cast<long long>(h) * a.tokens * D + 8 * sub) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+  }
+}
+
 template <typename TX, typename TQ, int G>
 __global__ void __launch_bounds__(kThreads) query_prepare_fwd_kernel(const wm_qprep_args a) {
   const int lane = threadIdx.x & 31;
@@ -238,6 +316,16 @@ template <typename TX, typename TQ, int G>
 static int launch(const wm_qprep_args& a, bool backward, cudaStream_t stream) {
   dim3 grid((a.tokens + kThreads / 32 - 1) / (kThreads / 32), a.batch);
   if (!backward) {
+    const bool wide = a.dtype == WM_BF16 && a.q_dtype == WM_BF16 && a.x_strides[0] % 8 == 0 && a.x_strides[1] % 8 == 0 &&
+                      a.x_strides[2] % 8 == 0 && a.cs_strides[0] % 8 == 0 && a.cs_strides[1] % 8 == 0 &&
+                      reinterpret_cast<uintptr_t>(a.x) % 16 == 0 && reinterpret_cast<uintptr_t>(a.q) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(a.cos) % 16 == 0 && reinterpret_cast<uintptr_t>(a.sin) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(a.weight) % 16 == 0;
+    if (wide) {
+      query_prepare_fwd_bf16_kernel<64 * G><<<grid, kThreads, 0, stream>>>(a);
+      count_launch();
+      return cuda_check(cudaGetLastError(), "query_prepare_fwd_bf16_kernel");
+    }
     query_prepare_fwd_kernel<TX, TQ, G><<<grid, kThreads, 0, stream>>>(a);
     count_launch();
     return cuda_check(cudaGetLastError(), "query_prepare_fwd_kernel");
