@@ -84,6 +84,7 @@ __device__ __forceinline__ void value_mma_role(Shared& sm, uint32_t tmem, const 
     const int b = n & 1;
     const int s = n % kStages;
     if (!wait_or_abort(sm, &sm.p_full[b], (n >> 1) & 1, 22)) return;
+    ptx::mbar_arrive(&sm.p_seen[b]);  // this phase of p_full has been consumed: the group may complete the next one
     trace_event(sm, 300 + n);
     if (!wait_or_abort(sm, &sm.v_full[s], (n / kStages) & 1, 23)) return;
     ptx::tc_fence_after();
@@ -110,7 +111,7 @@ struct FwdShared {
   uint64_t q_full;
   // s_full[i] and pv_done[i] also release K and V stage i (score buffers and stages share the ring size)
   uint64_t k_full[kStages], v_full[kStages];
-  uint64_t s_full[kScoreBuffers], pv_done[kStages], p_full[2], docs_full[2], sum_full;
+  uint64_t s_full[kScoreBuffers], pv_done[kStages], p_full[2], p_seen[2], docs_full[2], sum_full;
   int key_seg[2][2][kTileN];  // [group][tile of the group & 1]
   int key_end[2][2][kTileN];
   int tile_summary[2][2][4][3];
@@ -167,11 +168,6 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     // has arrived for the previous one, and its second arrival would complete that phase early: the previous
     // phase of p_full has to be over before anybody works towards the next arrival.
     if (it >= 1 && !wait_or_abort(sm, &sm.p_full[b], (it - 1) & 1, 40)) return;
-    // The PV issuer reads p_full by parity: the group must not complete the phase of this tile before the issuer
-    // has consumed the phase of the group's previous tile, or the issuer, late by whatever the scheduler does to
-    // a single-lane role, would see an unfinished phase of the same parity and wait for ever.  The PV product of
-    // the previous tile being complete proves that it has.
-    if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return;
     const int sb = n % kScoreBuffers;
     const int j0 = tile_first_key(n, w.first_tile, w.dummy_tile);
     int cls = !live || j0 >= rb.hi ? kTileNone : (j0 + kTileN <= rb.hi ? kTileFull : kTileCausal);
@@ -235,7 +231,8 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     // multiply this group's accumulator by `factor` (1 for rows that did not move); the accumulator was last
     // written by the PV product of the group's previous tile
     auto rescale_output = [&](float factor) -> bool {
-      ptx::tc_fence_after();  // (the PV product of the group's previous tile is complete: waited for at the top of the tile)
+      if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return false;
+      ptx::tc_fence_after();
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t raw[32];
@@ -405,6 +402,11 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       ptx::fence_async_shared();
     }
     ptx::tc_fence_before();
+    // The PV issuer reads p_full by parity: the group must not complete this tile's phase before the issuer has
+    // consumed the phase of the group's previous tile, or the issuer, late by whatever the scheduler does to a
+    // single-lane role, would see an unfinished phase of the same parity and wait for ever.  The issuer
+    // acknowledges every phase it consumes on p_seen; by now that acknowledgement is long there.
+    if (it >= 1 && !wait_or_abort(sm, &sm.p_seen[b], (it - 1) & 1, 42)) return;
     ptx::mbar_arrive(&sm.p_full[b]);
     WM_TRACE(1000 + n);
   }
@@ -486,6 +488,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&sm.p_full[b], kFwdGroup);
+      ptx::mbar_init(&sm.p_seen[b], 1);
       ptx::mbar_init(&sm.docs_full[b], kFwdGroup);
     }
     ptx::mbar_init(&sm.sum_full, kFwdSoftmax);
