@@ -458,6 +458,9 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
       ptx::tmem_wait_ld();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&sm.sdp_free);  // all scores are in registers: S/dP of the next pair may be issued
+      // the store that left shared memory during the previous pair has read it by now: hand its room back without
+      // having made anybody wait for it
+      release();
       if (tid == 0) trace_event(sm, 800 + it);
       math(xs, ys, causal_mask(half * 64 + 32) & dm_hi, pp1, dd1);
       if (tid == 0) trace_event(sm, 900 + it);
@@ -478,7 +481,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     ptx::tc_fence_before();
     ptx::mbar_arrive(&sm.pds_full);
     if (tid == 0) trace_event(sm, 1000 + it);
-    release();
+    if (e.last && release_stage >= 0) release();  // the next key tile is waiting for this K/V stage: no deferral
     if (e.last && it + 1 < n && !prepare(resident_iter(sm.sched[it + 1]))) return;
     if (e.last) {
       pending_kt = e.kt;
@@ -486,6 +489,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     }
   }
   if (n > 0) {
+    release();
     if (!wait_or_abort(sm, &sm.mma_done, (n - 1) & 1, 94)) return;
     ptx::tc_fence_after();
     if (pending_kt >= 0 && !stage_out(pending_kt, pending_stage, n, true)) return;
