@@ -164,10 +164,6 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
 
   for (int n = grp; n < w.n_tiles; n += 2) {
     const int it = n >> 1;  // tiles this group has finished
-    // A warp that needs nothing from a tile (nothing visible) could finish it before a slower warp of the group
-    // has arrived for the previous one, and its second arrival would complete that phase early: the previous
-    // phase of p_full has to be over before anybody works towards the next arrival.
-    if (it >= 1 && !wait_or_abort(sm, &sm.p_full[b], (it - 1) & 1, 40)) return;
     const int sb = n % kScoreBuffers;
     const int j0 = tile_first_key(n, w.first_tile, w.dummy_tile);
     int cls = !live || j0 >= rb.hi ? kTileNone : (j0 + kTileN <= rb.hi ? kTileFull : kTileCausal);
@@ -405,7 +401,10 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     // The PV issuer reads p_full by parity: the group must not complete this tile's phase before the issuer has
     // consumed the phase of the group's previous tile, or the issuer, late by whatever the scheduler does to a
     // single-lane role, would see an unfinished phase of the same parity and wait for ever.  The issuer
-    // acknowledges every phase it consumes on p_seen; by now that acknowledgement is long there.
+    // acknowledges every phase it consumes on p_seen; by now that acknowledgement is long there.  The same wait
+    // keeps a warp with nothing to do in a tile from arriving twice in one phase (the acknowledgement of a
+    // phase implies that all 128 threads have arrived for it), and with it every thread of the group has left
+    // the tile before the previous one when a thread starts a tile (the document tables are double-buffered).
     if (it >= 1 && !wait_or_abort(sm, &sm.p_seen[b], (it - 1) & 1, 42)) return;
     ptx::mbar_arrive(&sm.p_full[b]);
     WM_TRACE(1000 + n);
