@@ -5,10 +5,14 @@
 // 64 KB) and their dQ accumulators (TMEM) resident and walks over the key tiles: dK and dV of a
 // key tile are complete inside the block and leave through one TMA store each, dQ is written
 // once at the end -- no atomics, no fp32 scratch, no conversion pass.  K and V tiles stream
-// through a two-stage TMA ring.
+// through a two-stage TMA ring; once the first query tile has no pair left (or when there is only
+// one query tile), the Q / dO room of the idle query tile joins the ring as a third stage, which
+// is what lets the S / dP products of key tiles seen by one query tile only be issued while the
+// pair before them is still being computed.
 //
-// 352 threads: warps 0-7 compute (thread = query row (tid & 127), column half (tid >> 7) of the
-// 128-key tile), warp 8 TMA producer, warps 9 and 10 MMA issuers (S/dP products, gradient products).
+// 384 threads: warps 0-7 compute (thread = query row (tid & 127), column half (tid >> 7) of the
+// 128-key tile), warp 8 TMA producer, warps 9 and 10 MMA issuers (S/dP products, gradient products), warp 11
+// stores finished dK / dV tiles and hands their stage back.
 // TMEM: S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ0 [384,448) dQ1 [448,512).
 //
 // An iteration is one (key tile, query tile) pair; the list of visible pairs is built once per
@@ -18,7 +22,7 @@
 // after the dV/dK/dQ products of iteration i-1 have read the previous contents (mma_done).
 #pragma once
 
-constexpr int kResidentThreads = 352;
+constexpr int kResidentThreads = 384;
 constexpr int kResidentCompute = 256;
 
 
@@ -34,34 +38,10 @@ struct ResidentWalk {
 __device__ __forceinline__ bool pair_visible(const ResidentWalk& w, int kt, int qt) {
   if (qt >= w.nq) return false;
   const int j0 = kt * kTileN;
-  if (j0 >= w.hi_max[qt]) return false;
-  if (w.docs && j0 + kTileN - 1 < w.lo_min[qt] && !(w.dummy && kt == 0)) return false;
+  const int hi = qt ? w.hi_max[1] : w.hi_max[0], lo = qt ? w.lo_min[1] : w.lo_min[0];
+  if (j0 >= hi) return false;
+  if (w.docs && j0 + kTileN - 1 < lo && !(w.dummy && kt == 0)) return false;
   return true;
-}
-
-template <class Shared>
-__device__ __forceinline__ void resident_producer(Shared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
-                                              const CUtensorMap* map_v, const CUtensorMap* map_g, const ResidentWalk& w,
-                                              int head, int batch) {
-  ptx::prefetch_tmap(map_q);
-  ptx::prefetch_tmap(map_k);
-  ptx::prefetch_tmap(map_v);
-  ptx::prefetch_tmap(map_g);
-  ptx::mbar_expect_tx(&sm.qg_full, 2 * w.nq * kTileBytes);
-  for (int qt = 0; qt < w.nq; ++qt) {
-    ptx::tma_load_4d(sm.q[qt], map_q, &sm.qg_full, 0, qt * kTileM, head, batch);
-    ptx::tma_load_4d(sm.g[qt], map_g, &sm.qg_full, 0, qt * kTileM, head, batch);
-  }
-  int active = 0;
-  for (int kt = 0; kt < w.n_kt; ++kt) {
-    if (!pair_visible(w, kt, 0) && !pair_visible(w, kt, 1)) continue;
-    const int s = active & 1;
-    if (!wait_or_abort(sm, &sm.kv_empty[s], ((active >> 1) & 1) ^ 1, 71)) return;
-    ptx::mbar_expect_tx(&sm.kv_full[s], 2 * kTileBytes);
-    ptx::tma_load_4d(sm.k[s], map_k, &sm.kv_full[s], 0, kt * kTileN, head, batch);
-    ptx::tma_load_4d(sm.v[s], map_v, &sm.kv_full[s], 0, kt * kTileN, head, batch);
-    ++active;
-  }
 }
 
 // dV (half 0) or dK (half 1) rows of key tile `kt`: TMEM -> bf16 -> global, one key row per thread
@@ -105,18 +85,20 @@ struct ResidentShared {
   unsigned char p[2 * kTileBytes];
   unsigned char ds[2 * kTileBytes];
   uint64_t qg_full;
-  uint64_t kv_full[2], kv_ready[2], kv_empty[2];
+  uint64_t kv_full[3], kv_ready[3], kv_empty[3];
   uint64_t sdp_full, sdp_free, pds_full, mma_done;
   uint64_t out_full[2];  // dV (half 0) / dK (half 1) rows of a finished key tile are staged in shared memory
-  uint64_t stage_free[2];  // the store out of the spare staging room has read it
-  int key_seg[2][kTileN];
-  int key_end[2][kTileN];
-  int summary[2][4][3];
+  uint64_t out_seen;     // the storing thread has taken note of both
+  int key_seg[3][kTileN];
+  int key_end[3][kTileN];
+  int summary[3][4][3];
   int lo_min[2], hi_max[2];
   int has_dummy;
-  // iteration list: key tile | query tile << 12 | first-of-key-tile << 13 | last-of-key-tile << 14 | visited index << 16
+  // iteration list: key tile | query tile << 12 | first-of-key-tile << 13 | last-of-key-tile << 14 | K/V stage << 15 |
+  // parity of this use of the stage (kv_full, kv_ready) << 17 | parity the producer waits for on kv_empty << 18
   uint32_t sched[kResidentMaxIter];
   int n_iter;
+  int n_visited;     // key tiles on the list
   int q0_last_iter;  // last iteration that uses query tile 0 (-1: none)
   uint32_t tmem_base;
   int abort_flag;
@@ -125,7 +107,7 @@ struct ResidentShared {
 };
 
 struct ResidentIter {
-  int kt, qt, first, last, active;
+  int kt, qt, first, last, stage, parity, empty_parity;
 };
 
 __device__ __forceinline__ ResidentIter resident_iter(uint32_t e) {
@@ -134,15 +116,64 @@ __device__ __forceinline__ ResidentIter resident_iter(uint32_t e) {
   it.qt = (e >> 12) & 1;
   it.first = (e >> 13) & 1;
   it.last = (e >> 14) & 1;
-  it.active = e >> 16;
+  it.stage = (e >> 15) & 3;
+  it.parity = (e >> 17) & 1;
+  it.empty_parity = (e >> 18) & 1;
   return it;
 }
 
-__device__ __forceinline__ void resident_issue_sdp(ResidentShared& sm, uint32_t tmem, const ResidentIter& e) {
+// K / V room of a stage: stages 0 and 1 are the ring's own, stage 2 is the Q / dO room of the idle query tile
+// (query tile 1 when the tensor has only one, else query tile 0 once it has no pair left)
+template <class Shared>
+__device__ __forceinline__ unsigned char* resident_k_stage(Shared& sm, int stage, int nq) {
+  return stage < 2 ? sm.k[stage] : sm.q[nq == 1 ? 1 : 0];
+}
+template <class Shared>
+__device__ __forceinline__ unsigned char* resident_v_stage(Shared& sm, int stage, int nq) {
+  return stage < 2 ? sm.v[stage] : sm.g[nq == 1 ? 1 : 0];
+}
+
+// Q and dO of the block's query tiles: they depend on nothing the block works out first, so they are on their way
+// while the row bounds and the iteration list are still being made.
+template <class Shared>
+__device__ __forceinline__ void resident_load_queries(Shared& sm, const CUtensorMap* map_q, const CUtensorMap* map_g, int nq,
+                                                  int head, int batch) {
+  ptx::prefetch_tmap(map_q);
+  ptx::prefetch_tmap(map_g);
+  ptx::mbar_expect_tx(&sm.qg_full, 2 * nq * kTileBytes);
+  for (int qt = 0; qt < nq; ++qt) {
+    ptx::tma_load_4d(sm.q[qt], map_q, &sm.qg_full, 0, qt * kTileM, head, batch);
+    ptx::tma_load_4d(sm.g[qt], map_g, &sm.qg_full, 0, qt * kTileM, head, batch);
+  }
+}
+
+template <class Shared>
+__device__ __forceinline__ void resident_producer(Shared& sm, const CUtensorMap* map_k, const CUtensorMap* map_v,
+                                              const ResidentWalk& w, int head, int batch) {
+  ptx::prefetch_tmap(map_k);
+  ptx::prefetch_tmap(map_v);
+  const int n = sm.n_iter;
+  bool third_checked = false;
+  for (int it = 0; it < n; ++it) {
+    const ResidentIter e = resident_iter(sm.sched[it]);
+    if (!e.first) continue;
+    // the third stage is the room of a query tile: whatever was loaded there at the start has to have landed
+    if (e.stage == 2 && !third_checked) {
+      if (!wait_or_abort(sm, &sm.qg_full, 0, 72)) return;
+      third_checked = true;
+    }
+    if (!wait_or_abort(sm, &sm.kv_empty[e.stage], e.empty_parity, 71)) return;
+    ptx::mbar_expect_tx(&sm.kv_full[e.stage], 2 * kTileBytes);
+    ptx::tma_load_4d(resident_k_stage(sm, e.stage, w.nq), map_k, &sm.kv_full[e.stage], 0, e.kt * kTileN, head, batch);
+    ptx::tma_load_4d(resident_v_stage(sm, e.stage, w.nq), map_v, &sm.kv_full[e.stage], 0, e.kt * kTileN, head, batch);
+  }
+}
+
+__device__ __forceinline__ void resident_issue_sdp(ResidentShared& sm, uint32_t tmem, const ResidentIter& e, int nq) {
   constexpr uint32_t idesc_s = ptx::make_idesc_bf16(kTileM, kTileN, 0, 0);
-  const int s = e.active & 1;
   const uint32_t q_base = ptx::smem_u32(sm.q[e.qt]), g_base = ptx::smem_u32(sm.g[e.qt]);
-  const uint32_t k_base = ptx::smem_u32(sm.k[s]), v_base = ptx::smem_u32(sm.v[s]);
+  const uint32_t k_base = ptx::smem_u32(resident_k_stage(sm, e.stage, nq));
+  const uint32_t v_base = ptx::smem_u32(resident_v_stage(sm, e.stage, nq));
 #pragma unroll
   for (int kk = 0; kk < kHeadDim / 16; ++kk)
     ptx::mma_bf16_ss(tmem, ptx::make_smem_desc_sw128(q_base + kk * 32, 16, 1024),
@@ -158,7 +189,7 @@ __device__ __forceinline__ void resident_issue_sdp(ResidentShared& sm, uint32_t 
 // the issuing thread is busy for as long as its products run: one thread issues the S / dP products as soon as
 // the compute warps hold the previous pair in registers, the other the three gradient products of a pair as soon
 // as its P / dS are in shared memory; the waits of one never sit in front of the other's issue.
-__device__ __forceinline__ void resident_mma_scores(ResidentShared& sm, uint32_t tmem) {
+__device__ __forceinline__ void resident_mma_scores(ResidentShared& sm, uint32_t tmem, int nq, int kvis) {
   const int n = sm.n_iter;
   if (n == 0) return;
   if (!wait_or_abort(sm, &sm.qg_full, 0, 80)) return;
@@ -166,10 +197,15 @@ __device__ __forceinline__ void resident_mma_scores(ResidentShared& sm, uint32_t
     const ResidentIter e = resident_iter(sm.sched[it]);
     // S/dP of the previous pair are in the compute warps' registers: this pair may overwrite them
     if (it > 0 && !wait_or_abort(sm, &sm.sdp_free, (it - 1) & 1, 83)) return;
-    if (e.first && !wait_or_abort(sm, &sm.kv_ready[e.active & 1], (e.active >> 1) & 1, 81)) return;
+    // K and V straight from the TMA are good enough for these products, so a key tile does not wait for the
+    // compute warps to get round to it -- unless they have rows to clear in it (keys behind the last visible one)
+    if (e.first) {
+      const bool cleared = e.kt * kTileN + kTileN > kvis;
+      if (!wait_or_abort(sm, cleared ? &sm.kv_ready[e.stage] : &sm.kv_full[e.stage], e.parity, 81)) return;
+    }
     ptx::tc_fence_after();
     trace_event(sm, 100 + it);
-    resident_issue_sdp(sm, tmem, e);
+    resident_issue_sdp(sm, tmem, e, nq);
     trace_event(sm, 200 + it);
   }
 }
@@ -177,7 +213,6 @@ __device__ __forceinline__ void resident_mma_scores(ResidentShared& sm, uint32_t
 __device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t tmem, int nq) {
   const int n = sm.n_iter;
   if (n == 0) return;
-  const int spare_from = nq == 1 ? 0 : sm.q0_last_iter + 1;  // same rule as the compute warps' staging
   if (!wait_or_abort(sm, &sm.qg_full, 0, 84)) return;
   constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, kHeadDim, 1, 1);
   constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);
@@ -188,9 +223,8 @@ __device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t 
     if (!wait_or_abort(sm, &sm.pds_full, it & 1, 82)) return;
     ptx::tc_fence_after();
     trace_event(sm, 300 + it);
-    const int s = e.active & 1;
     const uint32_t q_base = ptx::smem_u32(sm.q[e.qt]), g_base = ptx::smem_u32(sm.g[e.qt]);
-    const uint32_t k_base = ptx::smem_u32(sm.k[s]);
+    const uint32_t k_base = ptx::smem_u32(resident_k_stage(sm, e.stage, nq));
     const bool acc_kv = !e.first;
     const bool acc_q = e.qt ? dq_started[1] : dq_started[0];
 #pragma unroll
@@ -208,19 +242,42 @@ __device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t 
                        ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, acc_q || (kk > 0));
     if (e.qt) dq_started[1] = true; else dq_started[0] = true;
     ptx::mma_commit(&sm.mma_done);
-    if (e.last && it + 1 >= spare_from) {
-      // the gradients of this key tile will be staged in spare room: its K/V stage is free as soon as these
-      // products are complete (two arrivals, as many as the staging threads give when they release a stage)
-      ptx::mma_commit(&sm.kv_empty[s]);
-      ptx::mma_commit(&sm.kv_empty[s]);
+    if (nq > 1 && it == sm.q0_last_iter) {
+      // these were the last products that read Q / dO of the first query tile: once they are complete its room
+      // is the ring's third stage
+      ptx::mma_commit(&sm.kv_empty[2]);
     }
     trace_event(sm, 400 + it);
   }
 }
 
+// One thread stores the finished dV / dK tiles: it waits until the compute warps have staged both halves of a
+// key tile, issues the two TMA stores, and gives the K/V stage back to the producer as soon as the stores have
+// read it, so nobody who has math to do waits for that.
+__device__ __forceinline__ void resident_store(ResidentShared& sm, const CUtensorMap* map_dk, const CUtensorMap* map_dv,
+                                           int nq, int head, int batch) {
+  ptx::prefetch_tmap(map_dk);
+  ptx::prefetch_tmap(map_dv);
+  const int n = sm.n_iter;
+  int tiles = 0;
+  for (int it = 0; it < n; ++it) {
+    const ResidentIter e = resident_iter(sm.sched[it]);
+    if (!e.last) continue;
+    if (!wait_or_abort(sm, &sm.out_full[0], tiles & 1, 97)) return;
+    if (!wait_or_abort(sm, &sm.out_full[1], tiles & 1, 98)) return;
+    ptx::mbar_arrive(&sm.out_seen);
+    ptx::tma_store_4d(map_dv, resident_v_stage(sm, e.stage, nq), 0, e.kt * kTileN, head, batch);
+    ptx::tma_store_4d(map_dk, resident_k_stage(sm, e.stage, nq), 0, e.kt * kTileN, head, batch);
+    ptx::tma_store_commit();
+    ptx::tma_store_wait_read();
+    ptx::mbar_arrive(&sm.kv_empty[e.stage]);
+    ++tiles;
+  }
+}
+
 __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_attn_args& a, uint32_t tmem, const ResidentWalk& w,
-                                             const float* delta, int head, int batch, const CUtensorMap* map_dk,
-                                             const CUtensorMap* map_dv) {
+                                             float lse0, float lse1, float dl0, float dl1, int head, int batch) {
+  const float nl0 = -lse0 * kLog2e, nl1 = -lse1 * kLog2e;
   const int tid = threadIdx.x;
   const int row = tid & 127;
   const int half = tid >> 7;
@@ -230,9 +287,8 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
   const GroupCtx g = group_ctx(a, 0);
   const int n = sm.n_iter;
 
-  // this thread's row in both query tiles
+  // this thread's row in both query tiles (its -lse * log2(e) and delta were fetched when the kernel began)
   RowBound rb0, rb1;
-  float nl0 = -INFINITY, nl1 = -INFINITY, dl0 = 0.f, dl1 = 0.f;
   bool live0 = false, live1 = false;
   {
     rb0.lo = rb0.hi = rb0.seg = 0;
@@ -242,24 +298,20 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     if (row < a.q_len) {
       live0 = true;
       rb0 = row_bound(a, g, batch, row);
-      const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + row;
-      nl0 = -a.lse[stat] * kLog2e;
-      dl0 = delta[stat];
     }
     if (w.nq > 1 && kTileM + row < a.q_len) {
       live1 = true;
       rb1 = row_bound(a, g, batch, kTileM + row);
-      const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + kTileM + row;
-      nl1 = -a.lse[stat] * kLog2e;
-      dl1 = delta[stat];
     }
   }
   unsigned char* prow = sm.p + half * kTileBytes + (row >> 3) * 1024 + (row & 7) * 128;
   unsigned char* drow = sm.ds + half * kTileBytes + (row >> 3) * 1024 + (row & 7) * 128;
 
   // key tiles nobody sees get exact zeros; they are not part of the iteration list
-  for (int kt = 0; kt < w.n_kt; ++kt)
-    if (!pair_visible(w, kt, 0) && !pair_visible(w, kt, 1)) resident_store_dkv(a, tmem, kt, row, half, lane_base, head, batch, true);
+  if (sm.n_visited != w.n_kt) {
+    for (int kt = 0; kt < w.n_kt; ++kt)
+      if (!pair_visible(w, kt, 0) && !pair_visible(w, kt, 1)) resident_store_dkv(a, tmem, kt, row, half, lane_base, head, batch, true);
+  }
 
   // Make a visited key tile ready for the MMAs: publish its document table, clear rows beyond the last visible
   // slot (they may hold anything), and meet the other compute threads at kv_ready.
@@ -279,7 +331,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     }
   };
   auto prepare = [&](const ResidentIter& e) -> bool {
-    const int s = e.active & 1;
+    const int s = e.stage;
     const int j0 = e.kt * kTileN;
     if (w.docs && half == 0) {
       if (pf_kt != e.kt) fetch_table(e.kt);
@@ -295,9 +347,9 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
         sm.summary[s][warp][2] = emin;
       }
     }
-    if (!wait_or_abort(sm, &sm.kv_full[s], (e.active >> 1) & 1, 90)) return false;
+    if (!wait_or_abort(sm, &sm.kv_full[s], e.parity, 90)) return false;
     if (j0 + row >= w.kvis) {
-      uint4* dst = reinterpret_cast<uint4*>((half ? sm.v[s] : sm.k[s]) + row * 128);
+      uint4* dst = reinterpret_cast<uint4*>((half ? resident_v_stage(sm, s, w.nq) : resident_k_stage(sm, s, w.nq)) + row * 128);
 #pragma unroll
       for (int c = 0; c < 8; ++c) dst[c] = make_uint4(0, 0, 0, 0);
     }
@@ -307,40 +359,19 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
   };
   // every compute thread has prepared the tile: its document table is complete
   auto prepared = [&](const ResidentIter& e) -> bool {
-    return wait_or_abort(sm, &sm.kv_ready[e.active & 1], (e.active >> 1) & 1, 91);
+    return wait_or_abort(sm, &sm.kv_ready[e.stage], e.parity, 91);
   };
 
   // dV / dK of a finished key tile: TMEM -> bf16 -> the tile's own (now idle) V / K stage in shared memory, in
-  // the 128B-swizzled row layout of the output tensor map -> one TMA store per half.  The stage goes back to the
-  // producer once the store has read it.
-  // Once the first query tile has no pair left (or when there is only one query tile), the Q / dO tiles of an
-  // idle query tile are spare staging room: the K/V stage then goes back to the producer at once, which hides
-  // the load of the next key tile behind the current pair (key tiles seen by one query tile only would otherwise
-  // expose it every time).
-  int outs = 0;  // staged stores so far (parity of out_full)
-  int spare_outs = 0;  // of those, through the spare room (parity of stage_free)
-  int release_stage = -1;  // stage whose staged gradients still have to be read before the producer may refill it
-  bool release_spare = false;
-  const int spare_tile = w.nq == 1 ? 1 : 0;
-  const int spare_from = w.nq == 1 ? 0 : sm.q0_last_iter + 1;  // first iteration index at which it is free
-  auto release = [&]() {
-    if (row == 0 && (release_stage >= 0 || release_spare)) {
-      ptx::tma_store_wait_read();
-      if (release_stage >= 0) ptx::mbar_arrive(&sm.kv_empty[release_stage]);
-      if (release_spare) ptx::mbar_arrive(&sm.stage_free[half]);
-    }
-    release_stage = -1;
-    release_spare = false;
-  };
-  auto stage_out = [&](int kt, int stage, int it_now, bool release_now) -> bool {
+  // the 128B-swizzled row layout of the output tensor map.  The storing thread (warp 11) takes it from there: one
+  // TMA store per half, and the stage goes back to the producer once the stores have read it.
+  int outs = 0;  // staged tiles so far (parity of out_full)
+  auto stage_out = [&](int stage) -> bool {
     const float sc = half ? a.scale : 1.f;
-    const bool spare = it_now >= spare_from;
-    unsigned char* tile = spare ? (half ? sm.q[spare_tile] : sm.g[spare_tile]) : (half ? sm.k[stage] : sm.v[stage]);
-    if (spare) {
-      // (the K/V stage of this key tile was handed back by the gradient issuer's commit)
-      // the previous store out of the spare room has to have read it
-      if (spare_outs > 0 && !wait_or_abort(sm, &sm.stage_free[half], (spare_outs - 1) & 1, 96)) return false;
-    }
+    unsigned char* tile = half ? resident_k_stage(sm, stage, w.nq) : resident_v_stage(sm, stage, w.nq);
+    // the storing thread is a single lane: it has to have seen the previous phase of out_full before this one
+    // can be allowed to complete, or it could take the next completed phase for the one it is waiting for
+    if (outs > 0 && !wait_or_abort(sm, &sm.out_seen, (outs - 1) & 1, 96)) return false;
     unsigned char* dst = tile + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {  // 32 columns at a time keeps the register footprint small
@@ -358,18 +389,6 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     }
     ptx::fence_async_shared();
     ptx::mbar_arrive(&sm.out_full[half]);
-    if (!wait_or_abort(sm, &sm.out_full[half], outs & 1, 95)) return false;
-    if (row == 0) {
-      ptx::tma_store_4d(half ? map_dk : map_dv, tile, 0, kt * kTileN, head, batch);
-      ptx::tma_store_commit();
-    }
-    if (spare) {
-      release_spare = true;
-      ++spare_outs;
-    } else {
-      release_stage = stage;
-    }
-    if (release_now) release();
     ++outs;
     return true;
   };
@@ -380,7 +399,7 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     const ResidentIter e = resident_iter(sm.sched[it]);
     if (e.first && !prepared(e)) return;
     if (e.last && it + 1 < n) fetch_table(resident_iter(sm.sched[it + 1]).kt);
-    const int s = e.active & 1;
+    const int s = e.stage;
     const int j0 = e.kt * kTileN;
     const RowBound& r = e.qt ? rb1 : rb0;
     const bool live = e.qt ? live1 : live0;
@@ -458,9 +477,6 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
       ptx::tmem_wait_ld();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&sm.sdp_free);  // all scores are in registers: S/dP of the next pair may be issued
-      // the store that left shared memory during the previous pair has read it by now: hand its room back without
-      // having made anybody wait for it
-      release();
       if (tid == 0) trace_event(sm, 800 + it);
       math(xs, ys, causal_mask(half * 64 + 32) & dm_hi, pp1, dd1);
       if (tid == 0) trace_event(sm, 900 + it);
@@ -472,16 +488,15 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
       store(1, pp1, dd1);
     }
     // dV / dK of a finished key tile leave TMEM before this iteration's products (which restart the accumulators)
-    // can be issued, i.e. before pds_full; the shared-memory stage is released and the next tile prepared after it
+    // can be issued, i.e. before pds_full; the next tile is prepared after it
     if (pending_kt >= 0) {
-      if (!stage_out(pending_kt, pending_stage, it, false)) return;
+      if (!stage_out(pending_stage)) return;
       pending_kt = -1;
     }
     ptx::fence_async_shared();
     ptx::tc_fence_before();
     ptx::mbar_arrive(&sm.pds_full);
     if (tid == 0) trace_event(sm, 1000 + it);
-    if (e.last && release_stage >= 0) release();  // the next key tile is waiting for this K/V stage: no deferral
     if (e.last && it + 1 < n && !prepare(resident_iter(sm.sched[it + 1]))) return;
     if (e.last) {
       pending_kt = e.kt;
@@ -489,10 +504,9 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     }
   }
   if (n > 0) {
-    release();
     if (!wait_or_abort(sm, &sm.mma_done, (n - 1) & 1, 94)) return;
     ptx::tc_fence_after();
-    if (pending_kt >= 0 && !stage_out(pending_kt, pending_stage, n, true)) return;
+    if (pending_kt >= 0 && !stage_out(pending_stage)) return;
   }
   {
     // half h writes the dQ rows of query tile h
@@ -541,15 +555,50 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
   const int batch = blockIdx.y;
   const GroupCtx g = group_ctx(a, 0);
 
+  const int nq = (a.q_len + kTileM - 1) / kTileM;
   if (tid == 0) {
     sm.abort_flag = 0;
     sm.epoch = epoch;
     trace_begin(sm, epoch);
+    trace_event(sm, 1);
     sm.lo_min[0] = sm.lo_min[1] = INT_MAX;
     sm.hi_max[0] = sm.hi_max[1] = 0;
-    sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
+    ptx::mbar_init(&sm.qg_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      ptx::mbar_init(&sm.kv_full[s], 1);
+      ptx::mbar_init(&sm.kv_ready[s], kResidentCompute);
+      ptx::mbar_init(&sm.kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) ptx::mbar_init(&sm.out_full[s], kTileM);
+    ptx::mbar_init(&sm.out_seen, 1);
+    ptx::mbar_init(&sm.sdp_full, 1);
+    ptx::mbar_init(&sm.sdp_free, kResidentCompute);
+    ptx::mbar_init(&sm.pds_full, kResidentCompute);
+    ptx::mbar_init(&sm.mma_done, 1);
+    ptx::mbar_fence_init();
+  }
+  if (tid == 32) sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
+  if (warp == 8) {
+    ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  // The compute threads' row statistics (thread = query row (tid & 127) of both query tiles) are asked for now
+  // and first used when the first scores are there.
+  float lse0 = INFINITY, lse1 = INFINITY, dl0 = 0.f, dl1 = 0.f;
+  if (tid < kResidentCompute) {
+    const int row = tid & 127;
+    const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + row;
+    if (row < a.q_len) {
+      lse0 = a.lse[stat];
+      dl0 = delta[stat];
+    }
+    if (nq > 1 && kTileM + row < a.q_len) {
+      lse1 = a.lse[stat + kTileM];
+      dl1 = delta[stat + kTileM];
+    }
   }
   __syncthreads();
+  if (tid == kResidentCompute) resident_load_queries(sm, &map_q, &map_g, nq, head, batch);
   if (tid < kResidentCompute) {
     const int qt = tid >> 7;
     int lo = INT_MAX, hi = 0;
@@ -567,7 +616,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
   }
   __syncthreads();
   ResidentWalk w;
-  w.nq = (a.q_len + kTileM - 1) / kTileM;
+  w.nq = nq;
   w.n_kt = (a.k_len + kTileN - 1) / kTileN;
   w.lo_min[0] = sm.lo_min[0];
   w.lo_min[1] = sm.lo_min[1];
@@ -576,55 +625,80 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
   w.kvis = max(w.hi_max[0], w.hi_max[1]);
   w.docs = a.q_seg != nullptr;
   w.dummy = sm.has_dummy != 0;
-  if (tid == 0) {
-    // the list of visible (key tile, query tile) pairs, in execution order
-    int n = 0, active = 0;
-    for (int kt = 0; kt < w.n_kt; ++kt) {
-      const bool v0 = pair_visible(w, kt, 0), v1 = pair_visible(w, kt, 1);
-      if (!v0 && !v1) continue;
-      if (v0) sm.sched[n++] = kt | (0u << 12) | (1u << 13) | ((v1 ? 0u : 1u) << 14) | (static_cast<uint32_t>(active) << 16);
-      if (v1) sm.sched[n++] = kt | (1u << 12) | ((v0 ? 0u : 1u) << 13) | (1u << 14) | (static_cast<uint32_t>(active) << 16);
-      ++active;
+  if (warp == 0) {
+    // The list of visible (key tile, query tile) pairs, in execution order: one lane per key tile decides, the
+    // positions come from ballots.  (Bits 20 and up carry the tile's visit index until the stages are assigned.)
+    int n = 0, tiles = 0, q0_last = -1;
+    for (int base = 0; base < w.n_kt; base += 32) {
+      const int kt = base + lane;
+      const bool v0 = kt < w.n_kt && pair_visible(w, kt, 0), v1 = kt < w.n_kt && pair_visible(w, kt, 1);
+      const uint32_t m0 = __ballot_sync(0xffffffffu, v0), m1 = __ballot_sync(0xffffffffu, v1);
+      const uint32_t below = (1u << lane) - 1u;
+      const int at = n + __popc(m0 & below) + __popc(m1 & below);
+      const uint32_t visit = static_cast<uint32_t>(tiles + __popc((m0 | m1) & below)) << 20;
+      if (v0) {
+        sm.sched[at] = kt | (0u << 12) | (1u << 13) | ((v1 ? 0u : 1u) << 14) | visit;
+        q0_last = max(q0_last, at);
+      }
+      if (v1) sm.sched[at + (v0 ? 1 : 0)] = kt | (1u << 12) | ((v0 ? 0u : 1u) << 13) | (1u << 14) | visit;
+      n += __popc(m0) + __popc(m1);
+      tiles += __popc(m0 | m1);
     }
-    sm.n_iter = n;
-    int q0_last = -1;
-    for (int i = 0; i < n; ++i)
-      if (((sm.sched[i] >> 12) & 1) == 0) q0_last = i;
-    sm.q0_last_iter = q0_last;
-    ptx::mbar_init(&sm.qg_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(&sm.kv_full[s], 1);
-      ptx::mbar_init(&sm.kv_ready[s], kResidentCompute);
-      ptx::mbar_init(&sm.kv_empty[s], 2);  // the two halves' store threads release a stage
-      ptx::mbar_init(&sm.out_full[s], kTileM);
-      ptx::mbar_init(&sm.stage_free[s], 1);
+    q0_last = __reduce_max_sync(0xffffffffu, q0_last);
+    __syncwarp();
+    // K/V stage of every visited key tile.  Stages 0 and 1 alternate; from the tile after the first one that
+    // starts behind the first query tile's last pair (t0), the idle query tile's room joins as stage 2 and the
+    // three take turns (the stage unused for longest comes next).  With one query tile that is so from the start.
+    // Stage 2 begins its life full (Q / dO of the first query tile) unless there is only one query tile or the
+    // first query tile has no pair at all, so there the producer's first wait is for a completed phase.
+    const int third_from = w.nq == 1 ? 0 : q0_last + 1;  // first iteration behind the first query tile's pairs
+    const bool third_starts_full = w.nq > 1 && q0_last >= 0;
+    int t0 = INT_MAX;
+    for (int i = lane; i < n; i += 32) {
+      const uint32_t entry = sm.sched[i];
+      if (((entry >> 13) & 1) && i >= third_from) t0 = min(t0, static_cast<int>(entry >> 20));
     }
-    ptx::mbar_init(&sm.sdp_full, 1);
-    ptx::mbar_init(&sm.sdp_free, kResidentCompute);
-    ptx::mbar_init(&sm.pds_full, kResidentCompute);
-    ptx::mbar_init(&sm.mma_done, 1);
-    ptx::mbar_fence_init();
-  }
-  if (warp == 8) {
-    ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
-    ptx::tmem_relinquish();
+    t0 = __reduce_min_sync(0xffffffffu, t0);
+    for (int i = lane; i < n; i += 32) {
+      const uint32_t entry = sm.sched[i];
+      const int tile = static_cast<int>(entry >> 20);
+      int stage = tile & 1, use = tile >> 1;  // how often the stage was used before
+      if (tile > t0) {
+        const int d = tile - t0 - 1, r = d % 3, c = d / 3;
+        stage = r == 0 ? 2 : (r == 1 ? ((t0 + 1) & 1) : (t0 & 1));
+        use = r == 0 ? c : ((t0 + 2 - stage) >> 1) + c;  // tiles up to t0 with the stage's parity, then every third
+      }
+      const int empty_parity = stage == 2 && third_starts_full ? (use & 1) : ((use & 1) ^ 1);
+      sm.sched[i] = (entry & 0x7fffu) | (static_cast<uint32_t>(stage) << 15) | (static_cast<uint32_t>(use & 1) << 17) |
+                    (static_cast<uint32_t>(empty_parity) << 18);
+    }
+    if (lane == 0) {
+      sm.n_iter = n;
+      sm.n_visited = tiles;
+      sm.q0_last_iter = q0_last;
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  if (tid == 0) trace_event(sm, 2);
   if (warp < 8) {
-    resident_compute(sm, a, tmem, w, delta, head, batch, &map_dk, &map_dv);
+    resident_compute(sm, a, tmem, w, lse0, lse1, dl0, dl1, head, batch);
   } else if (warp == 8) {
-    if (lane == 0) resident_producer(sm, &map_q, &map_k, &map_v, &map_g, w, head, batch);
+    if (lane == 0) resident_producer(sm, &map_k, &map_v, w, head, batch);
   } else if (warp == 9) {
-    if (lane == 0) resident_mma_scores(sm, tmem);
-  } else {
+    if (lane == 0) resident_mma_scores(sm, tmem, w.nq, w.kvis);
+  } else if (warp == 10) {
     if (lane == 0) resident_mma_grads(sm, tmem, w.nq);
+  } else {
+    if (lane == 0) resident_store(sm, &map_dk, &map_dv, w.nq, head, batch);
   }
+  if (tid == 0) trace_event(sm, 3);
   ptx::tma_store_wait_all();
   ptx::tc_fence_before();
   __syncthreads();
+  if (tid == 0) trace_event(sm, 4);
   trace_flush(sm);
   if (warp == 8) ptx::tmem_dealloc(tmem, kTmemCols);
 }
