@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels on exactly these
 # workloads, from the ncu captures summarised under profiles/ (one capture each; the bench cannot run ncu itself).
 NCU_TRAFFIC_BYTES = {
-    "attn_bwd_resident_kernel": 249.6e6,
+    "attn_bwd_resident_kernel": 255.7e6,
     "attn_fwd_tc_kernel": 177.4e6,
     "decode_split_kernel": 1086.4e6,
     "mix_fwd_kernel": 432.8e6,
@@ -181,33 +181,69 @@ class TrainingSweep:
             query_stride=STRIDE, query_offset=r, strict_past=True, metadata=self.metas[r], backend=self.backend,
         )
 
-    def step(self):
-        """All 8 residues forward and backward; returns nothing, gradients are discarded."""
-        for r in range(STRIDE):
-            out = self.forward(r)
-            torch.autograd.grad(out, (self.q[r], self.k, self.v), self.g[r])
+    def step(self, streams=None):
+        """All 8 residues forward and backward; returns nothing, gradients are discarded.
 
-    def capture(self):
+        The residue calls do not depend on one another.  With `streams` they are issued round-robin on those
+        streams (forked from and joined to the current one), so that the blocks of one call fill the SMs the last,
+        partial wave of another leaves idle: 256 blocks of one backward call are 1.7 waves on 148 SMs."""
+        if not streams:
+            for r in range(STRIDE):
+                out = self.forward(r)
+                torch.autograd.grad(out, (self.q[r], self.k, self.v), self.g[r])
+            return
+        main = torch.cuda.current_stream()
+        for stream in streams:
+            stream.wait_stream(main)
+        for r in range(STRIDE):
+            with torch.cuda.stream(streams[r % len(streams)]):
+                out = self.forward(r)
+                torch.autograd.grad(out, (self.q[r], self.k, self.v), self.g[r])
+        for stream in streams:
+            main.wait_stream(stream)
+
+    def _capture(self, streams):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step(streams)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.step(streams)
+        return graph
+
+    def capture(self, n_streams=1):
         """Capture one step in a CUDA graph (the 16 operator calls are launch-bound when issued eagerly).
 
         Returns the number of kernels of this library inside the graph."""
         from white_matter_b200 import _native
 
         lib = _native.load_library()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            self.step()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
         before = lib.wm_kernel_launch_count()
-        with torch.cuda.graph(self.graph):
-            self.step()
-        return lib.wm_kernel_launch_count() - before
+        self.graph_one_stream = self._capture(None)
+        per_step = (lib.wm_kernel_launch_count() - before) // 2  # the dry run and the captured one
+        self.graph = self.graph_one_stream
+        if n_streams > 1:
+            self.streams = [torch.cuda.Stream() for _ in range(n_streams)]
+            self.graph = self._capture(self.streams)
+        return per_step
 
     def replay(self):
         self.graph.replay()
+
+    def one_stream_ms(self, reps=10):
+        """Device time (ms) of one step with the 24 launches one after another (the per-kernel figures)."""
+        self.graph_one_stream.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(reps):
+            self.graph_one_stream.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / reps
 
     def forward_only_ms(self, reps=10):
         """Device time (ms) of the 8 forward launches of one step, from a CUDA graph replayed `reps` times."""
@@ -560,6 +596,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--backend", default="sm100", help="kernel family: sm100 | sm100_simt | sm100_tcgen05")
     parser.add_argument("--no-graph", action="store_true", help="issue the operator calls eagerly instead of replaying a CUDA graph")
+    parser.add_argument("--streams", type=int, default=8, help="streams the 8 independent residue calls of a step alternate over (1: one after another)")
     parser.add_argument("--skip-extras", action="store_true", help="only the headline workload (used for profiling)")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -608,14 +645,18 @@ def main():
     piped_max_ms, piped_flops = aggregate_throughput(piped_ms, float(sets[0].flops * e2e_steps), device)
     e2e_value = piped_flops / (piped_max_ms * 1e-3) / 1e12
 
+    if args.streams > 1:  # gradients of K and V are produced on the side streams on purpose
+        getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", lambda flag: None)(False)
     turn = [0]
     per_step_launches = None
     if not args.no_graph:
-        per_step_launches = [s.capture() for s in sets][0]
+        per_step_launches = [s.capture(args.streams) for s in sets][0]
+
+    eager_streams = [torch.cuda.Stream() for _ in range(args.streams)] if args.no_graph and args.streams > 1 else None
 
     def step():
         if args.no_graph:
-            sets[turn[0] % 2].step()
+            sets[turn[0] % 2].step(eager_streams)
         else:
             sets[turn[0] % 2].replay()
         turn[0] += 1
@@ -636,11 +677,15 @@ def main():
     step_ms, total_flops = aggregate_throughput(ms, float(flops), device)
     value = total_flops / (step_ms * 1e-3) / 1e12
 
-    # per-kernel device time: a graph with the 8 forward launches alone, replayed and timed with CUDA events;
-    # the backward kernel group is the step minus the forward part
+    # per-kernel device time, launches one after another: a graph with the 8 forward launches alone, replayed and
+    # timed with CUDA events; the backward kernel group is the one-stream step minus the forward part
     work = sets[0]
     fwd_ms = work.forward_only_ms(reps=max(3, min(args.steps, 20))) / STRIDE
     step_device_ms = step_ms / args.steps
+    one_stream_ms = None
+    if not args.no_graph:
+        one_stream_ms = work.one_stream_ms(reps=max(3, min(args.steps, 20)))
+        step_device_ms = one_stream_ms
     bwd_ms = max(step_device_ms / STRIDE - fwd_ms, 1e-6)
     tensor_peak = peaks["bf16_tflops_sustained"]
     fwd_tf = work.flops_fwd / STRIDE / (fwd_ms * 1e-3) / 1e12
@@ -659,7 +704,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
-            "device_status": int(lib.wm_device_status(0)), "backend": args.backend, "launch_mode": "eager" if args.no_graph else "cuda graph replay of one step",
+            "device_status": int(lib.wm_device_status(0)), "backend": args.backend, "launch_mode": ("eager" if args.no_graph else "cuda graph replay of one step") + (f", the 8 independent residue calls alternating over {args.streams} streams" if args.streams > 1 else ""),
+            "one_stream": None if one_stream_ms is None else {"ms_per_step": one_stream_ms, "value": work.flops / (one_stream_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "note": "the same step with its 24 launches one after another; the roofline figures are per kernel out of this"},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": sets[0].staging_bytes()[0],
                     "d2h_bytes_per_step": sets[0].staging_bytes()[1],
                     "mode": "copies on their own streams beside the kernels of the neighbouring steps (two staging sets)",
