@@ -11,7 +11,11 @@ residues, forward and backward, 16 operator calls.  Inputs are synthetic
 
 The headline ``value`` is TFLOP/s on the visible (query,key) pairs only,
 14*head_dim FLOP per pair (4 forward, 10 backward), with inputs resident in
-HBM.  ``e2e`` is the same metric through the public functions with every step's
+HBM.  The 8 residue calls of a step are independent; the step's CUDA graph has
+them on ``--streams`` streams (default 8) so that the blocks of one call fill
+the partial last wave of another; ``one_stream`` is the same step with its
+launches one after another, which is also what the per-kernel ``roofline``
+figures are taken from.  ``e2e`` is the same metric through the public functions with every step's
 inputs copied in from pinned host buffers and every step's results copied back
 inside the timed region; the copies run on their own streams beside the kernels
 of the neighbouring steps (``e2e.serialized`` is the same work on one stream).  The same line also reports the
