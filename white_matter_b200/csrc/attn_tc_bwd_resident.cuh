@@ -577,7 +577,6 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
     ptx::mbar_init(&sm.mma_done, 1);
     ptx::mbar_fence_init();
   }
-  if (tid == 32) sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
   if (warp == 8) {
     ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
     ptx::tmem_relinquish();
@@ -599,6 +598,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
   }
   __syncthreads();
   if (tid == kResidentCompute) resident_load_queries(sm, &map_q, &map_g, nq, head, batch);
+  // (a thread that has no row waits for this load, beside the rows' own loads)
+  if (tid == kResidentThreads - 1) sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
   if (tid < kResidentCompute) {
     const int qt = tid >> 7;
     int lo = INT_MAX, hi = 0;

@@ -475,7 +475,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     sm.abort_flag = 0;
     sm.epoch = epoch;
     trace_begin(sm, epoch);
-    sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
     ptx::mbar_init(&sm.q_full, 1);
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&sm.k_full[s], 1);
@@ -510,6 +509,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     ptx::mbar_expect_tx(&sm.q_full, kTileBytes);
     ptx::tma_load_4d(sm.q, &map_q, &sm.q_full, 0, q0, head, batch);
   }
+  // (a thread that has no row waits for this load, beside the rows' own loads)
+  if (tid == kFwdThreads - 1) sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
   RowBound rb;
   rb.lo = 0;
   rb.hi = 0;
