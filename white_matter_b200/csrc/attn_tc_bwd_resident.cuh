@@ -95,7 +95,8 @@ struct ResidentShared {
   int lo_min[2], hi_max[2];
   int has_dummy;
   // iteration list: key tile | query tile << 12 | first-of-key-tile << 13 | last-of-key-tile << 14 | K/V stage << 15 |
-  // parity of this use of the stage (kv_full, kv_ready) << 17 | parity the producer waits for on kv_empty << 18
+  // parity of this use of the stage (kv_full, kv_ready) << 17 | parity the producer waits for on kv_empty << 18 |
+  // dK/dV of the tile go straight to global memory << 19
   uint32_t sched[kResidentMaxIter];
   int n_iter;
   int n_visited;     // key tiles on the list
@@ -107,7 +108,7 @@ struct ResidentShared {
 };
 
 struct ResidentIter {
-  int kt, qt, first, last, stage, parity, empty_parity;
+  int kt, qt, first, last, stage, parity, empty_parity, direct;
 };
 
 __device__ __forceinline__ ResidentIter resident_iter(uint32_t e) {
@@ -119,6 +120,7 @@ __device__ __forceinline__ ResidentIter resident_iter(uint32_t e) {
   it.stage = (e >> 15) & 3;
   it.parity = (e >> 17) & 1;
   it.empty_parity = (e >> 18) & 1;
+  it.direct = (e >> 19) & 1;
   return it;
 }
 
@@ -242,6 +244,9 @@ __device__ __forceinline__ void resident_mma_grads(ResidentShared& sm, uint32_t 
                        ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, acc_q || (kk > 0));
     if (e.qt) dq_started[1] = true; else dq_started[0] = true;
     ptx::mma_commit(&sm.mma_done);
+    // a tile whose gradients will not be staged in its K/V stage gives the stage back as soon as these products
+    // have read it
+    if (e.direct) ptx::mma_commit(&sm.kv_empty[e.stage]);
     if (nq > 1 && it == sm.q0_last_iter) {
       // these were the last products that read Q / dO of the first query tile: once they are complete its room
       // is the ring's third stage
@@ -262,7 +267,7 @@ __device__ __forceinline__ void resident_store(ResidentShared& sm, const CUtenso
   int tiles = 0;
   for (int it = 0; it < n; ++it) {
     const ResidentIter e = resident_iter(sm.sched[it]);
-    if (!e.last) continue;
+    if (!e.last || e.direct) continue;
     if (!wait_or_abort(sm, &sm.out_full[0], tiles & 1, 97)) return;
     if (!wait_or_abort(sm, &sm.out_full[1], tiles & 1, 98)) return;
     ptx::mbar_arrive(&sm.out_seen);
@@ -393,8 +398,43 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     return true;
   };
 
+  // The other way out, for a key tile with one pair whose successor has one pair too while only two stages are
+  // open: there the load after next would wait for the staged gradients to leave this tile's stage, and the compute
+  // warps for that load.  Each thread writes its key row's 128 bytes of dV or dK itself (twice the time of the
+  // staging), and the gradient issuer's commit has handed the stage back long before.
+  auto direct_out = [&](int kt) {
+    const float sc = half ? a.scale : 1.f;
+    const int j = kt * kTileN + row;
+    const int64_t* st = half ? a.dk_strides : a.dv_strides;
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(half ? a.dk : a.dv) + batch * st[0] + head * st[1] +
+                                          static_cast<long long>(j) * st[2]);
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      uint32_t raw[32];
+      ptx::tmem_ld32(tmem + 2 * kTileN + half * kHeadDim + lane_base + h2 * 32, raw);
+      ptx::tmem_wait_ld();
+      if (j < a.k_len) {
+        const bool sectors = (reinterpret_cast<uintptr_t>(dst) & 31) == 0;  // rows the caller laid out on 32 bytes
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {  // whole 32-byte sectors: partial ones are what makes scattered rows slow
+          uint32_t pk[8];
+#pragma unroll
+          for (int e2 = 0; e2 < 8; ++e2)
+            pk[e2] = pack_bf16(__uint_as_float(raw[c * 16 + 2 * e2]) * sc, __uint_as_float(raw[c * 16 + 2 * e2 + 1]) * sc);
+          if (sectors) {
+            ptx::st_global_v8(dst + h2 * 4 + c * 2, pk);
+          } else {
+            dst[h2 * 4 + c * 2] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            dst[h2 * 4 + c * 2 + 1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          }
+        }
+      }
+    }
+  };
+
   if (n > 0 && !prepare(resident_iter(sm.sched[0]))) return;
   int pending_kt = -1, pending_stage = 0;
+  bool pending_direct = false;
   for (int it = 0; it < n; ++it) {
     const ResidentIter e = resident_iter(sm.sched[it]);
     if (e.first && !prepared(e)) return;
@@ -490,7 +530,8 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     // dV / dK of a finished key tile leave TMEM before this iteration's products (which restart the accumulators)
     // can be issued, i.e. before pds_full; the next tile is prepared after it
     if (pending_kt >= 0) {
-      if (!stage_out(pending_stage)) return;
+      if (pending_direct) direct_out(pending_kt);
+      else if (!stage_out(pending_stage)) return;
       pending_kt = -1;
     }
     ptx::fence_async_shared();
@@ -501,12 +542,16 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     if (e.last) {
       pending_kt = e.kt;
       pending_stage = s;
+      pending_direct = e.direct != 0;
     }
   }
   if (n > 0) {
     if (!wait_or_abort(sm, &sm.mma_done, (n - 1) & 1, 94)) return;
     ptx::tc_fence_after();
-    if (pending_kt >= 0 && !stage_out(pending_stage)) return;
+    if (pending_kt >= 0) {
+      if (pending_direct) direct_out(pending_kt);
+      else if (!stage_out(pending_stage)) return;
+    }
   }
   {
     // half h writes the dQ rows of query tile h
@@ -670,8 +715,13 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
         use = r == 0 ? c : ((t0 + 2 - stage) >> 1) + c;  // tiles up to t0 with the stage's parity, then every third
       }
       const int empty_parity = stage == 2 && third_starts_full ? (use & 1) : ((use & 1) ^ 1);
+      // one pair here, one pair in the next tile, and the third stage not yet open: gradients go out directly
+      // (the first / last bits of the follower read here are the same before and after its own rewrite)
+      const uint32_t single = (1u << 13) | (1u << 14);
+      const uint32_t follower = i + 1 < n ? sm.sched[i + 1] : 0u;
+      const bool direct = tile <= t0 && (entry & single) == single && (follower & single) == single;
       sm.sched[i] = (entry & 0x7fffu) | (static_cast<uint32_t>(stage) << 15) | (static_cast<uint32_t>(use & 1) << 17) |
-                    (static_cast<uint32_t>(empty_parity) << 18);
+                    (static_cast<uint32_t>(empty_parity) << 18) | ((direct ? 1u : 0u) << 19);
     }
     if (lane == 0) {
       sm.n_iter = n;
