@@ -108,6 +108,34 @@ def test_strict_past_all_residues(packed, stride, backend):
             assert out[:, :, 0].abs().max().item() == 0  # the first token of the row sees nothing
 
 
+@pytest.mark.parametrize("mean", [6, 48, 300])
+@pytest.mark.parametrize("dummy", [False, True])
+def test_document_masks_by_runs_and_by_rows(dummy, mean):
+    # the tcgen05 kernels build a key tile's document masks from its runs of equal (document, query bound) when the
+    # tile has at most 8 of them and row by row otherwise: documents of mean length 6 put ~20 runs in every 128-key
+    # tile, mean 48 mixes both ways, mean 300 stays with the runs
+    torch.manual_seed(17)
+    T, B, H, D, stride = 640, 2, 2, 64, 2
+    lead = int(dummy)
+    k = torch.randn(B, H, T + lead, D).bfloat16()
+    v = torch.randn(B, H, T + lead, D).bfloat16()
+    docs = geometric_documents(B, T, mean, seed=mean)
+    groups = [torch.arange(r, T, stride) for r in range(stride)]
+    metas = prepare_feedback_metadata(docs, groups, T + lead, use_dummy_token=dummy)
+    for r in range(stride):
+        n = groups[r].numel()
+        q = torch.randn(B, H, n, D).bfloat16()
+        probe = torch.randn(B, H, n, D).bfloat16()
+        c = dict(stride=stride, offset=r, strict_past=not dummy)
+        out, grads = run(q, k, v, probe, metas[r], c, torch.bfloat16, "sm100_tcgen05")
+        qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+        exp = oracle.cyclic_attention_oracle(qo, ko, vo, query_stride=stride, query_offset=r, strict_past=not dummy, metadata=metas[r])
+        exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.double())
+        assert_parity(out.float(), exp, what=f"out r={r}", **BF16_TOL)
+        for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+            assert_parity(g.float(), e, what=f"{name} r={r}", **BF16_TOL)
+
+
 @pytest.mark.parametrize("backend", BACKENDS)
 @pytest.mark.parametrize("documents", [False, True])
 def test_equal_scores_average_exactly_to_zero(documents, backend):

@@ -204,20 +204,62 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ uint32_t bits_below(int n) { return n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u)); }
+
 // Document visibility of the 128 key columns of a tile for the rows of one warp (row = lane), as four 32-column
-// bit masks per row.  Lane c holds the table entries of columns c, c+32, c+64 and c+96 in registers; the rows
-// that need a mask are visited in turn, their parameters broadcast, and four ballots give the row's masks --
-// no shared-memory access and no per-element loop in the row's own thread.
+// bit masks per row (all ones for rows that do not want one).  A key is visible to a row when
+// (row.qi < key.end) and (key.seg == -1 or (key.seg == row.seg and key >= row.lo)).
+//
+// The table of a tile is a handful of runs of equal (seg, end) -- one per document that touches the tile.  The warp
+// finds the run boundaries with four ballots, and every row then builds its masks from the runs by arithmetic:
+// a few hundred cycles whatever the number of rows that want a mask.  Tables with more than kDocRuns runs take
+// the general way: the rows that want a mask are visited in turn, their parameters broadcast, and four ballots
+// over the columns (lane c holds columns c, c+32, c+64, c+96) give one row's masks.
+constexpr int kDocRuns = 8;
+
 __device__ __forceinline__ void warp_doc_masks(const RowBound& rb, bool wanted, int j0, const int* key_seg,
                                                const int* key_end, uint32_t (&out)[4]) {
   const int lane = threadIdx.x & 31;
   int seg[4], end[4];
+  uint32_t rest[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    seg[c] = key_seg[32 * c + lane];
-    end[c] = key_end[32 * c + lane];
-    out[c] = 0xffffffffu;
+    const int x = 32 * c + lane;
+    seg[c] = key_seg[x];
+    end[c] = key_end[x];
+    const bool begins = x == 0 || key_seg[x - 1] != seg[c] || key_end[x - 1] != end[c];
+    rest[c] = __ballot_sync(0xffffffffu, begins);
   }
+  const int runs = __popc(rest[0]) + __popc(rest[1]) + __popc(rest[2]) + __popc(rest[3]);
+  if (runs <= kDocRuns) {
+    uint32_t m[4] = {0u, 0u, 0u, 0u};
+    const int lo_col = rb.lo - j0;
+    rest[0] &= ~1u;  // column 0 begins the first run
+    int start = 0;
+    for (int k = 0; k < runs; ++k) {
+      int next = kTileN;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (next == kTileN && rest[c] != 0u) {
+          next = 32 * c + __ffs(rest[c]) - 1;
+          rest[c] &= rest[c] - 1u;
+        }
+      }
+      const int run_seg = key_seg[start], run_end = key_end[start];  // the same address for every lane
+      const bool open = (rb.qi < run_end) & ((run_seg == -1) | (run_seg == rb.seg));
+      const int lo = run_seg == -1 ? start : max(start, lo_col);
+      if (open && lo < next) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) m[c] |= bits_below(next - 32 * c) & ~bits_below(lo - 32 * c);
+      }
+      start = next;
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) out[c] = wanted ? m[c] : 0xffffffffu;
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) out[c] = 0xffffffffu;
   for (uint32_t left = __ballot_sync(0xffffffffu, wanted); left != 0u; left &= left - 1u) {
     const int r = __ffs(left) - 1;
     const int rseg = __shfl_sync(0xffffffffu, rb.seg, r);
