@@ -47,8 +47,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels on exactly these
 # workloads, from the ncu captures summarised under profiles/ (one capture each; the bench cannot run ncu itself).
 NCU_TRAFFIC_BYTES = {
-    "attn_bwd_resident_kernel": 255.7e6,
-    "attn_fwd_tc_kernel": 177.4e6,
+    "attn_bwd_resident_kernel": 252.0e6,
+    "attn_fwd_tc_kernel": 177.8e6,
     "decode_split_kernel": 1086.4e6,
     "mix_fwd_kernel": 432.8e6,
     "query_prepare_fwd_bf16_kernel": 226.7e6,
