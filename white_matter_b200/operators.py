@@ -227,10 +227,13 @@ def _(Q, K, V, QSeg, KSeg, QStart, KQEnd, Out, Lse, dOut, K_stride, residue, blo
 def _cyclic_setup(ctx, inputs, output):
     *tensors, ctx.K_stride, ctx.residue, ctx.block_M = inputs
     ctx.save_for_backward(*tensors, *output)
+    ctx.set_materialize_grads(False)  # no zero fill for the unused gradient of Lse on every backward call
 
 
 def _cyclic_backward(ctx, dOut, dLse):
     tensors = ctx.saved_tensors
+    if dOut is None:
+        dOut = torch.zeros_like(tensors[-2])
     op = cyclic_attn_doc_bwd if len(tensors) == 9 else cyclic_attn_bwd
     grads = op(*tensors, dOut, ctx.K_stride, ctx.residue, ctx.block_M)
     return (*grads, *((None,) * (len(tensors) - 2)))
@@ -330,10 +333,13 @@ def _strict_setup(ctx, inputs, output):
     Q, K, V, query_start, ctx.query_start_value, kv_lengths, key_mask, ctx.use_dummy, ctx.scale, ctx.kernel = inputs
     ctx.save_for_backward(Q, K, V, *output)
     ctx.bounds = (query_start, kv_lengths, key_mask)
+    ctx.set_materialize_grads(False)
 
 
 def _strict_backward(ctx, dOut, dLse):
     Q, K, V, Out, Lse = ctx.saved_tensors
+    if dOut is None:
+        dOut = torch.zeros_like(Out)
     query_start, kv_lengths, key_mask = ctx.bounds
     grads = strict_attn_bwd(
         Q, K, V, Out, Lse, dOut, query_start, ctx.query_start_value, kv_lengths, key_mask, ctx.use_dummy, ctx.scale,
@@ -466,10 +472,13 @@ def _packed_setup(ctx, inputs, output):
     Q, K, V, *tables, ctx.scale, ctx.kernel = inputs
     ctx.save_for_backward(Q, K, V, *output)
     ctx.tables = tables
+    ctx.set_materialize_grads(False)
 
 
 def _packed_backward(ctx, dOut, dLse):
     Q, K, V, Out, Lse = ctx.saved_tensors
+    if dOut is None:
+        dOut = torch.zeros_like(Out)
     grads = strict_packed_bwd(Q, K, V, Out, Lse, dOut, *ctx.tables, ctx.scale, ctx.kernel)
     return (*grads, None, None, None, None, None, None, None)
 
