@@ -629,6 +629,9 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
   // The compute threads' row statistics (thread = query row (tid & 127) of both query tiles) are asked for now
   // and first used when the first scores are there.
   float lse0 = INFINITY, lse1 = INFINITY, dl0 = 0.f, dl1 = 0.f;
+  RowBound own;  // bounds of query `tid`, for the block's key range
+  own.lo = own.hi = own.seg = own.qi = 0;
+  if (tid < kResidentCompute && tid < a.q_len) own = row_bound(a, g, batch, tid);
   if (tid < kResidentCompute) {
     const int row = tid & 127;
     const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + row;
@@ -649,9 +652,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1)
     const int qt = tid >> 7;
     int lo = INT_MAX, hi = 0;
     if (tid < a.q_len) {
-      const RowBound rb = row_bound(a, g, batch, tid);
-      hi = rb.hi;
-      if (rb.hi > 0) lo = rb.lo;
+      hi = own.hi;
+      if (own.hi > 0) lo = own.lo;
     }
     lo = __reduce_min_sync(0xffffffffu, lo);
     hi = __reduce_max_sync(0xffffffffu, hi);

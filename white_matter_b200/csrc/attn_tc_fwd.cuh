@@ -469,6 +469,19 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   const int q0 = q_tile * kTileM;
   const GroupCtx g = group_ctx(a, 0);
 
+  // each softmax thread's row bounds: with documents they come from global memory, and asked for here they are on
+  // their way while the barriers are set up
+  RowBound rb;
+  rb.lo = 0;
+  rb.hi = 0;
+  rb.seg = 0;
+  rb.qi = q0 + (tid & 127);
+  bool live = false;
+  if (tid < kFwdSoftmax) {
+    live = rb.qi < a.q_len;
+    if (live) rb = row_bound(a, g, batch, rb.qi);
+  }
+
   if (tid == 0) {
     sm.red_min_lo = INT_MAX;
     sm.red_max_hi = 0;
@@ -511,15 +524,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   }
   // (a thread that has no row waits for this load, beside the rows' own loads)
   if (tid == kFwdThreads - 1) sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
-  RowBound rb;
-  rb.lo = 0;
-  rb.hi = 0;
-  rb.seg = 0;
-  rb.qi = q0 + (tid & 127);
-  bool live = false;
   if (tid < kFwdSoftmax) {
-    live = rb.qi < a.q_len;
-    if (live) rb = row_bound(a, g, batch, rb.qi);
     const int lo = live && rb.hi > 0 ? rb.lo : INT_MAX;
     const int wlo = __reduce_min_sync(0xffffffffu, lo);
     const int whi = __reduce_max_sync(0xffffffffu, rb.hi);
