@@ -579,9 +579,18 @@ __device__ __forceinline__ void resident_compute(ResidentShared& sm, const wm_at
     if (qt < w.nq && i < a.q_len) {
       uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dq) + batch * a.dq_strides[0] +
                                             head * a.dq_strides[1] + static_cast<long long>(i) * a.dq_strides[2]);
+      if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {  // whole 32-byte sectors
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t pk[8] = {packed[8 * c],     packed[8 * c + 1], packed[8 * c + 2], packed[8 * c + 3],
+                                  packed[8 * c + 4], packed[8 * c + 5], packed[8 * c + 6], packed[8 * c + 7]};
+          ptx::st_global_v8(dst + 2 * c, pk);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
     }
   }
 }

@@ -437,17 +437,25 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(a.out) + batch * a.out_strides[0] + head * a.out_strides[1] +
                           static_cast<long long>(rb.qi) * a.out_strides[2] + grp * 32;
     const bool use0 = w0 > 0.f, use1 = last >= 1 && w1 > 0.f;
+    // whole 32-byte sectors where the caller's rows allow it: rows of different lanes are far apart, and partial
+    // sectors are what makes such stores slow
+    const bool sectors = (reinterpret_cast<uintptr_t>(orow) & 31) == 0;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      uint32_t pk[4];
+    for (int u = 0; u < 2; ++u) {
+      uint32_t pk[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = 8 * u + 2 * e;
+      for (int e = 0; e < 8; ++e) {
+        const int i = 16 * u + 2 * e;
         const float lo = (use0 ? __uint_as_float(acc0[i]) * w0 : 0.f) + (use1 ? __uint_as_float(acc1[i]) * w1 : 0.f);
         const float hi = (use0 ? __uint_as_float(acc0[i + 1]) * w0 : 0.f) + (use1 ? __uint_as_float(acc1[i + 1]) * w1 : 0.f);
         pk[e] = pack_bf16(lo, hi);
       }
-      reinterpret_cast<uint4*>(orow)[u] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      if (sectors) {
+        ptx::st_global_v8(orow + 16 * u, pk);
+      } else {
+        reinterpret_cast<uint4*>(orow)[2 * u] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        reinterpret_cast<uint4*>(orow)[2 * u + 1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      }
     }
     if (grp == 0 && a.lse != nullptr)
       a.lse[(static_cast<long long>(batch) * a.q_heads + head) * a.q_len + rb.qi] =
