@@ -301,3 +301,28 @@ def test_many_launches_leave_the_status_word_clean():
             torch.autograd.grad(out, (q, k, v), probe)
         status = _native.device_status(True)
         assert status == 0, f"shape {(batch, heads, keys, stride, documents)}: wait {status & 255} gave up in block {status >> 8}"
+
+
+def test_first_cuda_action_of_a_thread_may_be_the_backward_call():
+    # In a fresh process the autograd worker thread has made no CUDA call of its own when the backward operator
+    # reaches the library: the tensor-map encoder (a driver entry point) then finds no context bound to the thread
+    # and the library has to bind the primary one itself.
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    code = (
+        "import torch\n"
+        "from white_matter_b200 import cyclic_attention\n"
+        "q = torch.randn(1, 2, 64, 64, device='cuda', dtype=torch.bfloat16, requires_grad=True)\n"
+        "k = torch.randn(1, 2, 256, 64, device='cuda', dtype=torch.bfloat16, requires_grad=True)\n"
+        "v = torch.randn(1, 2, 256, 64, device='cuda', dtype=torch.bfloat16, requires_grad=True)\n"
+        "out = cyclic_attention(q, k, v, query_stride=4, query_offset=1, backend='sm100_tcgen05')\n"
+        "g = torch.autograd.grad(out, (q, k, v), torch.ones_like(out))\n"
+        "torch.cuda.synchronize()\n"
+        "assert all(torch.isfinite(t.float()).all() for t in g)\n"
+        "print('ok')\n"
+    )
+    done = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and "ok" in done.stdout, done.stderr[-2000:]
