@@ -1,24 +1,14 @@
-// tcgen05 / TMEM attention forward for bf16, head_dim 64.
-//
-// One CTA owns a tile of 128 query rows of one (batch, head) and walks over
-// tiles of 128 key slots.  Roles inside the CTA (192 threads):
-//   warps 0-3  softmax: thread t owns query row t == TMEM lane t; reads S with
-//              tcgen05.ld, applies the mask, keeps the online-softmax state,
-//              writes P (bf16) into shared memory in the K-major 128B-swizzled
-//              layout the MMA reads, rescales O in TMEM when the running
-//              maximum moved by more than 2^8, and writes the result.
-//   warp 4     TMA producer: Q once, then K and V tiles through 3-deep rings.
-//   warp 5     MMA issuer (one lane): S = Q K^T into one of two TMEM buffers,
-//              O += P V into a third; completion is signalled by tcgen05.commit
-//              on mbarriers.
-// TMEM: S0 [0,128), S1 [128,256), O [256,320) columns; 512 allocated.
-// Key tiles that no row of the query tile can see are never loaded: the walk
-// ends at the largest visible slot, and document problems start at the
-// smallest document start of the tile (plus tile 0 for the shared dummy).
-//
-// Every mbarrier wait is bounded; a wait that runs out records an error code
-// in a device status word, and all roles fall through to the common exit where
-// TMEM is released.
+// tcgen05 / TMEM attention kernels for bf16, head_dim 64: host side (tensor maps, kernel selection, launches), the
+// helpers the pipelines share (bounded waits, the device status word, document masks), and the three pipelines
+// themselves, each in a header of its own:
+//   attn_tc_fwd.cuh       forward: one block per 128 query rows, two softmax groups on alternate key tiles, P kept
+//                         in tensor memory as the A operand of the PV product
+//   attn_tc_bwd_keys.cuh  backward for at most 256 queries per (batch, head) without grouped heads: one block per
+//                         (batch, head), key rows on the TMEM lanes, dQ resident in tensor memory
+//   attn_tc_bwd.cuh       backward for every other shape: one block per key tile, dQ through fp32 atomics
+// Key tiles that no query can see are never loaded.  Every mbarrier wait is bounded; a wait that runs out records
+// its code in a device status word, and all roles of the block fall through to the common exit where tensor memory
+// is released.
 #include <cuda.h>
 #include <atomic>
 #include <limits.h>
@@ -42,8 +32,7 @@ constexpr uint32_t kTileBytes = kTileN * kHeadDim * 2;  // 16 KB: one Q, K or V 
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
-__device__ int g_status = 0;       // first failure code since the last reset
-__device__ int g_abort_epoch = 0;  // launch number whose blocks should stop waiting
+__device__ int g_status = 0;  // first failure code since the last reset
 
 // Pipeline trace (builds with -DWM_B200_TRACE only): block (0,0,0) of the launch whose number equals g_trace_epoch
 // records (tag, clock) pairs in shared memory and copies them out when it ends.  Every warp has its own region of
@@ -103,7 +92,6 @@ __device__ __forceinline__ void record_failure(Shared& sm, int code) {
   // low byte: which wait gave up; above it: the linear index of the block
   const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   atomicCAS(&g_status, 0, code | static_cast<int>((block & 0x7fffffu) << 8));
-  atomicExch(&g_abort_epoch, sm.epoch);
   atomicExch(&sm.abort_flag, 1);
 }
 
@@ -114,17 +102,29 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static const EncodeTiledFn fn = [] {  // initialised once, also under concurrent first calls
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult result;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
         result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+      return reinterpret_cast<EncodeTiledFn>(ptr);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
   return fn;
+}
+
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of a kernel: one flag per
+// (kernel, device), set on the first launch there.
+constexpr int kMaxDevices = 64;
+template <class Kernel>
+int allow_shared_memory(Kernel kernel, std::atomic<bool> (&done)[kMaxDevices], size_t bytes) {
+  int device = 0;
+  WM_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices || !done[device].load(std::memory_order_acquire)) {
+    WM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    if (device >= 0 && device < kMaxDevices) done[device].store(true, std::memory_order_release);
+  }
+  return WM_OK;
 }
 
 // (batch, heads, tokens, 64) bf16 tensor with element strides s[0..2]; boxes of `rows` tokens x 64.
@@ -169,9 +169,12 @@ bool tma_ok(const void* p, const int64_t* s, int batch, int heads, int tokens) {
 // ---------------------------------------------------------------------------
 // device side
 
-// Bounded wait: gives up after about 0.1 s of clock ticks, or as soon as another role of the block or
-// another block of the same launch has given up.
-constexpr long long kWaitTicks = 200000000ll;
+// Bounded wait: gives up after about 0.1 s of clock ticks, or as soon as another role of the block has given up.
+// Nothing outlives the block: a launch that is replayed from a CUDA graph starts clean whatever happened before.
+#ifndef WM_B200_WAIT_TICKS
+#define WM_B200_WAIT_TICKS 200000000ll
+#endif
+constexpr long long kWaitTicks = WM_B200_WAIT_TICKS;
 
 template <class Shared>
 __device__ __forceinline__ bool wait_or_abort(Shared& sm, uint64_t* bar, uint32_t parity, int code) {
@@ -181,7 +184,6 @@ __device__ __forceinline__ bool wait_or_abort(Shared& sm, uint64_t* bar, uint32_
     if (ptx::mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 63u) {
       if (*reinterpret_cast<volatile int*>(&sm.abort_flag)) return false;
-      if (*reinterpret_cast<volatile int*>(&g_abort_epoch) == sm.epoch) return false;
       if (clock64() - begin > kWaitTicks) break;
     }
   }
@@ -295,7 +297,7 @@ struct TileWalk {
 
 #include "attn_tc_fwd.cuh"
 #include "attn_tc_bwd.cuh"
-#include "attn_tc_bwd_resident.cuh"
+#include "attn_tc_bwd_keys.cuh"
 
 }  // namespace
 
@@ -331,11 +333,9 @@ int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
   if (status != WM_OK) return status;
   dim3 grid(a.q_heads, a.batch, (a.q_len + kTileM - 1) / kTileM);
   const size_t smem = sizeof(FwdShared) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    WM_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    configured = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  status = allow_shared_memory(attn_fwd_tc_kernel, configured, smem);
+  if (status != WM_OK) return status;
   attn_fwd_tc_kernel<<<grid, kFwdThreads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
   count_launch();
   return cuda_check(cudaGetLastError(), "attn_fwd_tc_kernel");
@@ -370,7 +370,6 @@ int tc_device_status(bool reset) {
   if (reset && value != 0) {
     int zero = 0;
     cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    cudaMemcpyToSymbol(g_abort_epoch, &zero, sizeof(int));
   }
   return value;
 }
@@ -393,7 +392,7 @@ bool tc_bwd_supported(const wm_attn_args& a) {
 
 // The short-query pipeline keeps both query tiles of a (batch, head) resident.
 bool bwd_short_queries(const wm_attn_args& a) {
-  return a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
+  return a.q_len <= kMaxQueries && a.q_heads == a.kv_heads && a.k_len <= kKeysMaxTiles * kTileN;
 }
 
 size_t tc_attn_bwd_workspace(const wm_attn_args& a) {
@@ -422,29 +421,25 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
   count_launch();
   WM_CUDA(cudaGetLastError());
   if (bwd_short_queries(a)) {
-    const size_t smem_r = sizeof(ResidentShared) + 1024;
-    static bool configured_r = false;
-    if (!configured_r) {
-      WM_CUDA(cudaFuncSetAttribute(attn_bwd_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_r)));
-      configured_r = true;
-    }
+    const size_t smem_r = sizeof(KeysShared) + 1024;
+    static std::atomic<bool> configured_r[kMaxDevices];
+    status = allow_shared_memory(attn_bwd_keys_kernel, configured_r, smem_r);
+    if (status != WM_OK) return status;
     CUtensorMap map_dk, map_dv;
     status = make_map(&map_dk, a.dk, a.batch, a.kv_heads, a.k_len, a.dk_strides, kTileN);
     if (status != WM_OK) return status;
     status = make_map(&map_dv, a.dv, a.batch, a.kv_heads, a.k_len, a.dv_strides, kTileN);
     if (status != WM_OK) return status;
-    attn_bwd_resident_kernel<<<dim3(a.q_heads, a.batch), kResidentThreads, smem_r, stream>>>(map_q, map_k, map_v, map_g, map_dk,
-                                                                                   map_dv, a, delta, next_epoch());
+    attn_bwd_keys_kernel<<<dim3(a.q_heads, a.batch), kKeysThreads, smem_r, stream>>>(map_q, map_k, map_v, map_g, map_dk, map_dv, a,
+                                                                                     delta, next_epoch());
     count_launch();
     return cuda_check(cudaGetLastError(), "attention backward (tcgen05, resident queries)");
   }
   WM_CUDA(cudaMemsetAsync(dq_acc, 0, rows * kHeadDim * sizeof(float), stream));
   const size_t smem = sizeof(BwdShared) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    WM_CUDA(cudaFuncSetAttribute(attn_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    configured = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  status = allow_shared_memory(attn_bwd_tc_kernel, configured, smem);
+  if (status != WM_OK) return status;
   dim3 grid((a.k_len + kTileN - 1) / kTileN, a.kv_heads, a.batch);
   attn_bwd_tc_kernel<<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, map_g, a, delta, dq_acc, next_epoch());
   count_launch();
