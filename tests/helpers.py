@@ -74,16 +74,26 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     return (a.double() - b.double()).norm().item() / max(denom, 1e-30)
 
 
+PARITY_LOG: list[tuple[str, float, float, float]] = []  # (what, un-scaled max-abs error, |expected|max, rel-L2) of every check
+
+
 def assert_parity(actual: torch.Tensor, expected: torch.Tensor, *, max_abs_tol: float, rel_l2_tol: float, what: str = ""):
     """The parity gate of the attention path: max-abs and relative L2 error against the reference result."""
     actual, expected = actual.detach().cpu(), expected.detach().cpu()
     assert actual.shape == expected.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}"
     assert torch.isfinite(actual.float()).all(), f"{what}: non-finite values"
     ma, rl = max_abs(actual, expected), rel_l2(actual, expected)
-    # The absolute bound is stated for unit-scale tensors; a tensor whose entries reach magnitude M > 1 (gradients
-    # summed over many queries or heads) is held to the same bound relative to M.
-    bound = max_abs_tol * max(1.0, expected.abs().max().item() if expected.numel() else 0.0)
-    assert ma <= bound and rl <= rel_l2_tol, f"{what}: max_abs={ma:.3e} (tol {bound:.3e}), rel_l2={rl:.3e} (tol {rel_l2_tol})"
+    # The absolute bound is stated for unit-scale tensors.  A bf16 result cannot meet an absolute 2e-2 once its
+    # entries exceed about 8 (half an ulp of bf16 at 8 is 1.6e-2), so a tensor whose entries reach magnitude M > 1
+    # (gradients summed over many queries) is held to the same bound relative to M.  The un-scaled maximum error
+    # and M are part of the message and of PARITY_LOG, so that the relaxation is visible wherever it applies.
+    top = expected.abs().max().item() if expected.numel() else 0.0
+    bound = max_abs_tol * max(1.0, top)
+    PARITY_LOG.append((what, ma, top, rl))
+    assert ma <= bound and rl <= rel_l2_tol, (
+        f"{what}: max_abs={ma:.3e} un-scaled (bound {max_abs_tol:.1e} x max(1, |expected|max={top:.3g}) = {bound:.3e}), "
+        f"rel_l2={rl:.3e} (tol {rel_l2_tol})"
+    )
 
 
 # Tolerances of the parity contract: bf16 results within max-abs 2e-2 and

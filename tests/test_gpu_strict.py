@@ -179,3 +179,67 @@ def test_pool_read_at_full_size_matches_a_device_side_evaluation():
         s = (q128[b].float() @ kk.transpose(-1, -2) / 8).masked_fill(~keep, float("-inf"))
         p = torch.softmax(s, -1).nan_to_num(0.0)
         assert_parity(pre[b].transpose(0, 1).float(), p @ vv, what=f"prefill row {b}", **BF16_TOL)
+
+
+@pytest.mark.parametrize("backend", ["sm100_simt", "sm100"])
+@pytest.mark.parametrize("pads", [False, True])
+def test_softmax_scale_is_honoured_on_every_route(pads, backend):
+    """A plain Jacobi schedule goes to the cyclic document kernels, a schedule with padding to the gathered ones:
+    both have to use the caller's multiplier, forward and backward."""
+    torch.manual_seed(31)
+    B, H, T, D = 2, 2, 160, 64
+    docs = geometric_documents(B, T, 40, seed=5)
+    if pads:
+        docs[:, 50:55] = -1
+    q, k, v, probe = (torch.randn(B, H, T, D).bfloat16() for _ in range(4))
+    schedule = prepare_strict_causal_metadata(docs.cuda(), T)
+    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = strict_causal_attention(qq, kk, vv, metadata=schedule, softmax_scale=0.3, backend=backend)
+    grads = torch.autograd.grad(out, (qq, kk, vv), probe.transpose(1, 2).cuda())
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp = oracle.strict_causal_oracle(qo, ko, vo, metadata=prepare_strict_causal_metadata(docs, T), softmax_scale=0.3)
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.transpose(1, 2).double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert_parity(g.float(), e, what=name, **BF16_TOL)
+    default = strict_causal_attention(qq, kk, vv, metadata=schedule, backend=backend)
+    assert (default.float() - out.float()).abs().max().item() > 1e-2  # the multiplier does change the result
+
+
+@pytest.mark.parametrize("backend", ["sm100_simt", "sm100_tcgen05"])
+@pytest.mark.parametrize("masked", [False, True])
+@pytest.mark.parametrize("length", [128, 200])
+def test_gradients_with_nan_in_unused_capacity(length, masked, backend):
+    """Cached-prefix prefill with gradients: slots at or beyond kv_lengths hold NaN; the gradients must be finite,
+    match the oracle, and be exactly zero for the slots nobody sees."""
+    if masked and backend == "sm100_tcgen05":
+        pytest.skip("key_mask problems run on the SIMT kernels")
+    torch.manual_seed(41)
+    B, H, N, D = 2, 2, 333, 64
+    lengths = torch.tensor([150, 290])
+    starts = (lengths - length).clamp_min(0)
+    q, probe = (torch.randn(B, H, length, D).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, H, N, D).bfloat16() for _ in range(2))
+    key_mask = None
+    if masked:
+        key_mask = torch.rand(B, N) > 0.2
+    kn, vn = k.clone(), v.clone()
+    for b in range(B):
+        kn[b, :, int(lengths[b]):] = float("nan")
+        vn[b, :, int(lengths[b]):] = float("nan")
+    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, kn, vn))
+    out = strict_causal_attention(
+        qq, kk, vv, query_start=starts.cuda(), kv_lengths=lengths.cuda(), key_mask=None if key_mask is None else key_mask.cuda(),
+        backend=backend,
+    )
+    grads = torch.autograd.grad(out, (qq, kk, vv), probe.transpose(1, 2).cuda())
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp = oracle.strict_causal_oracle(qo, ko, vo, query_start=starts, kv_lengths=lengths, key_mask=key_mask)
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.transpose(1, 2).double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert torch.isfinite(g).all(), name
+        assert_parity(g.float(), e, what=name, **BF16_TOL)
+    for b in range(B):
+        assert grads[1][b, :, int(lengths[b]):].abs().max().item() == 0
+        assert grads[2][b, :, int(lengths[b]):].abs().max().item() == 0

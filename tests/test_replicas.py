@@ -27,6 +27,14 @@ def test_batch_first_then_heads():
         shard_batch_heads(2, 16, 0, 3)
 
 
+def test_grouped_heads_are_cut_between_kv_heads():
+    # 8 query heads over 2 KV heads, 2 rows on 4 ranks: a rank gets one row, one KV head and its 4 query heads
+    assert shard_batch_heads(2, 8, 3, 4, kv_heads=2) == (slice(1, 2), slice(4, 8), slice(1, 2))
+    assert shard_batch_heads(4, 8, 1, 2, kv_heads=2) == (slice(2, 4), slice(0, 8), slice(0, 2))
+    with pytest.raises(ValueError):
+        shard_batch_heads(1, 8, 0, 4, kv_heads=2)  # four ranks cannot share two KV heads
+
+
 def _worker(rank, world, port, results):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)

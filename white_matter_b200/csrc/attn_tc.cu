@@ -3,8 +3,8 @@
 // themselves, each in a header of its own:
 //   attn_tc_fwd.cuh       forward: one block per 128 query rows, two softmax groups on alternate key tiles, P kept
 //                         in tensor memory as the A operand of the PV product
-//   attn_tc_bwd_keys.cuh  backward for at most 256 queries per (batch, head) without grouped heads: one block per
-//                         (batch, head), key rows on the TMEM lanes, dQ resident in tensor memory
+//   attn_tc_bwd_resident.cuh  backward for at most 256 queries per (batch, head) without grouped heads: one block
+//                         per (batch, head), both query tiles and their dQ accumulators resident
 //   attn_tc_bwd.cuh       backward for every other shape: one block per key tile, dQ through fp32 atomics
 // Key tiles that no query can see are never loaded.  Every mbarrier wait is bounded; a wait that runs out records
 // its code in a device status word, and all roles of the block fall through to the common exit where tensor memory
@@ -297,7 +297,7 @@ struct TileWalk {
 
 #include "attn_tc_fwd.cuh"
 #include "attn_tc_bwd.cuh"
-#include "attn_tc_bwd_keys.cuh"
+#include "attn_tc_bwd_resident.cuh"
 
 }  // namespace
 
@@ -392,7 +392,7 @@ bool tc_bwd_supported(const wm_attn_args& a) {
 
 // The short-query pipeline keeps both query tiles of a (batch, head) resident.
 bool bwd_short_queries(const wm_attn_args& a) {
-  return a.q_len <= kMaxQueries && a.q_heads == a.kv_heads && a.k_len <= kKeysMaxTiles * kTileN;
+  return a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
 }
 
 size_t tc_attn_bwd_workspace(const wm_attn_args& a) {
@@ -421,17 +421,17 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
   count_launch();
   WM_CUDA(cudaGetLastError());
   if (bwd_short_queries(a)) {
-    const size_t smem_r = sizeof(KeysShared) + 1024;
+    const size_t smem_r = sizeof(ResidentShared) + 1024;
     static std::atomic<bool> configured_r[kMaxDevices];
-    status = allow_shared_memory(attn_bwd_keys_kernel, configured_r, smem_r);
+    status = allow_shared_memory(attn_bwd_resident_kernel, configured_r, smem_r);
     if (status != WM_OK) return status;
     CUtensorMap map_dk, map_dv;
     status = make_map(&map_dk, a.dk, a.batch, a.kv_heads, a.k_len, a.dk_strides, kTileN);
     if (status != WM_OK) return status;
     status = make_map(&map_dv, a.dv, a.batch, a.kv_heads, a.k_len, a.dv_strides, kTileN);
     if (status != WM_OK) return status;
-    attn_bwd_keys_kernel<<<dim3(a.q_heads, a.batch), kKeysThreads, smem_r, stream>>>(map_q, map_k, map_v, map_g, map_dk, map_dv, a,
-                                                                                     delta, next_epoch());
+    attn_bwd_resident_kernel<<<dim3(a.q_heads, a.batch), kResidentThreads, smem_r, stream>>>(map_q, map_k, map_v, map_g, map_dk,
+                                                                                             map_dv, a, delta, next_epoch());
     count_launch();
     return cuda_check(cudaGetLastError(), "attention backward (tcgen05, resident queries)");
   }

@@ -118,13 +118,14 @@ def _new_grads(q: Tensor, k: Tensor, v: Tensor) -> tuple[Tensor, Tensor, Tensor]
 # --------------------------------------------------------------------------- cyclic
 
 
-def _cyclic_args(Q, K, V, docs, K_stride, residue, kernel):
+def _cyclic_args(Q, K, V, docs, K_stride, residue, kernel, softmax_scale=0.0):
     if not -1 <= residue < K_stride:
         raise ValueError(f"cyclic residue must be in [-1, {K_stride}), got {residue}")
     q = _unit_inner(Q, Q.dtype)
     k = _unit_inner(K, Q.dtype)
     v = _unit_inner(V, Q.dtype)
-    a = _base_args(q, k, v, Q.shape[-1] ** -0.5, _native.WM_MASK_CYCLIC, kernel)
+    scale = float(softmax_scale) if softmax_scale > 0.0 else Q.shape[-1] ** -0.5
+    a = _base_args(q, k, v, scale, _native.WM_MASK_CYCLIC, kernel)
     a.query_stride, a.query_offset = K_stride, residue
     keep = [q, k, v]
     if docs is not None:
@@ -134,16 +135,16 @@ def _cyclic_args(Q, K, V, docs, K_stride, residue, kernel):
     return a, keep
 
 
-def _cyclic_fwd(Q, K, V, docs, K_stride, residue, kernel):
-    a, keep = _cyclic_args(Q, K, V, docs, K_stride, residue, kernel)
+def _cyclic_fwd(Q, K, V, docs, K_stride, residue, kernel, softmax_scale=0.0):
+    a, keep = _cyclic_args(Q, K, V, docs, K_stride, residue, kernel, softmax_scale)
     out, lse = _new_output(Q)
     _set_out(a, out, lse)
     _native.call("wm_cyclic_attn_fwd" if docs is None else "wm_cyclic_attn_doc_fwd", a, Q.device)
     return out, lse
 
 
-def _cyclic_bwd(Q, K, V, docs, Out, Lse, dOut, K_stride, residue, kernel):
-    a, keep = _cyclic_args(Q, K, V, docs, K_stride, residue, kernel)
+def _cyclic_bwd(Q, K, V, docs, Out, Lse, dOut, K_stride, residue, kernel, softmax_scale=0.0):
+    a, keep = _cyclic_args(Q, K, V, docs, K_stride, residue, kernel, softmax_scale)
     out = _unit_inner(Out, Q.dtype)
     dout = _unit_inner(dOut, Q.dtype)
     lse = Lse.contiguous()
@@ -157,25 +158,39 @@ def _cyclic_bwd(Q, K, V, docs, Out, Lse, dOut, K_stride, residue, kernel):
 
 
 @torch.library.custom_op("wm_b200::cyclic_attn_fwd", mutates_args=())
-def cyclic_attn_fwd(Q: Tensor, K: Tensor, V: Tensor, K_stride: int, residue: int, block_M: int) -> tuple[Tensor, Tensor]:
-    """Out (B,HQ,Q,D) view of (B,Q,HQ,D) storage and Lse (B,HQ,Q); block_M selects the kernel family."""
-    return _cyclic_fwd(Q, K, V, None, K_stride, residue, block_M)
+def cyclic_attn_fwd(
+    Q: Tensor, K: Tensor, V: Tensor, K_stride: int, residue: int, block_M: int, softmax_scale: float = 0.0
+) -> tuple[Tensor, Tensor]:
+    """Out (B,HQ,Q,D) view of (B,Q,HQ,D) storage and Lse (B,HQ,Q); block_M selects the kernel family.
+
+    ``softmax_scale`` (not in the upstream schema, which always scales by head_dim**-0.5) is the multiplier of the
+    scores; 0 stands for head_dim**-0.5."""
+    return _cyclic_fwd(Q, K, V, None, K_stride, residue, block_M, softmax_scale)
 
 
 @cyclic_attn_fwd.register_fake
-def _(Q, K, V, K_stride, residue, block_M):
+def _(Q, K, V, K_stride, residue, block_M, softmax_scale=0.0):
     return _fake_output(Q)
 
 
 @torch.library.custom_op("wm_b200::cyclic_attn_bwd", mutates_args=())
 def cyclic_attn_bwd(
-    Q: Tensor, K: Tensor, V: Tensor, Out: Tensor, Lse: Tensor, dOut: Tensor, K_stride: int, residue: int, block_M: int
+    Q: Tensor,
+    K: Tensor,
+    V: Tensor,
+    Out: Tensor,
+    Lse: Tensor,
+    dOut: Tensor,
+    K_stride: int,
+    residue: int,
+    block_M: int,
+    softmax_scale: float = 0.0,
 ) -> tuple[Tensor, Tensor, Tensor]:
-    return _cyclic_bwd(Q, K, V, None, Out, Lse, dOut, K_stride, residue, block_M)
+    return _cyclic_bwd(Q, K, V, None, Out, Lse, dOut, K_stride, residue, block_M, softmax_scale)
 
 
 @cyclic_attn_bwd.register_fake
-def _(Q, K, V, Out, Lse, dOut, K_stride, residue, block_M):
+def _(Q, K, V, Out, Lse, dOut, K_stride, residue, block_M, softmax_scale=0.0):
     return _fake_grads(Q, K, V)
 
 
@@ -191,12 +206,13 @@ def cyclic_attn_doc_fwd(
     K_stride: int,
     residue: int,
     block_M: int,
+    softmax_scale: float = 0.0,
 ) -> tuple[Tensor, Tensor]:
-    return _cyclic_fwd(Q, K, V, (QSeg, KSeg, QStart, KQEnd), K_stride, residue, block_M)
+    return _cyclic_fwd(Q, K, V, (QSeg, KSeg, QStart, KQEnd), K_stride, residue, block_M, softmax_scale)
 
 
 @cyclic_attn_doc_fwd.register_fake
-def _(Q, K, V, QSeg, KSeg, QStart, KQEnd, K_stride, residue, block_M):
+def _(Q, K, V, QSeg, KSeg, QStart, KQEnd, K_stride, residue, block_M, softmax_scale=0.0):
     return _fake_output(Q)
 
 
@@ -215,17 +231,18 @@ def cyclic_attn_doc_bwd(
     K_stride: int,
     residue: int,
     block_M: int,
+    softmax_scale: float = 0.0,
 ) -> tuple[Tensor, Tensor, Tensor]:
-    return _cyclic_bwd(Q, K, V, (QSeg, KSeg, QStart, KQEnd), Out, Lse, dOut, K_stride, residue, block_M)
+    return _cyclic_bwd(Q, K, V, (QSeg, KSeg, QStart, KQEnd), Out, Lse, dOut, K_stride, residue, block_M, softmax_scale)
 
 
 @cyclic_attn_doc_bwd.register_fake
-def _(Q, K, V, QSeg, KSeg, QStart, KQEnd, Out, Lse, dOut, K_stride, residue, block_M):
+def _(Q, K, V, QSeg, KSeg, QStart, KQEnd, Out, Lse, dOut, K_stride, residue, block_M, softmax_scale=0.0):
     return _fake_grads(Q, K, V)
 
 
 def _cyclic_setup(ctx, inputs, output):
-    *tensors, ctx.K_stride, ctx.residue, ctx.block_M = inputs
+    *tensors, ctx.K_stride, ctx.residue, ctx.block_M, ctx.softmax_scale = inputs
     ctx.save_for_backward(*tensors, *output)
     ctx.set_materialize_grads(False)  # no zero fill for the unused gradient of Lse on every backward call
 
@@ -235,8 +252,8 @@ def _cyclic_backward(ctx, dOut, dLse):
     if dOut is None:
         dOut = torch.zeros_like(tensors[-2])
     op = cyclic_attn_doc_bwd if len(tensors) == 9 else cyclic_attn_bwd
-    grads = op(*tensors, dOut, ctx.K_stride, ctx.residue, ctx.block_M)
-    return (*grads, *((None,) * (len(tensors) - 2)))
+    grads = op(*tensors, dOut, ctx.K_stride, ctx.residue, ctx.block_M, ctx.softmax_scale)
+    return (*grads, *((None,) * (len(tensors) - 1)))
 
 
 cyclic_attn_fwd.register_autograd(_cyclic_backward, setup_context=_cyclic_setup)

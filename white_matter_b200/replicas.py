@@ -21,17 +21,29 @@ def shard_range(total: int, rank: int, world: int) -> tuple[int, int]:
     return begin, begin + base + (1 if rank < extra else 0)
 
 
-def shard_batch_heads(batch: int, heads: int, rank: int, world: int) -> tuple[slice, slice]:
-    """Batch slice and head slice of a rank: batch first, heads only when there are more ranks than rows."""
+def shard_batch_heads(batch: int, heads: int, rank: int, world: int, kv_heads: int | None = None):
+    """Batch slice and head slice of a rank: batch first, heads only when there are more ranks than rows.
+
+    With grouped query heads (``kv_heads`` given and smaller than ``heads``) the heads are cut between KV heads, so
+    that a rank holds whole groups, and three slices come back: batch, query heads, KV heads.
+    """
+    kv = heads if kv_heads is None else kv_heads
+    if kv < 1 or heads % kv:
+        raise ValueError("heads must be a multiple of kv_heads")
+    group = heads // kv
     if world <= batch:
         b0, b1 = shard_range(batch, rank, world)
-        return slice(b0, b1), slice(0, heads)
-    per_row = -(-world // batch)  # ranks sharing one batch row
-    if heads % per_row or batch * per_row != world:
-        raise ValueError("world size must be batch * (a divisor of heads) when it exceeds the batch")
-    row, part = divmod(rank, per_row)
-    h0, h1 = shard_range(heads, part, per_row)
-    return slice(row, row + 1), slice(h0, h1)
+        rows, q_part, kv_part = slice(b0, b1), slice(0, heads), slice(0, kv)
+    else:
+        per_row = -(-world // batch)  # ranks sharing one batch row
+        if kv % per_row or batch * per_row != world:
+            raise ValueError("world size must be batch * (a divisor of the KV heads) when it exceeds the batch")
+        row, part = divmod(rank, per_row)
+        h0, h1 = shard_range(kv, part, per_row)
+        rows, q_part, kv_part = slice(row, row + 1), slice(h0 * group, h1 * group), slice(h0, h1)
+    if kv_heads is None:
+        return rows, q_part
+    return rows, q_part, kv_part
 
 
 def aggregate_throughput(local_ms: float, local_units: float, device: torch.device | None = None) -> tuple[float, float]:

@@ -102,7 +102,7 @@ def strict_causal_attention(
         ):
             cyc = metadata.cyclic_equivalent(query.device, length)
             out = operators.cyclic_attn_doc_fwd(
-                query, key[..., :length, :], value[..., :length, :], *cyc, 1, lead_slots - 1, kernel
+                query, key[..., :length, :], value[..., :length, :], *cyc, 1, lead_slots - 1, kernel, scale
             )[0]
             return out.transpose(1, 2)
         fwd_q, bwd_q, bwd_k = operators.packed_tile_rows(query, key, kernel)
