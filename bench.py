@@ -11,11 +11,13 @@ residues, forward and backward, 16 operator calls.  Inputs are synthetic
 
 The headline ``value`` is TFLOP/s on the visible (query,key) pairs only,
 14*head_dim FLOP per pair (4 forward, 10 backward), with inputs resident in
-HBM.  The 8 residue calls of a step are independent; the step's CUDA graph has
-them on ``--streams`` streams (default 8) so that the blocks of one call fill
-the partial last wave of another; ``one_stream`` is the same step with its
-launches one after another, which is also what the per-kernel ``roofline``
-figures are taken from.  ``e2e`` is the same metric through the public functions with every step's
+HBM, the 16 operator calls of a step stream-ordered one after another (in the
+model the residue groups depend on one another: K/V are refreshed after each
+group), replayed from a CUDA graph.  ``multi_stream`` is a labelled extra: the
+same calls spread over 8 streams, which a caller whose calls are independent
+may do.  ``eager`` is the same step without the graph (host-bound).
+``--scaling strong`` splits the B=16 rows over the ranks instead of giving
+every rank its own 16.  ``e2e`` is the same metric through the public functions with every step's
 inputs copied in from pinned host buffers and every step's results copied back
 inside the timed region; the copies run on their own streams beside the kernels
 of the neighbouring steps (``e2e.serialized`` is the same work on one stream).  The same line also reports the
@@ -152,18 +154,19 @@ class ClockSampler:
 class TrainingSweep:
     """Device-resident inputs of one 8-residue sweep and the calls of one step."""
 
-    def __init__(self, device, seed, backend="sm100"):
+    def __init__(self, device, seed, backend="sm100", rows=slice(0, B)):
         from white_matter_b200 import cyclic_attention, prepare_feedback_metadata
 
         self.attention = cyclic_attention
         self.backend = backend
         self.device = device
-        self.docs = geometric_documents(B, T, DOC_MEAN, seed=7 + seed)
+        self.docs = geometric_documents(B, T, DOC_MEAN, seed=7 + seed)[rows]
+        self.batch = self.docs.shape[0]
         groups = [torch.arange(r, T, STRIDE) for r in range(STRIDE)]
         metas = prepare_feedback_metadata(self.docs, groups, T, use_dummy_token=False)
         self.metas = [tuple(t.to(device) for t in m) for m in metas]
         gen = torch.Generator().manual_seed(seed)
-        shape_q, shape_k = (B, H, T // STRIDE, D), (B, H, T, D)
+        shape_q, shape_k = (self.batch, H, T // STRIDE, D), (self.batch, H, T, D)
         # pinned host copies feed the end-to-end arm; the device copies feed the kernel arm
         self.host = {
             "q": [torch.randn(shape_q, generator=gen).bfloat16().pin_memory() for _ in range(STRIDE)],
@@ -354,28 +357,32 @@ class TrainingSweep:
         torch.cuda.synchronize()
         return begin.elapsed_time(end)
 
-    @staticmethod
-    def staging_bytes():
-        q_bytes = B * H * (T // STRIDE) * D * 2
-        k_bytes = B * H * T * D * 2
+    def staging_bytes(self):
+        q_bytes = self.batch * H * (T // STRIDE) * D * 2
+        k_bytes = self.batch * H * T * D * 2
         return 2 * STRIDE * q_bytes + 2 * k_bytes, 2 * STRIDE * q_bytes + 2 * k_bytes
+
+    def call_bytes(self):
+        """Algorithmic HBM bytes of one residue call: forward reads Q, K, V and writes O and the row statistics;
+        backward reads Q, K, V, O, dO and the statistics and writes dQ, dK, dV."""
+        q_bytes = self.batch * H * (T // STRIDE) * D * 2
+        k_bytes = self.batch * H * T * D * 2
+        stat = self.batch * H * (T // STRIDE) * 4
+        return 2 * q_bytes + 2 * k_bytes + stat, 4 * q_bytes + 4 * k_bytes + 2 * stat
 
     def staging(self):
         dev = self.device
-        shape_q, shape_k = (B, H, T // STRIDE, D), (B, H, T, D)
+        shape_q, shape_k = (self.batch, H, T // STRIDE, D), (self.batch, H, T, D)
         mk = lambda s: torch.empty(s, dtype=torch.bfloat16, device=dev)
         pin = lambda s: torch.empty(s, dtype=torch.bfloat16).pin_memory()
         s = {
             "q": [mk(shape_q) for _ in range(STRIDE)], "g": [mk(shape_q) for _ in range(STRIDE)],
             "k": mk(shape_k), "v": mk(shape_k),
-            "out_host": [pin((B, T // STRIDE, H, D)) for _ in range(STRIDE)],
+            "out_host": [pin((self.batch, T // STRIDE, H, D)) for _ in range(STRIDE)],
             "dq_host": [pin(shape_q) for _ in range(STRIDE)],
             "dk_host": pin(shape_k), "dv_host": pin(shape_k),
         }
-        q_bytes = B * H * (T // STRIDE) * D * 2
-        k_bytes = B * H * T * D * 2
-        s["h2d"] = 2 * STRIDE * q_bytes + 2 * k_bytes
-        s["d2h"] = 2 * STRIDE * q_bytes + 2 * k_bytes
+        s["h2d"], s["d2h"] = self.staging_bytes()
         return s
 
 
@@ -461,17 +468,19 @@ def bench_jacobi(device, peaks, iters=10):
 
 
 def bench_mixing(device, peaks, iters=10):
-    """25-source mixture of a per-GPU shard: sources (25, 4, 16, 2048, 64) bf16 = 419 MB, read once."""
+    """25-source mixture at the training configuration's size: sources (25, 16, 16, 2048, 64) bf16 = 1.68 GB, read once."""
     from white_matter_b200 import mix_kv_sources
 
-    src = torch.randn(25, 4, 16, 2048, 64, device=device, dtype=torch.bfloat16)
+    src = torch.empty(25, B, H, T, D, device=device, dtype=torch.bfloat16)
+    for i in range(25):  # filled source by source: no fp32 temporary of the whole stack
+        src[i].normal_()
     logits = torch.randn(25, device=device)
     call = lambda: mix_kv_sources(src, logits)
     ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
     nbytes = src.numel() * 2 + src[0].numel() * 2
     gbs = nbytes / (ms * 1e-3) / 1e9
     return {
-        "workload": "mix 25 sources (25,4,16,2048,64) bf16, 419 MB read + 17 MB written",
+        "workload": "mix 25 sources (25,16,16,2048,64) bf16, 1678 MB read + 67 MB written",
         "ms": ms, "bytes": nbytes, "value": gbs, "unit": "GB/s",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["mix_fwd_kernel"]},
@@ -511,6 +520,67 @@ def bench_query_prepare(device, peaks, iters=20):
     }
 
 
+def bench_incumbents(device, iters=10):
+    """The library kernels the upstream GPU backends call (src/white_matter/ops/flash_attention.py:15-36,52-103), timed
+    on the same GPU as comparators: FlashAttention-2 (flash_attn package) and PyTorch's flash SDPA.  Labelled extras:
+    nothing of this library's path runs here."""
+    out = {}
+    batch, heads, slots, dim = 64, 16, 8192, 64
+    gen = torch.Generator().manual_seed(0)
+    lengths = torch.randint(1, slots + 1, (batch,), generator=gen).to(device)
+    k = torch.randn(batch, slots, heads, dim, device=device, dtype=torch.bfloat16)
+    v = torch.randn(batch, slots, heads, dim, device=device, dtype=torch.bfloat16)
+    q = torch.randn(batch, 1, heads, dim, device=device, dtype=torch.bfloat16)
+    nbytes = int(lengths.sum().item()) * 2 * heads * dim * 2
+    try:
+        from flash_attn import flash_attn_varlen_func, flash_attn_with_kvcache
+
+        call = lambda: flash_attn_with_kvcache(q, k, v, cache_seqlens=lengths.int(), causal=True)
+        ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+        out["flash_attn_with_kvcache decode"] = {"ms": ms, "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
+                                                 "workload": "B=64 H=16 D=64 lengths~U[1,8192], cache (B,N,H,D)"}
+        # Jacobi prefill as the upstream flash path runs it: packed documents as varlen sequences (strict past = causal
+        # attention of each token over its predecessors, without the diagonal: the upstream path shifts by one)
+        b2, t2 = 8, 2048
+        docs = geometric_documents(b2, t2, 512, seed=7)
+        lens = []
+        for row in docs.tolist():
+            run = 1
+            for t in range(1, t2):
+                if row[t] == row[t - 1]:
+                    run += 1
+                else:
+                    lens.append(run)
+                    run = 1
+            lens.append(run)
+        cu = torch.tensor([0] + lens, device=device).cumsum(0).int()
+        qv = torch.randn(b2 * t2, heads, dim, device=device, dtype=torch.bfloat16)
+        kv = torch.randn(b2 * t2, heads, dim, device=device, dtype=torch.bfloat16)
+        vv = torch.randn(b2 * t2, heads, dim, device=device, dtype=torch.bfloat16)
+        call = lambda: flash_attn_varlen_func(qv, kv, vv, cu, cu, max(lens), max(lens), causal=True)
+        ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+        pairs = sum(n * (n + 1) // 2 for n in lens) * heads
+        out["flash_attn_varlen_func prefill"] = {"ms": ms, "value": 4 * dim * pairs / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                                 "workload": "B=8 T=2048 documents of mean 512 as varlen sequences, causal"}
+    except Exception as exc:  # the package is optional
+        out["flash_attn"] = {"unavailable": str(exc)[:200]}
+    try:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+
+        b2, t2 = 8, 2048
+        qd = torch.randn(b2, heads, t2, dim, device=device, dtype=torch.bfloat16)
+        kd, vd = torch.randn_like(qd), torch.randn_like(qd)
+        with sdpa_kernel([SDPBackend.FLASH_ATTENTION]):
+            call = lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, is_causal=True)
+            ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+        pairs = b2 * heads * t2 * (t2 + 1) // 2
+        out["torch flash SDPA dense causal"] = {"ms": ms, "value": 4 * dim * pairs / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                                "workload": "B=8 H=16 T=2048 D=64 dense causal (no documents)"}
+    except Exception as exc:
+        out["torch_sdpa"] = {"unavailable": str(exc)[:200]}
+    return out
+
+
 def use_all_host_threads():
     """torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU legs are meant to use every core the process may run on."""
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
@@ -519,8 +589,9 @@ def use_all_host_threads():
     return torch.get_num_threads()
 
 
-def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1):
-    """The CPU oracle on a bounded sample of the training workload: `rows` batch rows, the given residues, fwd+bwd, fp32.
+def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1, dtype=torch.float32):
+    """The CPU oracle on a bounded sample of the training workload: `rows` batch rows, the given residues, fwd+bwd,
+    in `dtype` (fp32, or bf16 as the upstream portable backend runs bf16 tensors on the CPU).
 
     The default sample is one whole step (all 16 rows, all 8 residues).
     Returns (TFLOP/s over the sample's visible pairs, seconds per repeat, threads, description).
@@ -534,10 +605,10 @@ def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1):
     groups = [torch.arange(r, T, STRIDE) for r in range(STRIDE)]
     metas = prepare_feedback_metadata(docs, groups, T, use_dummy_token=False)
     gen = torch.Generator().manual_seed(0)
-    q = torch.randn(rows, H, T // STRIDE, D, generator=gen).requires_grad_()
-    k = torch.randn(rows, H, T, D, generator=gen).requires_grad_()
-    v = torch.randn(rows, H, T, D, generator=gen).requires_grad_()
-    g = torch.randn(rows, H, T // STRIDE, D, generator=gen)
+    q = torch.randn(rows, H, T // STRIDE, D, generator=gen).to(dtype).requires_grad_()
+    k = torch.randn(rows, H, T, D, generator=gen).to(dtype).requires_grad_()
+    v = torch.randn(rows, H, T, D, generator=gen).to(dtype).requires_grad_()
+    g = torch.randn(rows, H, T // STRIDE, D, generator=gen).to(dtype)
     flops = 14 * D * sum(visible_pairs_per_head(docs, r, STRIDE) for r in residues) * H
     best = None
     for _ in range(repeats):
@@ -545,12 +616,13 @@ def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1):
         for r in residues:
             out = oracle.cyclic_attention_oracle(
                 q, k, v, query_stride=STRIDE, query_offset=r, strict_past=True, metadata=metas[r],
-                compute_dtype=torch.float32,
+                compute_dtype=dtype,
             )
             torch.autograd.grad(out, (q, k, v), g)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    what = (f"{rows} of {B} batch rows, {len(residues)} of {STRIDE} residues, fwd+bwd fp32, "
+    name = {torch.float32: "fp32", torch.bfloat16: "bf16"}.get(dtype, str(dtype))
+    what = (f"{rows} of {B} batch rows, {len(residues)} of {STRIDE} residues, fwd+bwd {name}, "
             "oracle port on torch CPU, all host threads")
     return flops / best / 1e12, best, torch.get_num_threads(), what
 
@@ -559,48 +631,68 @@ def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1):
 
 
 def run_reference_arm(args, rank, world):
-    """The upstream algorithm on the host cores (the CPU oracle port), bounded sample per step."""
+    """The upstream algorithm on the host cores (the CPU oracle port): one step is the whole workload step, all 16
+    batch rows and all 8 residues, in whichever of fp32 and bf16 the host runs faster (the configuration is bf16;
+    the upstream portable backend evaluates bf16 tensors in bf16 on the CPU)."""
     if rank != 0:
         return
-    # one step of the reference arm = a quarter of the workload's step (4 of 16 batch rows, all residues)
-    rows = 4
-    for _ in range(min(args.warmup, 1)):
-        cpu_sample(rows=rows)
+    probes = {dt: cpu_sample(dtype=dt) for dt in (torch.float32, torch.bfloat16)}
+    dtype = max(probes, key=lambda dt: probes[dt][0])
+    for _ in range(max(args.warmup - 1, 0)):
+        cpu_sample(dtype=dtype)
     t0 = time.perf_counter()
-    values = [cpu_sample(rows=rows) for _ in range(args.steps)]
+    values = [cpu_sample(dtype=dtype) for _ in range(args.steps)]
     wall = time.perf_counter() - t0
     tflops = statistics.median(v[0] for v in values)
     line = {
         "impl": "reference", "metric": "cyclic_attention fwd+bwd TFLOP/s", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": values[0][2], "kind": "port", "sample": values[0][3]},
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+        "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
+        "config": workload_config(args.gpus, args.scaling),
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": values[0][2], "kind": "port", "sample": values[0][3],
+                         "fp32_tflops": probes[torch.float32][0], "bf16_tflops": probes[torch.bfloat16][0]},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
+def workload_config(n_gpus, scaling="weak"):
+    per_gpu = B if scaling == "weak" else -(-B // n_gpus)
     return {
         "workload": "cyclic_attention training sweep fwd+bwd: B=16 H=16 K=2048 Q=256/residue D=64 stride=8, "
                     "8 residues per step, packed documents (geometric, mean 1024), strict_past, bf16",
-        "per_gpu_batch": B, "global_batch": B * n_gpus, "heads": H, "key_len": T, "head_dim": D,
-        "query_stride": STRIDE, "parallelism": f"replicas x{n_gpus} over batch (no collective)",
+        "per_gpu_batch": per_gpu, "global_batch": B * n_gpus if scaling == "weak" else B, "heads": H, "key_len": T,
+        "head_dim": D, "query_stride": STRIDE,
+        "parallelism": f"replicas x{n_gpus} over batch (no collective), {scaling} scaling",
+        "calls": "16 operator calls per step, stream-ordered one after another, replayed from a CUDA graph",
         "l2": "inputs larger than L2: K+V 134 MB per sweep, rotated over 2 input sets",
         "flops": "14*D per visible (query,key) pair",
     }
 
 
+def eager_step_us(work, steps=5):
+    """Host time (us) of one operator call when a step is issued eagerly: 16 calls, wall clock around `steps` steps
+    with one synchronisation at the end (the calls are launch-bound, so the host is what is being timed)."""
+    work.step(None)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        work.step(None)
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / (steps * 2 * STRIDE) * 1e6
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--backend", default="sm100", help="kernel family: sm100 | sm100_simt | sm100_tcgen05")
+    parser.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                        help="weak: every rank runs its own B=16 rows; strong: the B=16 rows are split over the ranks")
     parser.add_argument("--no-graph", action="store_true", help="issue the operator calls eagerly instead of replaying a CUDA graph")
-    parser.add_argument("--streams", type=int, default=8, help="streams the 8 independent residue calls of a step alternate over (1: one after another)")
     parser.add_argument("--skip-extras", action="store_true", help="only the headline workload (used for profiling)")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -626,11 +718,21 @@ def main():
             torch.cuda.synchronize()
 
     from white_matter_b200 import _native
+    from white_matter_b200.replicas import aggregate_throughput, shard_batch_heads
 
     lib = _native.load_library()
     peaks, peak_kind = load_peaks()
-    sets = [TrainingSweep(device, seed=rank * 2 + i, backend=args.backend) for i in range(2)]
-    from white_matter_b200.replicas import aggregate_throughput
+    rows = slice(0, B)
+    if args.scaling == "strong":
+        if world > B:
+            raise SystemExit("strong scaling splits the 16 batch rows: at most 16 ranks")
+        rows = shard_batch_heads(B, H, rank, world)[0]
+    seed_of = (lambda i: rank * 2 + i) if args.scaling == "weak" else (lambda i: i)  # strong: slices of one problem
+    sets = [TrainingSweep(device, seed=seed_of(i), backend=args.backend, rows=rows) for i in range(2)]
+    status = {}
+
+    def check(where):
+        status[where] = int(lib.wm_device_status(1))
 
     # end to end (measured first, before the CUDA graphs of the device-resident arm exist): pinned host -> device -> pinned host every step
     staging = sets[0].staging()
@@ -645,22 +747,20 @@ def main():
     # of this arm vary by 2x from box to box: the better of two runs is reported
     piped_ms = min(sets[0].e2e_pipelined_ms(e2e_steps, warmup=3) for _ in range(2))
     sync()
+    check("e2e")
     torch.cuda.empty_cache()
     piped_max_ms, piped_flops = aggregate_throughput(piped_ms, float(sets[0].flops * e2e_steps), device)
     e2e_value = piped_flops / (piped_max_ms * 1e-3) / 1e12
+    eager_us = eager_step_us(sets[0])
 
-    if args.streams > 1:  # gradients of K and V are produced on the side streams on purpose
-        getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", lambda flag: None)(False)
     turn = [0]
     per_step_launches = None
     if not args.no_graph:
-        per_step_launches = [s.capture(args.streams) for s in sets][0]
-
-    eager_streams = [torch.cuda.Stream() for _ in range(args.streams)] if args.no_graph and args.streams > 1 else None
+        per_step_launches = [s.capture(1) for s in sets][0]
 
     def step():
         if args.no_graph:
-            sets[turn[0] % 2].step(eager_streams)
+            sets[turn[0] % 2].step(None)
         else:
             sets[turn[0] % 2].replay()
         turn[0] += 1
@@ -676,24 +776,44 @@ def main():
     if per_step_launches is not None:
         launches = per_step_launches * args.steps  # kernels inside the replayed graphs
     clocks = sampler.stop()
+    check("headline")
 
     flops = sum(sets[i % 2].flops for i in range(args.steps))
     step_ms, total_flops = aggregate_throughput(ms, float(flops), device)
     value = total_flops / (step_ms * 1e-3) / 1e12
 
-    # per-kernel device time, launches one after another: a graph with the 8 forward launches alone, replayed and
-    # timed with CUDA events; the backward kernel group is the one-stream step minus the forward part
+    # per-kernel device time: a graph with the 8 forward launches alone, replayed and timed with CUDA events; the
+    # backward kernel group is the step minus the forward part
     work = sets[0]
     fwd_ms = work.forward_only_ms(reps=max(3, min(args.steps, 20))) / STRIDE
     step_device_ms = step_ms / args.steps
-    one_stream_ms = None
     if not args.no_graph:
-        one_stream_ms = work.one_stream_ms(reps=max(3, min(args.steps, 20)))
-        step_device_ms = one_stream_ms
+        step_device_ms = work.one_stream_ms(reps=max(3, min(args.steps, 20)))
     bwd_ms = max(step_device_ms / STRIDE - fwd_ms, 1e-6)
     tensor_peak = peaks["bf16_tflops_sustained"]
     fwd_tf = work.flops_fwd / STRIDE / (fwd_ms * 1e-3) / 1e12
     bwd_tf = (work.flops - work.flops_fwd) / STRIDE / (bwd_ms * 1e-3) / 1e12
+    fwd_bytes, bwd_bytes = work.call_bytes()
+    hbm = peaks["hbm_gbs"]
+
+    def hbm_view(nbytes, call_ms, flops_of_call):
+        """Where the call stands against the HBM-limited ceiling: at the stride-8 shape a call moves 128 FLOP per
+        byte, below the ridge of the machine, so bandwidth bounds it before the tensor pipe does."""
+        floor_ms = nbytes / (hbm * 1e9) * 1e3
+        return {"algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (call_ms * 1e-3) / 1e9, "hbm_frac": floor_ms / call_ms,
+                "ceiling_tflops": flops_of_call / (floor_ms * 1e-3) / 1e12}
+
+    multi = None
+    if not args.no_graph and not args.skip_extras:
+        # labelled extra, not the headline: the same 16 calls spread over 8 streams, which only a caller whose residue
+        # calls do not depend on one another may do
+        getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", lambda flag: None)(False)
+        work.capture(STRIDE)
+        multi_ms = time_steps(work.replay, max(3, min(args.steps, 20)), 2, sync) / max(3, min(args.steps, 20))
+        multi = {"ms_per_step": multi_ms, "value": work.flops / (multi_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "streams": STRIDE,
+                 "note": "not the headline: the 8 residue calls of a step on 8 streams fill each other's partial waves; in the model "
+                         "the residue groups depend on one another and run one after another"}
+        check("multi_stream")
 
     extras = {}
     if not args.skip_extras:
@@ -702,26 +822,34 @@ def main():
         extras["jacobi"] = bench_jacobi(device, peaks)
         extras["mixing"] = bench_mixing(device, peaks)
         extras["query_prepare"] = bench_query_prepare(device, peaks)
+        check("extras")
+        if world == 1:
+            torch.cuda.empty_cache()
+            extras["incumbents"] = bench_incumbents(device)
     if rank == 0:
         line = {
             "metric": "cyclic_attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
-            "device_status": int(lib.wm_device_status(0)), "backend": args.backend, "launch_mode": ("eager" if args.no_graph else "cuda graph replay of one step") + (f", the 8 independent residue calls alternating over {args.streams} streams" if args.streams > 1 else ""),
-            "one_stream": None if one_stream_ms is None else {"ms_per_step": one_stream_ms, "value": work.flops / (one_stream_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "note": "the same step with its 24 launches one after another; the roofline figures are per kernel out of this"},
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(world, args.scaling), "clocks": clocks, "gpu_launches": int(launches),
+            "device_status": status, "backend": args.backend,
+            "launch_mode": "eager" if args.no_graph else "cuda graph replay of one step, its 24 launches one after another",
+            "multi_stream": multi,
+            "eager": {"host_us_per_call": eager_us, "note": "the same step without the graph: 16 operator calls, host-bound"},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": sets[0].staging_bytes()[0],
                     "d2h_bytes_per_step": sets[0].staging_bytes()[1],
                     "mode": "copies on their own streams beside the kernels of the neighbouring steps (two staging sets)",
                     "serialized": e2e_serial, "steps": e2e_steps, "runs": "best of 2"},
             "roofline": {"bound": "tensor", "kernel": "backward kernels of one residue call (attn_bwd_resident_kernel + bwd_delta_kernel)",
                          "achieved": bwd_tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": bwd_tf / tensor_peak,
-                         "traffic": NCU_TRAFFIC_BYTES["attn_bwd_resident_kernel"] if args.backend != "sm100_simt" else None, "peak_kind": f"{peak_kind} bf16_tflops_sustained", "ms": bwd_ms},
+                         "traffic": NCU_TRAFFIC_BYTES["attn_bwd_resident_kernel"] if args.backend != "sm100_simt" else None,
+                         "peak_kind": f"{peak_kind} bf16_tflops_sustained", "ms": bwd_ms,
+                         "hbm": hbm_view(bwd_bytes, bwd_ms, (work.flops - work.flops_fwd) / STRIDE)},
             "roofline_forward": {"bound": "tensor", "kernel": "attn_fwd_tc_kernel, one residue call",
                                  "achieved": fwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
                                  "frac": fwd_tf / tensor_peak,
                                  "traffic": NCU_TRAFFIC_BYTES["attn_fwd_tc_kernel"] if args.backend != "sm100_simt" else None,
-                                 "ms": fwd_ms},
+                                 "ms": fwd_ms, "hbm": hbm_view(fwd_bytes, fwd_ms, work.flops_fwd / STRIDE)},
         }
         line.update(extras)
         if world == 1 and not args.skip_extras:
