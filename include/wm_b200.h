@@ -186,11 +186,6 @@ WM_API const char* wm_last_error(void);
 WM_API int wm_device_status(int reset);
 /* Number of kernels this library has launched in the process so far (diagnostic). */
 WM_API unsigned long long wm_kernel_launch_count(void);
-/* Developer facility, no counterpart in the reference: pipeline event trace of the tcgen05 kernels.  Arms the
- * trace for the launch after the next `arm_after` launches (negative: disarm) and copies out the (tag, clock)
- * pairs block (0,0,0) recorded so far; returns their count.  Always 0 unless the library was built with
- * -DWM_B200_TRACE (python -m white_matter_b200.build --trace). */
-WM_API int wm_debug_trace(long long* out, int capacity, int arm_after);
 
 /* Rows per tile that the kernel selected for `args` cuts packed groups into
  * (queries when key_side == 0, keys otherwise; backward != 0 for the gradient kernels). */
@@ -239,7 +234,7 @@ WM_API int wm_strict_decode_no_alloc(const wm_attn_args* args, void* stream);
 WM_API int wm_mix_sources_fwd(const wm_mix_args* args, void* stream);
 WM_API int wm_mix_sources_bwd(const wm_mix_args* args, void* stream);
 
-/* the step in front of the attention operators inside the attention layer (first of the "next" components) */
+/* the step in front of the attention operators inside the attention layer: q_norm, rotary embedding, layout change */
 WM_API int wm_query_prepare_fwd(const wm_qprep_args* args, void* stream);
 WM_API int wm_query_prepare_bwd(const wm_qprep_args* args, void* stream);
 

@@ -92,7 +92,7 @@ def main(upstream_src: str) -> None:
             strict_past=strict_past, docs=docs, seed=seed, inputs_stored=store_inputs,
         )
 
-    # BASELINE config 1: inputs are regenerated from the seed, only results are stored
+    # the CPU-runnable fp32 configuration (B=2, H=4, 256 keys, stride 4): inputs are regenerated from the seed, only results are stored
     cyclic_case("c1", 2, 4, 4, 64, 256, 64, 4, 0, True, None, 0, store_inputs=False)
     cyclic_case("cyc_gqa", 2, 4, 2, 33, 132, 64, 4, 1, False, None, 23)
     cyclic_case("cyc_gqa_docs", 2, 4, 2, 33, 132, 64, 4, 1, False, "sorted", 23)

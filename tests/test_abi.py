@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol that include/wm_b200.h declares (no GPU work)."""
+"""The C-ABI library loads and exports every symbol that include/*.h declare (no GPU work)."""
 
 import ctypes
 import re
@@ -10,10 +10,11 @@ from white_matter_b200 import _native
 
 ROOT = Path(__file__).resolve().parent.parent
 HEADER = (ROOT / "include" / "wm_b200.h").read_text()
+ALL_HEADERS = "\n".join(p.read_text() for p in sorted((ROOT / "include").glob("*.h")))
 
 
 def declared_symbols():
-    return sorted(set(re.findall(r"^WM_API [\w\s\*]*?\b(wm_\w+)\s*\(", HEADER, flags=re.M)))
+    return sorted(set(re.findall(r"^WM_API [\w\s\*]*?\b(wm_\w+)\s*\(", ALL_HEADERS, flags=re.M)))
 
 
 def test_header_declares_the_operator_roles():

@@ -326,3 +326,34 @@ def test_first_cuda_action_of_a_thread_may_be_the_backward_call():
     )
     done = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0 and "ok" in done.stdout, done.stderr[-2000:]
+
+
+@pytest.mark.expects_wait_timeout
+def test_a_wait_that_runs_out_is_reported_and_the_next_launch_is_clean():
+    """Every mbarrier wait of the pipelined kernels is bounded.  A one-block kernel of the library waits, with the
+    limit shortened to a millisecond, on a barrier that nothing arrives on: the wait has to give up, leave its code
+    in the status word and return normally (no trap, no fault), and the launches after it must be unaffected."""
+    import ctypes
+
+    from white_matter_b200 import _native
+
+    lib = _native.load_library()
+    lib.wm_debug_expire_wait.argtypes = [ctypes.c_longlong, ctypes.c_void_p]
+    lib.wm_debug_expire_wait.restype = ctypes.c_int
+    assert _native.device_status(True) == 0
+    assert lib.wm_debug_expire_wait(2_000_000, torch.cuda.current_stream().cuda_stream) == 0
+    status = _native.device_status(True)  # synchronises, reads and clears
+    assert status & 255 == 250 and status >> 8 == 0
+    assert _native.device_status(False) == 0
+    # limits outside (0, the production limit] are refused before any launch
+    assert lib.wm_debug_expire_wait(0, None) != 0
+    torch.manual_seed(9)
+    q = torch.randn(2, 4, 65, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(2, 4, 260, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn_like(k, requires_grad=True)
+    out = cyclic_attention(q, k, v, query_stride=4, backend="sm100_tcgen05")
+    grads = torch.autograd.grad(out, (q, k, v), torch.randn_like(out))
+    assert _native.device_status(True) == 0
+    exp = oracle.cyclic_attention_oracle(q.detach().cpu().double(), k.detach().cpu().double(), v.detach().cpu().double(), query_stride=4)
+    assert_parity(out.float(), exp, what="out after an expired wait", **BF16_TOL)
+    assert all(torch.isfinite(g).all() for g in grads)

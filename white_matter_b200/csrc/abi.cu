@@ -6,6 +6,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "wm_b200_debug.h"
 
 namespace wm {
 
@@ -69,16 +70,7 @@ int validate_attn(const wm_attn_args* a, bool backward, const char* who) {
   return WM_OK;
 }
 
-// WM_B200_FORCE_SIMT=1 in the environment routes every attention call to the SIMT kernels (bring-up aid).
-bool force_simt() {
-  static const bool forced = [] {
-    const char* v = getenv("WM_B200_FORCE_SIMT");
-    return v != nullptr && v[0] == '1';
-  }();
-  return forced;
-}
-
-bool want_tc(const wm_attn_args* a) { return a->kernel != WM_KERNEL_SIMT && !(force_simt() && a->kernel == WM_KERNEL_AUTO); }
+bool want_tc(const wm_attn_args* a) { return a->kernel != WM_KERNEL_SIMT; }
 
 namespace {
 
@@ -117,6 +109,10 @@ const char* wm_last_error(void) { return wm::g_error; }
 
 int wm_debug_trace(long long* out, int capacity, int arm_after) {
   return wm::tc_debug_trace(out, capacity, arm_after);
+}
+
+int wm_debug_expire_wait(long long limit_ticks, void* stream) {
+  return wm::tc_debug_expire_wait(limit_ticks, static_cast<cudaStream_t>(stream));
 }
 
 int wm_device_status(int reset) { return wm::tc_device_status(reset != 0); }

@@ -177,14 +177,15 @@ bool tma_ok(const void* p, const int64_t* s, int batch, int heads, int tokens) {
 constexpr long long kWaitTicks = WM_B200_WAIT_TICKS;
 
 template <class Shared>
-__device__ __forceinline__ bool wait_or_abort(Shared& sm, uint64_t* bar, uint32_t parity, int code) {
+__device__ __forceinline__ bool wait_or_abort(Shared& sm, uint64_t* bar, uint32_t parity, int code,
+                                              long long limit = kWaitTicks) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long begin = clock64();
   for (uint32_t spin = 0;; ++spin) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 63u) {
       if (*reinterpret_cast<volatile int*>(&sm.abort_flag)) return false;
-      if (clock64() - begin > kWaitTicks) break;
+      if (clock64() - begin > limit) break;
     }
   }
   record_failure(sm, code);
@@ -295,6 +296,27 @@ struct TileWalk {
   int kmax;
 };
 
+// A wait that nothing will ever satisfy, with a short limit: what the bounded waits do when they run out (the
+// status word gets the code, the block leaves through its normal exit).
+struct ExpireShared {
+  uint64_t never;
+  int abort_flag;
+  int epoch;
+};
+
+__global__ void expire_wait_kernel(long long limit) {
+  __shared__ ExpireShared sm;
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    sm.epoch = 0;
+    ptx::mbar_init(&sm.never, 1);
+    ptx::mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) wait_or_abort(sm, &sm.never, 0, 250, limit);
+  __syncthreads();
+}
+
 #include "attn_tc_fwd.cuh"
 #include "attn_tc_bwd.cuh"
 #include "attn_tc_bwd_resident.cuh"
@@ -362,6 +384,13 @@ int tc_debug_trace(long long* out, int capacity, int arm_after) {
   (void)arm_after;
   return 0;
 #endif
+}
+
+int tc_debug_expire_wait(long long limit_ticks, cudaStream_t stream) {
+  if (limit_ticks < 1 || limit_ticks > kWaitTicks) return fail(WM_EINVAL, "wm_debug_expire_wait: the limit must be in [1, %lld] ticks", kWaitTicks);
+  expire_wait_kernel<<<1, 32, 0, stream>>>(limit_ticks);
+  count_launch();
+  return cuda_check(cudaGetLastError(), "expire_wait_kernel");
 }
 
 int tc_device_status(bool reset) {

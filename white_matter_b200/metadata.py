@@ -40,15 +40,23 @@ class CyclicAttentionMetadata(NamedTuple):
     key_query_end: torch.Tensor
 
 
+def _runs(row: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """First index of every run of equal values of a 1-D array, and the exclusive end of every run."""
+    first = np.flatnonzero(np.concatenate(([True], row[1:] != row[:-1])))
+    return first, np.append(first[1:], row.size)
+
+
 def prepare_cyclic_attention_metadata(
     query_document_ids: torch.Tensor, key_document_ids: torch.Tensor, *, use_dummy_token: bool = True
 ) -> CyclicAttentionMetadata:
     """Bounds from sorted per-row document ids of queries and key slots.
 
-    Same contract as upstream metadata.py:17-56: integer (batch, length)
-    matrices, ids nondecreasing per row, nonnegative except for the leading
-    dummy key (id -1) that must be present when ``use_dummy_token``; ids must
-    fit int32.
+    Same contract, checks and messages as upstream metadata.py:17-56: integer (batch, length) matrices, ids
+    nondecreasing per row, nonnegative except for the leading dummy key (id -1) that must be present when
+    ``use_dummy_token``; ids must fit int32.  The tables themselves are worked out on the host from the runs of
+    equal ids (a row has a handful of documents, whatever its length): a query's first key is the first slot of the
+    first key run whose id reaches the query's id, a key's query bound the end of the last query run whose id does
+    not exceed the key's.
     """
     if query_document_ids.ndim != 2 or key_document_ids.ndim != 2:
         raise ValueError("segment IDs must have shape (batch, length)")
@@ -62,23 +70,43 @@ def prepare_cyclic_attention_metadata(
     for ids in (query_document_ids, key_document_ids):
         if ids.dtype not in (torch.int32, torch.int64):
             raise ValueError("segment IDs must be int32 or int64")
-        if ids.dtype == torch.int64 and bool((ids > _INT32_MAX).any()):
+    device = query_document_ids.device
+    q_host = query_document_ids.detach().cpu().numpy().astype(np.int64)
+    k_host = key_document_ids.detach().cpu().numpy().astype(np.int64)
+    for ids in (q_host, k_host):
+        if ids.max(initial=0) > _INT32_MAX:
             raise ValueError("segment IDs must fit int32 (maximum 2147483647)")
-        if bool((ids[:, 1:] < ids[:, :-1]).any()):
+        if (np.diff(ids, axis=1) < 0).any():
             raise ValueError("segment IDs must be nondecreasing within each row")
     lead = int(use_dummy_token)
-    if bool((query_document_ids < 0).any()) or bool((key_document_ids[:, lead:] < 0).any()):
+    if (q_host < 0).any() or (k_host[:, lead:] < 0).any():
         raise ValueError("only the leading key dummy may have a negative segment ID")
-    if use_dummy_token and not bool((key_document_ids[:, 0] == -1).all()):
+    if use_dummy_token and not (k_host[:, 0] == -1).all():
         raise ValueError("document attention requires a leading dummy key with segment ID -1")
-    queries = query_document_ids.to(torch.int32).contiguous()
-    keys = key_document_ids.to(torch.int32).contiguous()
-    # first key slot whose id reaches the query's id / number of queries whose id does not exceed the key's
-    first_key = torch.searchsorted(keys, queries).to(torch.int32)
-    query_end = torch.searchsorted(queries, keys, right=True).to(torch.int32)
+    batch, n_q = q_host.shape
+    n_k = k_host.shape[1]
+    first_key = np.empty((batch, n_q), dtype=np.int32)
+    query_end = np.empty((batch, n_k), dtype=np.int32)
+    for b in range(batch):
+        q_first, q_stop = _runs(q_host[b])
+        k_first, k_stop = _runs(k_host[b])
+        q_ids, k_ids = q_host[b][q_first], k_host[b][k_first]
+        # per query run: the key run it starts at (the first one whose id is not smaller); behind the last run: n_k
+        at = np.searchsorted(k_ids, q_ids, side="left")
+        run_start = np.append(k_first, n_k)[at]
+        first_key[b] = np.repeat(run_start, q_stop - q_first)
+        # per key run: the query run it ends with (the last one whose id is not larger); in front of the first: 0
+        upto = np.searchsorted(q_ids, k_ids, side="right")
+        run_end = np.concatenate(([0], q_stop))[upto]
+        query_end[b] = np.repeat(run_end, k_stop - k_first)
     if use_dummy_token:
-        query_end[:, 0] = queries.shape[1]
-    return CyclicAttentionMetadata(queries, keys, first_key, query_end)
+        query_end[:, 0] = n_q
+    return CyclicAttentionMetadata(
+        query_document_ids.to(torch.int32).contiguous(),
+        key_document_ids.to(torch.int32).contiguous(),
+        torch.from_numpy(first_key).to(device),
+        torch.from_numpy(query_end).to(device),
+    )
 
 
 def prepare_feedback_metadata(
@@ -88,12 +116,14 @@ def prepare_feedback_metadata(
     *,
     use_dummy_token: bool = True,
 ) -> tuple[CyclicAttentionMetadata, ...]:
-    """Per-residue metadata from token document ids (B,T).
+    """Per-residue metadata from token document ids (B,T); the tensors upstream
+    blocks/_execution/metadata.py:11-55 builds.
 
-    Group r holds the query tokens ``query_positions[r]`` (r, r+stride, ...).
-    With a dummy, key slot 0 is shared (-1) and slot s+1 stores token s;
-    otherwise slot s stores token s.  Padding tokens (negative ids) become
-    document -2.  Follows blocks/_execution/metadata.py:11-55.
+    Group r holds the query tokens ``query_positions[r]`` (r, r+stride, ...).  With a dummy, key slot 0 is shared
+    (-1) and slot s+1 stores token s; otherwise slot s stores token s.  Padding tokens (negative ids) become
+    document -2.  A token's document is the run of equal ids it sits in: its queries start at the run's first slot,
+    and a key is open to the queries of residue r that lie in front of its run's end, ceil((end - r) / stride) of
+    them.
     """
     lead = int(use_dummy_token)
     stride = len(query_positions)
@@ -103,27 +133,30 @@ def prepare_feedback_metadata(
     if key_length > length + lead:
         raise ValueError(f"key_length={key_length} exceeds dummy-shifted token extent {length + lead}")
     device = document_ids.device
-    index = torch.arange(length, device=device).expand(batch, length)
-    begins = torch.ones_like(document_ids, dtype=torch.bool)
-    begins[:, 1:] = document_ids[:, 1:] != document_ids[:, :-1]
-    # first token of each token's document, and first token of the next document
-    doc_first = torch.where(begins, index, 0).cummax(dim=1).values
-    next_first = torch.full_like(index, length)
-    next_first[:, :-1] = torch.where(begins[:, 1:], index[:, 1:], length)
-    doc_end = next_first.flip((1,)).cummin(dim=1).values.flip((1,))
-
-    labels = document_ids.to(torch.int32).masked_fill(document_ids < 0, -2)
-    key_ids = torch.cat((labels.new_full((batch, lead), -1), labels), dim=1)[:, :key_length].contiguous()
+    ids = document_ids.detach().cpu().numpy().astype(np.int64)
+    run_first = np.empty((batch, length), dtype=np.int64)  # first token of each token's run
+    run_stop = np.empty((batch, length), dtype=np.int64)   # first token behind it
+    for b in range(batch):
+        first, stop = _runs(ids[b])
+        run_first[b] = np.repeat(first, stop - first)
+        run_stop[b] = np.repeat(stop, stop - first)
+    labels = np.where(ids < 0, -2, ids).astype(np.int32)
+    key_ids = np.concatenate((np.full((batch, lead), -1, dtype=np.int32), labels), axis=1)[:, :key_length]
+    key_ids_t = torch.from_numpy(np.ascontiguousarray(key_ids)).to(device)
     result = []
     for residue, slots in enumerate(query_positions):
-        count = slots.numel()
-        query_ids = labels.index_select(1, slots).contiguous()
-        key_start = doc_first.index_select(1, slots).to(torch.int32).add_(lead).contiguous()
-        # number of queries of this residue that lie before the end of each token's document
-        ends = torch.div((doc_end - residue).clamp_min(0) + stride - 1, stride, rounding_mode="floor")
-        ends = ends.clamp_max(count).to(torch.int32)
-        query_end = torch.cat((labels.new_full((batch, lead), count), ends), dim=1)[:, :key_length].contiguous()
-        result.append(CyclicAttentionMetadata(query_ids, key_ids, key_start, query_end))
+        at = slots.detach().cpu().numpy()
+        count = at.size
+        ends = np.clip(-(-(run_stop - residue) // stride), 0, count).astype(np.int32)
+        query_end = np.concatenate((np.full((batch, lead), count, dtype=np.int32), ends), axis=1)[:, :key_length]
+        result.append(
+            CyclicAttentionMetadata(
+                torch.from_numpy(np.ascontiguousarray(labels[:, at])).to(device),
+                key_ids_t,
+                torch.from_numpy((run_first[:, at] + lead).astype(np.int32)).to(device),
+                torch.from_numpy(np.ascontiguousarray(query_end)).to(device),
+            )
+        )
     return tuple(result)
 
 

@@ -398,13 +398,18 @@ def _(Q, K, V, query_start, query_start_value, kv_lengths, key_mask, use_dummy, 
 
 
 def decode_supported(Q: Tensor, K: Tensor, V: Tensor) -> bool:
-    """Whether the split-KV read kernel takes these layouts (16-byte rows)."""
+    """Whether the split-KV read kernel takes these layouts (16-byte rows).
+
+    While a compiler traces the caller there are no addresses to look at: the strides decide alone, and a view that
+    does turn out to start off a 16-byte boundary is refused by the library when the call runs."""
     esize = Q.element_size()
     vec = 16 // esize
     if Q.shape[-1] % vec or Q.shape[-1] > 32 * vec:
         return False
+    tracing = torch.compiler.is_compiling()
     for t in (Q, K, V):
-        if t.stride(-1) != 1 or t.data_ptr() % 16 or any((s * esize) % 16 for s in t.stride()[:3]):
+        misaligned = False if tracing else t.data_ptr() % 16 != 0
+        if t.stride(-1) != 1 or misaligned or any((s * esize) % 16 for s in t.stride()[:3]):
             return False
     return True
 
