@@ -177,6 +177,23 @@ typedef struct wm_qprep_args {
   float eps;
 } wm_qprep_args;
 
+/* Commit of new tokens to a static KV pool (models/cache.py:43-60 of the reference: the update of a static cache
+ * layer, an index_copy_ at the layer's running length): row (b, h, i) of `src` goes to slot
+ * lengths[b] + lead + i of `pool`, for i < n_new; rows whose slot would lie beyond `capacity` are dropped.  `pool`
+ * is (batch, heads, capacity, head_dim), `src` (batch, heads, n_new, head_dim), both with unit stride in head_dim and
+ * element strides for (batch, head, token); head_dim * element size must be a multiple of 16 bytes and all rows
+ * 16-byte aligned.  The lengths stay on the device and are not changed by the call. */
+typedef struct wm_pool_append_args {
+  void* pool;
+  const void* src;
+  const int32_t* lengths; /* (batch,) committed real tokens per sequence */
+  int64_t pool_strides[3];
+  int64_t src_strides[3];
+  int32_t dtype;
+  int32_t batch, heads, capacity, n_new, head_dim;
+  int32_t lead; /* 1 when slot 0 is the shared dummy */
+} wm_pool_append_args;
+
 WM_API int wm_abi_version(void);
 WM_API const char* wm_last_error(void);
 /* Status word of the pipelined kernels on the current device: 0 when every bounded
@@ -229,6 +246,9 @@ WM_API int wm_strict_decode(const wm_attn_args* args, void* stream);
  * - Calls no cudaMalloc / cudaFree and no allocating library routine.
  */
 WM_API int wm_strict_decode_no_alloc(const wm_attn_args* args, void* stream);
+
+/* commit of new K or V rows to a static pool at device-resident lengths */
+WM_API int wm_pool_append(const wm_pool_append_args* args, void* stream);
 
 /* KV source mixing */
 WM_API int wm_mix_sources_fwd(const wm_mix_args* args, void* stream);

@@ -5,6 +5,7 @@ live in ``libwm_b200.so`` behind the C ABI of ``include/wm_b200.h``.
 """
 
 from .cyclic import cyclic_attention
+from .decode_step import DecodeStepGraph, KVPoolCache, document_key_mask
 from .metadata import (
     CyclicAttentionMetadata,
     StrictCausalMetadata,
@@ -27,4 +28,7 @@ __all__ = [
     "prepare_cyclic_attention_metadata",
     "prepare_feedback_metadata",
     "mix_kv_sources",
+    "KVPoolCache",
+    "DecodeStepGraph",
+    "document_key_mask",
 ]

@@ -123,6 +123,25 @@ class QueryPrepArgs(ctypes.Structure):
     ]
 
 
+class PoolAppendArgs(ctypes.Structure):
+    """Mirror of ``wm_pool_append_args``."""
+
+    _fields_ = [
+        ("pool", ctypes.c_void_p),
+        ("src", ctypes.c_void_p),
+        ("lengths", ctypes.c_void_p),
+        ("pool_strides", _Strides),
+        ("src_strides", _Strides),
+        ("dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("capacity", ctypes.c_int32),
+        ("n_new", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("lead", ctypes.c_int32),
+    ]
+
+
 ATTN_ENTRY_POINTS = (
     "wm_cyclic_attn_fwd",
     "wm_cyclic_attn_bwd",
@@ -180,6 +199,8 @@ def load_library() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.argtypes = [ctypes.POINTER(QueryPrepArgs), ctypes.c_void_p]
             fn.restype = ctypes.c_int
+        lib.wm_pool_append.argtypes = [ctypes.POINTER(PoolAppendArgs), ctypes.c_void_p]
+        lib.wm_pool_append.restype = ctypes.c_int
         lib.wm_query_prepare_workspace_bytes.argtypes = [ctypes.POINTER(QueryPrepArgs)]
         lib.wm_query_prepare_workspace_bytes.restype = ctypes.c_size_t
         lib.wm_abi_version.argtypes = []

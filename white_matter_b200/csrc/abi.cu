@@ -199,6 +199,11 @@ int wm_strict_decode_no_alloc(const wm_attn_args* a, void* stream) {
   return wm::decode_launch_with_scratch(*a, scratch, static_cast<cudaStream_t>(stream));
 }
 
+int wm_pool_append(const wm_pool_append_args* a, void* stream) {
+  if (a == nullptr) return wm::fail(WM_EINVAL, "wm_pool_append: null arguments");
+  return wm::pool_append_launch(*a, static_cast<cudaStream_t>(stream));
+}
+
 int wm_mix_sources_fwd(const wm_mix_args* a, void* stream) {
   if (a == nullptr) return wm::fail(WM_EINVAL, "wm_mix_sources_fwd: null arguments");
   return wm::mix_fwd_launch(*a, static_cast<cudaStream_t>(stream));

@@ -34,6 +34,7 @@ int decode_launch_with_scratch(const wm_attn_args& a, float* scratch, cudaStream
 bool decode_supported(const wm_attn_args& a);
 size_t decode_static_capacity();
 int decode_static_scratch(float** out);
+int pool_append_launch(const wm_pool_append_args& a, cudaStream_t stream);
 int mix_fwd_launch(const wm_mix_args& a, cudaStream_t stream);
 int mix_bwd_launch(const wm_mix_args& a, cudaStream_t stream);
 size_t mix_workspace(const wm_mix_args& a);

@@ -373,4 +373,42 @@ int decode_launch(const wm_attn_args& a, cudaStream_t stream) {
   return decode_launch_with_scratch(a, static_cast<float*>(a.workspace), stream);
 }
 
+// ---------------------------------------------------------------------------
+// commit of new rows to a static pool: one 16-byte word per thread
+__global__ void pool_append_kernel(const wm_pool_append_args a, int words_per_row, int esize) {
+  const long long word = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = static_cast<long long>(a.batch) * a.heads * a.n_new * words_per_row;
+  if (word >= total) return;
+  const int w = static_cast<int>(word % words_per_row);
+  long long rest = word / words_per_row;
+  const int i = static_cast<int>(rest % a.n_new);
+  rest /= a.n_new;
+  const int h = static_cast<int>(rest % a.heads);
+  const int b = static_cast<int>(rest / a.heads);
+  const long long slot = static_cast<long long>(a.lengths[b]) + a.lead + i;
+  if (slot < 0 || slot >= a.capacity) return;
+  const char* src = static_cast<const char*>(a.src) + (b * a.src_strides[0] + h * a.src_strides[1] + i * a.src_strides[2]) * esize;
+  char* dst = static_cast<char*>(a.pool) + (b * a.pool_strides[0] + h * a.pool_strides[1] + slot * a.pool_strides[2]) * esize;
+  reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(src)[w];
+}
+
+int pool_append_launch(const wm_pool_append_args& a, cudaStream_t stream) {
+  if (a.pool == nullptr || a.src == nullptr || a.lengths == nullptr) return fail(WM_EINVAL, "wm_pool_append: pool, src and lengths are required");
+  if (a.dtype != WM_F32 && a.dtype != WM_BF16) return fail(WM_EINVAL, "wm_pool_append: dtype must be WM_F32 or WM_BF16");
+  if (a.batch < 1 || a.heads < 1 || a.capacity < 1 || a.n_new < 1 || a.head_dim < 1) return fail(WM_EINVAL, "wm_pool_append: sizes must be positive");
+  if (a.lead != 0 && a.lead != 1) return fail(WM_EINVAL, "wm_pool_append: lead must be 0 or 1");
+  const int esize = a.dtype == WM_F32 ? 4 : 2;
+  if ((a.head_dim * esize) % 16) return fail(WM_EUNSUPPORTED, "wm_pool_append: head_dim must be a multiple of 16 bytes");
+  if (reinterpret_cast<uintptr_t>(a.pool) % 16 || reinterpret_cast<uintptr_t>(a.src) % 16)
+    return fail(WM_EUNSUPPORTED, "wm_pool_append: rows must be 16-byte aligned");
+  for (int i = 0; i < 3; ++i)
+    if ((a.pool_strides[i] * esize) % 16 || (a.src_strides[i] * esize) % 16)
+      return fail(WM_EUNSUPPORTED, "wm_pool_append: rows must be 16-byte aligned");
+  const int words = a.head_dim * esize / 16;
+  const long long total = static_cast<long long>(a.batch) * a.heads * a.n_new * words;
+  pool_append_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(a, words, esize);
+  count_launch();
+  return cuda_check(cudaGetLastError(), "pool_append_kernel");
+}
+
 }  // namespace wm
