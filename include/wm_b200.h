@@ -177,6 +177,71 @@ typedef struct wm_qprep_args {
   float eps;
 } wm_qprep_args;
 
+/* Source mixing of the KV pool (modules/kv_pool.py:97-146 and modules/routing.py:82-122 of the reference: the part
+ * of KVPool._project before the per-channel projections).  For every token row it normalises each of the
+ * `sources` layer inputs (RMS, source_eps), applies the K- and V-side pre-mix gains, mixes them into `channels`
+ * vectors per side with signed routing logits, normalises each mixture (RMS, mix_eps) and applies the post-mix
+ * gain -- one read of the layer stack and one write of the projection inputs instead of the reference's chain of
+ * full-size temporaries:
+ *
+ *   n[l]   = x[l] * rsqrt(mean(x[l]^2) + source_eps)
+ *   a[c,l] = bias[c*sources + l] + sum_j partial[j, row, c*sources + l] * rsqrt(mean(x[s_j]^2) + source_eps)
+ *   h[c]   = sum_l a[c,l] * pre_mix[l] * n[l]
+ *   out[c, row] = h[c] * rsqrt(mean(h[c]^2) + mix_eps) * gain[c]
+ *
+ * with s_j = route_start + j * route_stride the sources the router reads.  `partial` carries the content-dependent
+ * part of the logits, not yet scaled by the sources' norms: partial[j] = x[s_j] @ (router_weight[:, j] *
+ * pre_mix[s_j])^T, one plain GEMM per routed source that the caller runs on the raw layer stack; n_routed = 0 (or
+ * NULL partials) gives the static router whose logits are the bias alone.  `stacked` is (batch, tokens, sources,
+ * hidden) with element strides for (batch, token, source) and unit stride in hidden; the partials are
+ * (n_routed, batch*tokens, channels*sources) contiguous; the results are (channels, batch*tokens, hidden)
+ * contiguous, the A operand of the per-channel projection.  stacked, partials and results share `dtype`; gains,
+ * biases are float32.  hidden must be a multiple of 128 and at most 2048; sources at most 32. */
+typedef struct wm_pool_mix_args {
+  const void* stacked;
+  int64_t stacked_strides[3];
+  const float* pre_mix_k; /* (sources, hidden) */
+  const float* pre_mix_v;
+  const float* bias_k; /* (channels * sources,) */
+  const float* bias_v;
+  const void* partial_k; /* NULL for a static router */
+  const void* partial_v;
+  const float* gain_k; /* (channels, hidden) */
+  const float* gain_v;
+  void* mixed_k;
+  void* mixed_v;
+  int32_t dtype;
+  int32_t batch, tokens, sources, channels, hidden;
+  int32_t route_start, route_stride, n_routed;
+  float source_eps, mix_eps;
+} wm_pool_mix_args;
+
+/* Publication of projected channels into the KV pool (modules/kv_pool.py:147-176 of the reference: the permute of
+ * the projected channels, the per-channel key norm and the rotary embedding; blocks/_execution/cyclic.py:406-424:
+ * the copy into the pool).  `k_proj` and `v_proj` are the per-channel projections (channels, batch*tokens,
+ * kv_heads*head_dim) contiguous in `in_dtype`.  Keys get rms_norm(eps) over head_dim, the channel's gain
+ * k_norm_weight[c] and the rotary embedding of row rope_offset + t of cos / sin; values are moved unchanged.  Both
+ * land at slot token_offset + t of head c*kv_heads + h of `k_out` / `v_out`, which are (batch, channels*kv_heads,
+ * capacity, head_dim) in `out_dtype` with element strides out_strides for (batch, head, slot) -- the wire format of
+ * the decode cache, or a fresh (batch, channels, kv_heads, tokens, head_dim) tensor.  cos / sin are float32
+ * (batch, >= rope_offset + tokens, head_dim) with element strides cs_strides for (batch, row); a batch stride of 0
+ * broadcasts one table. */
+typedef struct wm_pool_finish_args {
+  const void* k_proj;
+  const void* v_proj;
+  const float* k_norm_weight; /* (channels, head_dim) */
+  const float* cos;
+  const float* sin;
+  void* k_out;
+  void* v_out;
+  int64_t cs_strides[2];
+  int64_t out_strides[3];
+  int32_t in_dtype, out_dtype;
+  int32_t batch, tokens, channels, kv_heads, head_dim; /* head_dim 64 or 128 */
+  int32_t token_offset, rope_offset;
+  float eps;
+} wm_pool_finish_args;
+
 /* Commit of new tokens to a static KV pool (models/cache.py:43-60 of the reference: the update of a static cache
  * layer, an index_copy_ at the layer's running length): row (b, h, i) of `src` goes to slot
  * lengths[b] + lead + i of `pool`, for i < n_new; rows whose slot would lie beyond `capacity` are dropped.  `pool`
@@ -249,6 +314,10 @@ WM_API int wm_strict_decode_no_alloc(const wm_attn_args* args, void* stream);
 
 /* commit of new K or V rows to a static pool at device-resident lengths */
 WM_API int wm_pool_append(const wm_pool_append_args* args, void* stream);
+
+/* KV-pool projection path either side of its per-channel GEMMs */
+WM_API int wm_pool_mix(const wm_pool_mix_args* args, void* stream);
+WM_API int wm_pool_finish(const wm_pool_finish_args* args, void* stream);
 
 /* KV source mixing */
 WM_API int wm_mix_sources_fwd(const wm_mix_args* args, void* stream);

@@ -44,13 +44,41 @@ def test_abi_version_and_argument_rejection_without_a_device():
     assert lib.wm_mix_sources_fwd(ctypes.byref(mix), None) == -1
 
 
-def test_struct_layout_matches_header_field_order():
-    fields = [name for name, _ in _native.AttnArgs._fields_]
-    body = HEADER.split("typedef struct wm_attn_args {")[1].split("} wm_attn_args;")[0]
+STRUCTS = {
+    "wm_attn_args": _native.AttnArgs,
+    "wm_mix_args": _native.MixArgs,
+    "wm_qprep_args": _native.QueryPrepArgs,
+    "wm_pool_append_args": _native.PoolAppendArgs,
+    "wm_pool_mix_args": _native.PoolMixArgs,
+    "wm_pool_finish_args": _native.PoolFinishArgs,
+}
+C_TYPES = {"int64_t": ctypes.c_int64, "int32_t": ctypes.c_int32, "size_t": ctypes.c_size_t, "float": ctypes.c_float}
+
+
+def header_fields(struct):
+    """(name, ctypes type) of every member of a struct of the public header, in order."""
+    body = HEADER.split(f"typedef struct {struct} {{")[1].split(f"}} {struct};")[0]
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
-    declared = re.findall(r"(\w+)(?:\[3\])?;", body)
-    assert fields == declared
-    mix_fields = [name for name, _ in _native.MixArgs._fields_]
-    body = HEADER.split("typedef struct wm_mix_args {")[1].split("} wm_mix_args;")[0]
-    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
-    assert mix_fields == re.findall(r"(\w+);", body)
+    fields = []
+    for statement in filter(None, (part.strip() for part in body.split(";"))):
+        match = re.fullmatch(r"(?:const\s+)?(\w+)\s*(\*?)\s*(.+)", statement, flags=re.S)
+        base = match.group(1) + match.group(2)
+        for declarator in match.group(3).split(","):
+            name, _, extent = declarator.strip().partition("[")
+            kind = ctypes.c_void_p if base.endswith("*") else C_TYPES[base]
+            fields.append((name.strip(), kind * int(extent.rstrip("]")) if extent else kind))
+    return fields
+
+
+def test_every_struct_of_the_header_is_mirrored():
+    assert sorted(re.findall(r"typedef struct (\w+) \{", HEADER)) == sorted(STRUCTS)
+
+
+@pytest.mark.parametrize("struct", sorted(STRUCTS))
+def test_struct_layout_matches_header(struct):
+    declared = header_fields(struct)
+    mirrored = STRUCTS[struct]._fields_
+    assert [name for name, _ in mirrored] == [name for name, _ in declared]
+    for (name, have), (_, want) in zip(mirrored, declared):
+        assert ctypes.sizeof(have) == ctypes.sizeof(want), name
+        assert (have is ctypes.c_float) == (want is ctypes.c_float), name

@@ -13,6 +13,7 @@ from .metadata import (
     prepare_feedback_metadata,
     prepare_strict_causal_metadata,
 )
+from .kv_pool import KVPool
 from .layer import cyclic_attention_layer, prepare_queries
 from .mixing import mix_kv_sources
 from .strict import strict_causal_attention
@@ -28,6 +29,7 @@ __all__ = [
     "prepare_cyclic_attention_metadata",
     "prepare_feedback_metadata",
     "mix_kv_sources",
+    "KVPool",
     "KVPoolCache",
     "DecodeStepGraph",
     "document_key_mask",

@@ -142,6 +142,62 @@ class PoolAppendArgs(ctypes.Structure):
     ]
 
 
+class PoolMixArgs(ctypes.Structure):
+    """Mirror of ``wm_pool_mix_args``."""
+
+    _fields_ = [
+        ("stacked", ctypes.c_void_p),
+        ("stacked_strides", _Strides),
+        ("pre_mix_k", ctypes.c_void_p),
+        ("pre_mix_v", ctypes.c_void_p),
+        ("bias_k", ctypes.c_void_p),
+        ("bias_v", ctypes.c_void_p),
+        ("partial_k", ctypes.c_void_p),
+        ("partial_v", ctypes.c_void_p),
+        ("gain_k", ctypes.c_void_p),
+        ("gain_v", ctypes.c_void_p),
+        ("mixed_k", ctypes.c_void_p),
+        ("mixed_v", ctypes.c_void_p),
+        ("dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("tokens", ctypes.c_int32),
+        ("sources", ctypes.c_int32),
+        ("channels", ctypes.c_int32),
+        ("hidden", ctypes.c_int32),
+        ("route_start", ctypes.c_int32),
+        ("route_stride", ctypes.c_int32),
+        ("n_routed", ctypes.c_int32),
+        ("source_eps", ctypes.c_float),
+        ("mix_eps", ctypes.c_float),
+    ]
+
+
+class PoolFinishArgs(ctypes.Structure):
+    """Mirror of ``wm_pool_finish_args``."""
+
+    _fields_ = [
+        ("k_proj", ctypes.c_void_p),
+        ("v_proj", ctypes.c_void_p),
+        ("k_norm_weight", ctypes.c_void_p),
+        ("cos", ctypes.c_void_p),
+        ("sin", ctypes.c_void_p),
+        ("k_out", ctypes.c_void_p),
+        ("v_out", ctypes.c_void_p),
+        ("cs_strides", ctypes.c_int64 * 2),
+        ("out_strides", _Strides),
+        ("in_dtype", ctypes.c_int32),
+        ("out_dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("tokens", ctypes.c_int32),
+        ("channels", ctypes.c_int32),
+        ("kv_heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("token_offset", ctypes.c_int32),
+        ("rope_offset", ctypes.c_int32),
+        ("eps", ctypes.c_float),
+    ]
+
+
 ATTN_ENTRY_POINTS = (
     "wm_cyclic_attn_fwd",
     "wm_cyclic_attn_bwd",
@@ -201,6 +257,10 @@ def load_library() -> ctypes.CDLL:
             fn.restype = ctypes.c_int
         lib.wm_pool_append.argtypes = [ctypes.POINTER(PoolAppendArgs), ctypes.c_void_p]
         lib.wm_pool_append.restype = ctypes.c_int
+        lib.wm_pool_mix.argtypes = [ctypes.POINTER(PoolMixArgs), ctypes.c_void_p]
+        lib.wm_pool_mix.restype = ctypes.c_int
+        lib.wm_pool_finish.argtypes = [ctypes.POINTER(PoolFinishArgs), ctypes.c_void_p]
+        lib.wm_pool_finish.restype = ctypes.c_int
         lib.wm_query_prepare_workspace_bytes.argtypes = [ctypes.POINTER(QueryPrepArgs)]
         lib.wm_query_prepare_workspace_bytes.restype = ctypes.c_size_t
         lib.wm_abi_version.argtypes = []

@@ -204,6 +204,16 @@ int wm_pool_append(const wm_pool_append_args* a, void* stream) {
   return wm::pool_append_launch(*a, static_cast<cudaStream_t>(stream));
 }
 
+int wm_pool_mix(const wm_pool_mix_args* a, void* stream) {
+  if (a == nullptr) return wm::fail(WM_EINVAL, "wm_pool_mix: null arguments");
+  return wm::pool_mix_launch(*a, static_cast<cudaStream_t>(stream));
+}
+
+int wm_pool_finish(const wm_pool_finish_args* a, void* stream) {
+  if (a == nullptr) return wm::fail(WM_EINVAL, "wm_pool_finish: null arguments");
+  return wm::pool_finish_launch(*a, static_cast<cudaStream_t>(stream));
+}
+
 int wm_mix_sources_fwd(const wm_mix_args* a, void* stream) {
   if (a == nullptr) return wm::fail(WM_EINVAL, "wm_mix_sources_fwd: null arguments");
   return wm::mix_fwd_launch(*a, static_cast<cudaStream_t>(stream));

@@ -35,6 +35,8 @@ bool decode_supported(const wm_attn_args& a);
 size_t decode_static_capacity();
 int decode_static_scratch(float** out);
 int pool_append_launch(const wm_pool_append_args& a, cudaStream_t stream);
+int pool_mix_launch(const wm_pool_mix_args& a, cudaStream_t stream);
+int pool_finish_launch(const wm_pool_finish_args& a, cudaStream_t stream);
 int mix_fwd_launch(const wm_mix_args& a, cudaStream_t stream);
 int mix_bwd_launch(const wm_mix_args& a, cudaStream_t stream);
 size_t mix_workspace(const wm_mix_args& a);
