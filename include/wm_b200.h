@@ -187,7 +187,8 @@ typedef struct wm_qprep_args {
  *   n[l]   = x[l] * rsqrt(mean(x[l]^2) + source_eps)
  *   a[c,l] = bias[c*sources + l] + sum_j partial[j, row, c*sources + l] * rsqrt(mean(x[s_j]^2) + source_eps)
  *   h[c]   = sum_l a[c,l] * pre_mix[l] * n[l]
- *   out[c, row] = h[c] * rsqrt(mean(h[c]^2) + mix_eps) * gain[c]
+ *   out[c, row] = h[c] * rsqrt(mean(h[c]^2) + mix_eps) * gain[c]          (gain = 1 when gain_k / gain_v are NULL:
+ *                                                                          a caller may fold it into the projection)
  *
  * with s_j = route_start + j * route_stride the sources the router reads.  `partial` carries the content-dependent
  * part of the logits, not yet scaled by the sources' norms: partial[j] = x[s_j] @ (router_weight[:, j] *
@@ -206,7 +207,7 @@ typedef struct wm_pool_mix_args {
   const float* bias_v;
   const void* partial_k; /* NULL for a static router */
   const void* partial_v;
-  const float* gain_k; /* (channels, hidden) */
+  const float* gain_k; /* (channels, hidden), or both NULL */
   const float* gain_v;
   void* mixed_k;
   void* mixed_v;

@@ -31,6 +31,26 @@ def _rms(x, eps):
     return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
 
 
+def mix_pool_oracle(stacked, params, *, route_stride=1, dynamic=True, source_eps=1e-6, mix_eps=1e-4, compute_dtype=torch.float64):
+    """The part before the projections: stacked (B,T,L,Dm) -> gained mixtures (2, k, B*T, Dm), K side first."""
+    p = {name: value.to(compute_dtype) for name, value in params.items()}
+    x = stacked.to(compute_dtype)
+    sources, hidden = x.shape[2:]
+    channels = p["gain_k"].shape[0]
+    selected = list(range((sources - 1) % route_stride, sources, route_stride))
+    sides = []
+    for side in ("k", "v"):
+        source = _rms(x, source_eps) * p[f"pre_mix_{side}"]
+        logits = p[f"router_{side}_bias"].expand(*x.shape[:2], -1)
+        if dynamic:
+            logits = source[:, :, selected].flatten(2) @ p[f"router_{side}_weight"].T + logits
+        logits = logits.unflatten(-1, (channels, sources))
+        mixed = torch.einsum("btld,btkl->kbtd", source, logits)
+        mixed = _rms(mixed, mix_eps) * p[f"gain_{side}"][:, None, None, :]
+        sides.append(mixed.reshape(channels, -1, hidden))
+    return torch.stack(sides)
+
+
 def project_pool_oracle(
     stacked,
     params,

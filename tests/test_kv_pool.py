@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from helpers import BF16_TOL, F32_TOL, assert_parity
-from oracle.pool_oracle import project_pool_oracle
+from oracle.pool_oracle import mix_pool_oracle, project_pool_oracle
 
 VECTORS = np.load(Path(__file__).resolve().parent / "golden" / "pool_vectors.npz")
 CASES = sorted({name.split("/", 1)[0] for name in VECTORS.files})
@@ -165,6 +165,41 @@ def test_model_sized_pool_matches_the_oracle(dynamic, stride):
     )
     assert_parity(keys.cpu().double(), want_k, what="keys", **BF16_TOL)
     assert_parity(values.cpu().double(), want_v, what="values", **BF16_TOL)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="requires CUDA")
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ["dynamic", "strided_dummy", "static"])
+def test_mix_entry_point_applies_the_post_mix_gain_when_given(case, dtype):
+    """wm_pool_mix called directly with gain tables (the host module folds them into the projections instead)."""
+    from white_matter_b200 import _native
+
+    pool = build_pool(case, dtype)
+    st = state(case)
+    x = get(case, "stacked").cuda().to(dtype)
+    batch, tokens, layers, hidden = x.shape
+    rows, k = batch * tokens, pool.num_kv_channels
+    mixed = torch.empty(2, k, rows, hidden, device="cuda", dtype=dtype)
+    a = _native.PoolMixArgs()
+    a.stacked, a.stacked_strides = x.data_ptr(), _native._Strides(x.stride(0), x.stride(1), x.stride(2))
+    a.pre_mix_k, a.pre_mix_v = pool.pre_mix_k_weight.data_ptr(), pool.pre_mix_v_weight.data_ptr()
+    a.bias_k, a.bias_v = pool.k_router_bias.data_ptr(), pool.v_router_bias.data_ptr()
+    keep = []
+    if pool.router_dynamic:
+        flat = x[:, :, pool.source_start :: pool.router_layer_stride].reshape(rows, pool.num_sources, hidden).transpose(0, 1)
+        keep = [torch.bmm(flat, pool._route_k), torch.bmm(flat, pool._route_v)]
+        a.partial_k, a.partial_v = keep[0].data_ptr(), keep[1].data_ptr()
+        a.route_start, a.route_stride, a.n_routed = pool.source_start, pool.router_layer_stride, pool.num_sources
+    a.gain_k, a.gain_v = pool.k_gain.data_ptr(), pool.v_gain.data_ptr()
+    a.mixed_k, a.mixed_v = mixed[0].data_ptr(), mixed[1].data_ptr()
+    a.dtype = _native.dtype_code(dtype)
+    a.batch, a.tokens, a.sources, a.channels, a.hidden = batch, tokens, layers, k, hidden
+    a.source_eps, a.mix_eps = pool.rms_norm_eps, pool.mix_norm_eps
+    _native.call("wm_pool_mix", a, x.device)
+    want = mix_pool_oracle(x.cpu(), oracle_params(st), route_stride=pool.router_layer_stride, dynamic=pool.router_dynamic)
+    tol = F32_TOL if dtype == torch.float32 else BF16_TOL
+    assert_parity(mixed.cpu().double(), want, what="gained mixtures", **tol)
 
 
 @pytest.mark.gpu

@@ -393,6 +393,14 @@ int tc_debug_expire_wait(long long limit_ticks, cudaStream_t stream) {
   return cuda_check(cudaGetLastError(), "expire_wait_kernel");
 }
 
+// Device address of the status word, for kernels of other files that report a wait that ran out.
+int tc_status_word(int** out) {
+  void* address = nullptr;
+  WM_CUDA(cudaGetSymbolAddress(&address, g_status));
+  *out = static_cast<int*>(address);
+  return WM_OK;
+}
+
 int tc_device_status(bool reset) {
   int value = 0;
   if (cudaMemcpyFromSymbol(&value, g_status, sizeof(int)) != cudaSuccess) return -1;

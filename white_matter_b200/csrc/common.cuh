@@ -46,6 +46,7 @@ bool tc_bwd_supported(const wm_attn_args& a);
 int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream);
 size_t tc_attn_bwd_workspace(const wm_attn_args& a);
 int tc_device_status(bool reset);
+int tc_status_word(int** out);
 int tc_debug_trace(long long* out, int capacity, int arm_after);
 int tc_debug_expire_wait(long long limit_ticks, cudaStream_t stream);
 int query_prepare(const wm_qprep_args& a, bool backward, cudaStream_t stream);

@@ -11,14 +11,16 @@ Host-side mirror of the upstream ``KVPool`` (src/white_matter/modules/kv_pool.py
   ``logits = bias + sum_j rsqrt(mean(x_j^2)+eps) * (x_j @ (W_j * pre_mix_j)^T)``.  The bracket is one plain batched
   GEMM over the routed sources on the layer stack as it lies in memory (library call); the norms and the sum are
   applied inside ``wm_pool_mix``.
-* The per-channel projections are plain batched GEMMs (library call).
+* The per-channel projections are plain batched GEMMs (library call); the post-mix gains are folded into their
+  weights.
 * ``wm_pool_finish`` applies the per-channel key norm and the rotary embedding and writes keys and values straight
   into their final layout -- a fresh (B,k,HKV,T,D) tensor or the slots of a decode cache -- which replaces the
   upstream permute/contiguous, norm, rotate_half chain and the index_copy publication
   (blocks/_execution/cyclic.py:406-424).
 
-Token rows are processed in chunks sized so that the chunk's intermediates (routing partials, mixtures, projections)
-stay in the 126 MB L2 between the four kernels; HBM then sees the layer stack once and the pool once.
+Token rows are processed in chunks of ``chunk_rows`` (default 16384) to bound the temporaries (routing partials,
+mixtures, projections: about 75 KB per row at 25 sources of width 1024).  Smaller, L2-sized chunks were measured
+slower on B200: the mixing kernel is bound by instruction issue, not by HBM, and more launches only add host time.
 
 Only the routed mixer is built (the upstream default); gradients are not: the path serves prefill and decode.
 """
@@ -65,7 +67,7 @@ class KVPool:
         router_dynamic: bool = True,
         device: torch.device | str = "cuda",
         dtype: torch.dtype = torch.bfloat16,
-        chunk_rows: int = 1024,
+        chunk_rows: int = 16384,
     ) -> None:
         if not 1 <= num_kv_channels <= num_layers:
             raise ValueError(f"num_kv_channels must be in [1, {num_layers}], got {num_kv_channels}")
@@ -128,8 +130,9 @@ class KVPool:
 
         self._route_k = folded(self.k_router_weight, self.pre_mix_k_weight)
         self._route_v = folded(self.v_router_weight, self.pre_mix_v_weight)
-        self._proj_k = self.k_proj_weight.transpose(1, 2).to(self.dtype).contiguous()
-        self._proj_v = self.v_proj_weight.transpose(1, 2).to(self.dtype).contiguous()
+        # the post-mix gain scales the columns of the projection's input: folded into the projection weights
+        self._proj_k = (self.k_proj_weight * self.k_gain[:, None, :]).transpose(1, 2).to(self.dtype).contiguous()
+        self._proj_v = (self.v_proj_weight * self.v_gain[:, None, :]).transpose(1, 2).to(self.dtype).contiguous()
 
     # ------------------------------------------------------------------ kernels
     def _check(self, stacked: torch.Tensor) -> None:
@@ -165,7 +168,6 @@ class KVPool:
         if partial_k is not None:
             a.partial_k, a.partial_v = partial_k.data_ptr(), partial_v.data_ptr()
             a.route_start, a.route_stride, a.n_routed = self.source_start, self.router_layer_stride, self.num_sources
-        a.gain_k, a.gain_v = self.k_gain.data_ptr(), self.v_gain.data_ptr()
         a.mixed_k, a.mixed_v = mixed[0].data_ptr(), mixed[1].data_ptr()
         a.dtype = _native.dtype_code(self.dtype)
         a.batch, a.tokens, a.sources, a.channels, a.hidden = batch, tokens, layers, k, hidden
