@@ -29,6 +29,7 @@ fraction, and the CPU oracle timed on a bounded sample.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -520,6 +521,74 @@ def bench_query_prepare(device, peaks, iters=20):
     }
 
 
+def bench_pool_projection(device, peaks, iters=5):
+    """KV-pool projection of the 24-layer model's prefill: layer stack (8, 2048, 25, 1024) bf16 -> keys, values
+    (8, 8, 16, 2048, 64), dynamic router over every second source (the upstream default) and static router.  The
+    whole path (routing GEMM, mixing kernel, projection GEMMs, key norm + rotary + publication) is timed; the mixing
+    and publication kernels are also timed alone, against their algorithmic bytes."""
+    from white_matter_b200 import KVPool, _native
+
+    batch, tokens, layers, hidden, channels, heads, dim = 8, 2048, 25, 1024, 8, 16, 64
+    stacked = torch.empty(batch, tokens, layers, hidden, device=device, dtype=torch.bfloat16)
+    for b in range(batch):
+        stacked[b].normal_()
+    angle = torch.rand(1, tokens, dim // 2, device=device) * 6.283
+    tables = (torch.cat((angle.cos(), angle.cos()), -1), torch.cat((angle.sin(), angle.sin()), -1))
+    rows = batch * tokens
+    stack_bytes, pool_bytes = stacked.numel() * 2, 2 * rows * channels * heads * dim * 2
+    mixed_bytes = 2 * channels * rows * hidden * 2
+    out = {"workload": "KV-pool projection (8,2048,25,1024) bf16 -> K,V (8,8,16,2048,64); 839 MB stack read, 268 MB pool written"}
+    for name, dynamic in (("dynamic_router", True), ("static_router", False)):
+        pool = KVPool(hidden, heads, dim, layers, channels, router_layer_stride=2, router_dynamic=dynamic, device=device)
+        pool.k_router_weight.normal_(0, 0.004)
+        pool.v_router_weight.normal_(0, 0.004)
+        pool.k_router_bias.normal_()
+        pool.v_router_bias.normal_()
+        pool.refresh()
+        call = lambda: pool.project_sequence(stacked, tables)
+        ms = time_steps(call, iters, 3, torch.cuda.synchronize) / iters
+        gbs = (stack_bytes + pool_bytes) / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "bytes": stack_bytes + pool_bytes, "value": gbs, "unit": "GB/s",
+                     "hbm_frac": gbs / peaks["hbm_gbs"], "note": "whole path; floor = stack read + pool write"}
+    # the two kernels of this library alone (static router: no partials), through the C ABI
+    mixed = torch.empty(2, channels, rows, hidden, device=device, dtype=torch.bfloat16)
+    a = _native.PoolMixArgs()
+    a.stacked, a.stacked_strides = stacked.data_ptr(), _native._Strides(stacked.stride(0), stacked.stride(1), stacked.stride(2))
+    a.pre_mix_k, a.pre_mix_v = pool.pre_mix_k_weight.data_ptr(), pool.pre_mix_v_weight.data_ptr()
+    a.bias_k, a.bias_v = pool.k_router_bias.data_ptr(), pool.v_router_bias.data_ptr()
+    a.mixed_k, a.mixed_v = mixed[0].data_ptr(), mixed[1].data_ptr()
+    a.dtype = _native.WM_BF16
+    a.batch, a.tokens, a.sources, a.channels, a.hidden = batch, tokens, layers, channels, hidden
+    a.source_eps, a.mix_eps = pool.rms_norm_eps, pool.mix_norm_eps
+    mix_call = lambda: _native.call("wm_pool_mix", a, device)
+    mix_ms = time_steps(mix_call, iters, 3, torch.cuda.synchronize) / iters
+    mix_gbs = (stack_bytes + mixed_bytes) / (mix_ms * 1e-3) / 1e9
+    out["mix_kernel"] = {"ms": mix_ms, "bytes": stack_bytes + mixed_bytes, "value": mix_gbs, "unit": "GB/s",
+                         "roofline": {"bound": "hbm", "achieved": mix_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                      "frac": mix_gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get("pool_mix_mma_kernel")}}
+    del mixed
+    proj = torch.randn(2, channels, rows, heads * dim, device=device, dtype=torch.bfloat16)
+    keys = torch.empty(batch, channels * heads, tokens, dim, device=device, dtype=torch.bfloat16)
+    values = torch.empty_like(keys)
+    f = _native.PoolFinishArgs()
+    f.k_proj, f.v_proj = proj[0].data_ptr(), proj[1].data_ptr()
+    f.k_norm_weight = pool.k_norm_weight.data_ptr()
+    f.cos, f.sin = tables[0].data_ptr(), tables[1].data_ptr()
+    f.k_out, f.v_out = keys.data_ptr(), values.data_ptr()
+    f.cs_strides = (ctypes.c_int64 * 2)(0, tables[0].stride(1))
+    f.out_strides = _native._Strides(keys.stride(0), keys.stride(1), keys.stride(2))
+    f.in_dtype = f.out_dtype = _native.WM_BF16
+    f.batch, f.tokens, f.channels, f.kv_heads, f.head_dim = batch, tokens, channels, heads, dim
+    f.eps = pool.rms_norm_eps
+    finish_call = lambda: _native.call("wm_pool_finish", f, device)
+    finish_ms = time_steps(finish_call, iters, 3, torch.cuda.synchronize) / iters
+    finish_gbs = 2 * pool_bytes / (finish_ms * 1e-3) / 1e9
+    out["finish_kernel"] = {"ms": finish_ms, "bytes": 2 * pool_bytes, "value": finish_gbs, "unit": "GB/s",
+                            "roofline": {"bound": "hbm", "achieved": finish_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                         "frac": finish_gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get("pool_finish_kernel")}}
+    return out
+
+
 def bench_incumbents(device, iters=10):
     """The library kernels the upstream GPU backends call (src/white_matter/ops/flash_attention.py:15-36,52-103), timed
     on the same GPU as comparators: FlashAttention-2 (flash_attn package) and PyTorch's flash SDPA.  Labelled extras:
@@ -822,6 +891,8 @@ def main():
         extras["jacobi"] = bench_jacobi(device, peaks)
         extras["mixing"] = bench_mixing(device, peaks)
         extras["query_prepare"] = bench_query_prepare(device, peaks)
+        torch.cuda.empty_cache()
+        extras["pool_projection"] = bench_pool_projection(device, peaks)
         check("extras")
         if world == 1:
             torch.cuda.empty_cache()

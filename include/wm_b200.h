@@ -153,6 +153,16 @@ typedef struct wm_mix_args {
   int32_t dtype;
 } wm_mix_args;
 
+/* K and V of a decode read given as stacks of sources that are mixed while they are read: source s of K lies
+ * k_source_stride elements after args->k and enters with weight softmax(k_logits)[s]; likewise V. */
+typedef struct wm_source_mix {
+  const float* k_logits; /* (n_sources,) fp32, device */
+  const float* v_logits;
+  int64_t k_source_stride;
+  int64_t v_source_stride;
+  int32_t n_sources; /* 1..64 */
+} wm_source_mix;
+
 /* Query preparation of the attention layer (layers/white_matter.py:105-111 of the reference: q_norm, transpose,
  * rotary embedding): q[b,h,t,:] = rope(rms_norm(x[b,t,h,:]) * weight).  x has element strides x_strides for
  * (batch, token, head) and unit stride in head_dim; q is contiguous (batch, heads, tokens, head_dim); cos / sin are
@@ -312,6 +322,15 @@ WM_API int wm_strict_decode(const wm_attn_args* args, void* stream);
  * - Calls no cudaMalloc / cudaFree and no allocating library routine.
  */
 WM_API int wm_strict_decode_no_alloc(const wm_attn_args* args, void* stream);
+
+/*
+ * wm_strict_decode over K/V that are soft-max mixtures of stacked sources (the learned KV source mixing of
+ * blocks/feedback_transformer.py:35-36 of the reference, applied to projected sources), with the mixture formed in
+ * the K/V load path: every visible row of every source is read once and nothing is materialised.  A single-query
+ * read touches each K/V row once, so this is the place where mixing on the fly saves traffic (the write and
+ * re-read of the mixture); the same arguments, workspace and result as wm_strict_decode.
+ */
+WM_API int wm_strict_decode_mixed(const wm_attn_args* args, const wm_source_mix* mix, void* stream);
 
 /* commit of new K or V rows to a static pool at device-resident lengths */
 WM_API int wm_pool_append(const wm_pool_append_args* args, void* stream);

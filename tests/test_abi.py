@@ -51,6 +51,7 @@ STRUCTS = {
     "wm_pool_append_args": _native.PoolAppendArgs,
     "wm_pool_mix_args": _native.PoolMixArgs,
     "wm_pool_finish_args": _native.PoolFinishArgs,
+    "wm_source_mix": _native.SourceMix,
 }
 C_TYPES = {"int64_t": ctypes.c_int64, "int32_t": ctypes.c_int32, "size_t": ctypes.c_size_t, "float": ctypes.c_float}
 

@@ -60,3 +60,44 @@ def test_mixed_sources_feed_attention_with_gradients_to_logits():
     assert_parity(out, exp, what="out", max_abs_tol=1e-4, rel_l2_tol=1e-4)
     for g, e, name in zip(grads, exp_grads, ("dq", "dksrc", "dvsrc", "dlogits_k", "dlogits_v")):
         assert_parity(g, e, what=name, max_abs_tol=2e-4, rel_l2_tol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sources,heads,kv_heads,dummy,masked", [(25, 4, 4, False, False), (3, 4, 2, True, False), (2, 8, 2, False, True), (1, 3, 1, True, True)])
+def test_decode_with_the_mixture_formed_in_the_load_path(sources, heads, kv_heads, dummy, masked, dtype):
+    """mixed_pool_decode against the oracle's mixture followed by the oracle's strict attention; slots beyond the
+    committed lengths hold NaN in every source and must not be read."""
+    from white_matter_b200 import mixed_pool_decode, strict_causal_attention
+
+    torch.manual_seed(21)
+    batch, slots, dim = 3, 300, 64
+    lead = int(dummy)
+    lengths = torch.tensor([299 - lead, 17, 0])
+    ksrc = torch.randn(sources, batch, kv_heads, slots, dim).to(dtype)
+    vsrc = torch.randn(sources, batch, kv_heads, slots, dim).to(dtype)
+    for b in range(batch):
+        ksrc[:, b, :, lead + int(lengths[b]):] = float("nan")
+        vsrc[:, b, :, lead + int(lengths[b]):] = float("nan")
+    lk, lv = torch.randn(sources), torch.randn(sources)
+    q = torch.randn(batch, heads, 1, dim).to(dtype)
+    mask = None
+    if masked:
+        mask = torch.rand(batch, slots) < 0.7
+        mask[:, 0] = True
+    got = mixed_pool_decode(
+        q.cuda(), ksrc.cuda(), vsrc.cuda(), lk.cuda(), lv.cuda(), query_start=lengths.cuda(), kv_lengths=lengths.cuda(),
+        use_dummy_token=dummy, key_mask=None if mask is None else mask.cuda(),
+    )
+    clean_k, clean_v = torch.nan_to_num(ksrc.double()), torch.nan_to_num(vsrc.double())
+    want = oracle.strict_causal_oracle(
+        q.double(), oracle.mix_sources_oracle(clean_k, lk.double()), oracle.mix_sources_oracle(clean_v, lv.double()),
+        query_start=lengths, kv_lengths=lengths, use_dummy_token=dummy, key_mask=mask,
+    )
+    tol = dict(max_abs_tol=1e-4, rel_l2_tol=1e-4) if dtype == torch.float32 else dict(max_abs_tol=2e-2, rel_l2_tol=1e-2)
+    assert_parity(got.float(), want, what="mixed decode", **tol)
+    # and against the two-step form of this library
+    two_step = strict_causal_attention(
+        q.cuda(), mix_kv_sources(torch.nan_to_num(ksrc).cuda(), lk.cuda()), mix_kv_sources(torch.nan_to_num(vsrc).cuda(), lv.cuda()),
+        query_start=lengths.cuda(), kv_lengths=lengths.cuda(), use_dummy_token=dummy, key_mask=None if mask is None else mask.cuda(),
+    )
+    assert_parity(got.float(), two_step.float(), what="fused vs materialised", **tol)

@@ -15,7 +15,7 @@ from .metadata import (
 )
 from .kv_pool import KVPool
 from .layer import cyclic_attention_layer, prepare_queries
-from .mixing import mix_kv_sources
+from .mixing import mix_kv_sources, mixed_pool_decode
 from .strict import strict_causal_attention
 
 __all__ = [
@@ -29,6 +29,7 @@ __all__ = [
     "prepare_cyclic_attention_metadata",
     "prepare_feedback_metadata",
     "mix_kv_sources",
+    "mixed_pool_decode",
     "KVPool",
     "KVPoolCache",
     "DecodeStepGraph",

@@ -97,6 +97,18 @@ class MixArgs(ctypes.Structure):
     ]
 
 
+class SourceMix(ctypes.Structure):
+    """Mirror of ``wm_source_mix``."""
+
+    _fields_ = [
+        ("k_logits", ctypes.c_void_p),
+        ("v_logits", ctypes.c_void_p),
+        ("k_source_stride", ctypes.c_int64),
+        ("v_source_stride", ctypes.c_int64),
+        ("n_sources", ctypes.c_int32),
+    ]
+
+
 class QueryPrepArgs(ctypes.Structure):
     """Mirror of ``wm_qprep_args``."""
 
@@ -257,6 +269,8 @@ def load_library() -> ctypes.CDLL:
             fn.restype = ctypes.c_int
         lib.wm_pool_append.argtypes = [ctypes.POINTER(PoolAppendArgs), ctypes.c_void_p]
         lib.wm_pool_append.restype = ctypes.c_int
+        lib.wm_strict_decode_mixed.argtypes = [ctypes.POINTER(AttnArgs), ctypes.POINTER(SourceMix), ctypes.c_void_p]
+        lib.wm_strict_decode_mixed.restype = ctypes.c_int
         lib.wm_pool_mix.argtypes = [ctypes.POINTER(PoolMixArgs), ctypes.c_void_p]
         lib.wm_pool_mix.restype = ctypes.c_int
         lib.wm_pool_finish.argtypes = [ctypes.POINTER(PoolFinishArgs), ctypes.c_void_p]

@@ -199,6 +199,14 @@ int wm_strict_decode_no_alloc(const wm_attn_args* a, void* stream) {
   return wm::decode_launch_with_scratch(*a, scratch, static_cast<cudaStream_t>(stream));
 }
 
+int wm_strict_decode_mixed(const wm_attn_args* a, const wm_source_mix* mix, void* stream) {
+  if (mix == nullptr) return wm::fail(WM_EINVAL, "wm_strict_decode_mixed: null mixture");
+  int status = wm::validate_attn(a, false, "wm_strict_decode_mixed");
+  if (status != WM_OK) return status;
+  if (!wm::decode_supported(*a)) return wm::fail(WM_EUNSUPPORTED, "wm_strict_decode_mixed: needs one query, the strict mask and 16-byte aligned rows");
+  return wm::decode_mixed_launch(*a, *mix, static_cast<cudaStream_t>(stream));
+}
+
 int wm_pool_append(const wm_pool_append_args* a, void* stream) {
   if (a == nullptr) return wm::fail(WM_EINVAL, "wm_pool_append: null arguments");
   return wm::pool_append_launch(*a, static_cast<cudaStream_t>(stream));

@@ -34,6 +34,7 @@ int decode_launch_with_scratch(const wm_attn_args& a, float* scratch, cudaStream
 bool decode_supported(const wm_attn_args& a);
 size_t decode_static_capacity();
 int decode_static_scratch(float** out);
+int decode_mixed_launch(const wm_attn_args& a, const wm_source_mix& m, cudaStream_t stream);
 int pool_append_launch(const wm_pool_append_args& a, cudaStream_t stream);
 int pool_mix_launch(const wm_pool_mix_args& a, cudaStream_t stream);
 int pool_finish_launch(const wm_pool_finish_args& a, cudaStream_t stream);

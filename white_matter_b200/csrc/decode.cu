@@ -66,9 +66,19 @@ __device__ __forceinline__ long long partial_at(const wm_attn_args& a, int b, in
   return ((static_cast<long long>(b) * a.q_heads + h) * splits + split) * (a.head_dim + 2);
 }
 
-template <typename T, int LPK, int G>
+// K and V as stacks of sources that are mixed while they are read (kMixed): source s lies `stride` elements after
+// source 0 and enters with weight softmax(logits)[s].
+struct SourceMix {
+  const float* k_logits;
+  const float* v_logits;
+  long long k_stride, v_stride;
+  int sources;
+};
+constexpr int kMaxMixSources = 64;
+
+template <typename T, int LPK, int G, bool kMixed>
 __global__ void __launch_bounds__(kThreads) decode_split_kernel(const wm_attn_args a, float* partial, int chunk,
-                                                                int splits) {
+                                                                int splits, const SourceMix mix) {
   constexpr int VEC = VecOf<T>::N;
   constexpr int KPW = 32 / LPK;  // keys per warp per step
   __shared__ float sm_m[kWarps][G];
@@ -93,6 +103,21 @@ __global__ void __launch_bounds__(kThreads) decode_split_kernel(const wm_attn_ar
   const int c = lane % LPK;
   const int kk = lane / LPK;
   const bool dlive = c * VEC < a.head_dim;
+
+  __shared__ float mix_w[kMixed ? 2 * kMaxMixSources : 1];
+  if (kMixed) {
+    if (warp < 2) {  // warp 0: soft-max of the key logits, warp 1: of the value logits
+      const float* logits = warp == 0 ? mix.k_logits : mix.v_logits;
+      float top = -INFINITY;
+      for (int s = lane; s < mix.sources; s += 32) top = fmaxf(top, logits[s]);
+      for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+      float sum = 0.f;
+      for (int s = lane; s < mix.sources; s += 32) sum += expf(logits[s] - top);
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      for (int s = lane; s < mix.sources; s += 32) mix_w[warp * kMaxMixSources + s] = expf(logits[s] - top) / sum;
+    }
+    __syncthreads();
+  }
 
   float q[G][VEC];
   const float sl2 = a.scale * kLog2e;
@@ -123,22 +148,66 @@ __global__ void __launch_bounds__(kThreads) decode_split_kernel(const wm_attn_ar
   const unsigned char* mask = a.key_mask ? a.key_mask + static_cast<long long>(b) * a.k_len : nullptr;
 
   for (int j0 = j_begin + warp * KPW * kUnroll; j0 < j_end; j0 += kWarps * KPW * kUnroll) {
-    uint4 kraw[kUnroll], vraw[kUnroll];
+    uint4 vraw[kUnroll];
     bool vis[kUnroll];
+    float kf[kUnroll][VEC];
+    float vmix[kMixed ? kUnroll : 1][VEC];  // the mixed value rows (kMixed only)
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       int j = j0 + u * KPW + kk;
       vis[u] = j < j_end && (mask == nullptr || mask[j] != 0);
-      kraw[u] = make_uint4(0, 0, 0, 0);
-      vraw[u] = make_uint4(0, 0, 0, 0);
-      if (vis[u] && dlive) {
-        kraw[u] = ld_stream(kbase + static_cast<long long>(j) * a.k_strides[2]);
-        vraw[u] = ld_stream(vbase + static_cast<long long>(j) * a.v_strides[2]);
+    }
+    if (!kMixed) {
+      uint4 kraw[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        int j = j0 + u * KPW + kk;
+        kraw[u] = make_uint4(0, 0, 0, 0);
+        vraw[u] = make_uint4(0, 0, 0, 0);
+        if (vis[u] && dlive) {
+          kraw[u] = ld_stream(kbase + static_cast<long long>(j) * a.k_strides[2]);
+          vraw[u] = ld_stream(vbase + static_cast<long long>(j) * a.v_strides[2]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) unpack<T>(kraw[u], kf[u]);
+    } else {
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) kf[u][e] = vmix[kMixed ? u : 0][e] = 0.f;
+      // every source row is read once; the loads of two sources are in flight together
+      for (int s0 = 0; s0 < mix.sources; s0 += 2) {
+        uint4 kraw[2][kUnroll], vsrc[2][kUnroll];
+#pragma unroll
+        for (int d = 0; d < 2; ++d)
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            int j = j0 + u * KPW + kk;
+            kraw[d][u] = make_uint4(0, 0, 0, 0);
+            vsrc[d][u] = make_uint4(0, 0, 0, 0);
+            if (vis[u] && dlive && s0 + d < mix.sources) {
+              kraw[d][u] = ld_stream(kbase + (s0 + d) * mix.k_stride + static_cast<long long>(j) * a.k_strides[2]);
+              vsrc[d][u] = ld_stream(vbase + (s0 + d) * mix.v_stride + static_cast<long long>(j) * a.v_strides[2]);
+            }
+          }
+#pragma unroll
+        for (int d = 0; d < 2; ++d) {
+          const bool live = s0 + d < mix.sources;
+          const float wk = live ? mix_w[s0 + d] : 0.f, wv = live ? mix_w[kMaxMixSources + s0 + d] : 0.f;
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            float x[VEC];
+            unpack<T>(kraw[d][u], x);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) kf[u][e] = fmaf(wk, x[e], kf[u][e]);
+            unpack<T>(vsrc[d][u], x);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) vmix[kMixed ? u : 0][e] = fmaf(wv, x[e], vmix[kMixed ? u : 0][e]);
+          }
+        }
       }
     }
-    float kf[kUnroll][VEC];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) unpack<T>(kraw[u], kf[u]);
 #pragma unroll
     for (int h = 0; h < G; ++h) {
       float s[kUnroll];
@@ -164,7 +233,12 @@ __global__ void __launch_bounds__(kThreads) decode_split_kernel(const wm_attn_ar
           if (vis[u]) {
             float p = exp2f(s[u] - m_new);
             float vf[VEC];
-            unpack<T>(vraw[u], vf);
+            if (kMixed) {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) vf[e] = vmix[kMixed ? u : 0][e];
+            } else {
+              unpack<T>(vraw[u], vf);
+            }
             l[h] += p;
 #pragma unroll
             for (int e = 0; e < VEC; ++e) acc[h][e] = fmaf(p, vf[e], acc[h][e]);
@@ -270,26 +344,21 @@ int lanes_per_key(const wm_attn_args& a) {
   return lpk;
 }
 
-template <typename T, int LPK>
-int launch(const wm_attn_args& a, float* partial, cudaStream_t stream) {
+template <typename T, int LPK, bool kMixed>
+int launch(const wm_attn_args& a, float* partial, const SourceMix& mix, cudaStream_t stream) {
   const int chunk = pick_chunk(a);
   const int splits = (a.k_len + chunk - 1) / chunk;
   const int hpk = a.q_heads / a.kv_heads;
   if (hpk == 2) {
     dim3 grid(splits, a.kv_heads, a.batch);
-    decode_split_kernel<T, LPK, 2><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits); count_launch();
+    decode_split_kernel<T, LPK, 2, kMixed><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits, mix); count_launch();
   } else if (hpk == 4) {
     dim3 grid(splits, a.kv_heads, a.batch);
-    decode_split_kernel<T, LPK, 4><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits); count_launch();
+    decode_split_kernel<T, LPK, 4, kMixed><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits, mix); count_launch();
   } else {
+    // one block per query head; with other group sizes K/V are re-read through L2
     dim3 grid(splits, a.q_heads, a.batch);
-    if (hpk == 1) {
-      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits); count_launch();
-    } else {
-      // other group sizes: one block per query head, K/V re-read through L2
-      wm_attn_args single = a;
-      decode_split_kernel<T, LPK, 1><<<grid, kThreads, 0, stream>>>(single, partial, chunk, splits); count_launch();
-    }
+    decode_split_kernel<T, LPK, 1, kMixed><<<grid, kThreads, 0, stream>>>(a, partial, chunk, splits, mix); count_launch();
   }
   WM_CUDA(cudaGetLastError());
   int threads = a.head_dim <= 64 ? 64 : 128;
@@ -297,19 +366,19 @@ int launch(const wm_attn_args& a, float* partial, cudaStream_t stream) {
   return cuda_check(cudaGetLastError(), "decode_merge_kernel");
 }
 
-template <typename T>
-int dispatch(const wm_attn_args& a, float* partial, cudaStream_t stream) {
+template <typename T, bool kMixed>
+int dispatch(const wm_attn_args& a, float* partial, const SourceMix& mix, cudaStream_t stream) {
   switch (lanes_per_key(a)) {
     case 1:
     case 2:
     case 4:
-      return launch<T, 4>(a, partial, stream);
+      return launch<T, 4, kMixed>(a, partial, mix, stream);
     case 8:
-      return launch<T, 8>(a, partial, stream);
+      return launch<T, 8, kMixed>(a, partial, mix, stream);
     case 16:
-      return launch<T, 16>(a, partial, stream);
+      return launch<T, 16, kMixed>(a, partial, mix, stream);
     default:
-      return launch<T, 32>(a, partial, stream);
+      return launch<T, 32, kMixed>(a, partial, mix, stream);
   }
 }
 
@@ -332,7 +401,22 @@ size_t decode_workspace(const wm_attn_args& a) {
 }
 
 int decode_launch_with_scratch(const wm_attn_args& a, float* scratch, cudaStream_t stream) {
-  return a.dtype == WM_F32 ? dispatch<float>(a, scratch, stream) : dispatch<__nv_bfloat16>(a, scratch, stream);
+  const SourceMix none = {nullptr, nullptr, 0, 0, 0};
+  return a.dtype == WM_F32 ? dispatch<float, false>(a, scratch, none, stream) : dispatch<__nv_bfloat16, false>(a, scratch, none, stream);
+}
+
+int decode_mixed_launch(const wm_attn_args& a, const wm_source_mix& m, cudaStream_t stream) {
+  if (m.k_logits == nullptr || m.v_logits == nullptr) return fail(WM_EINVAL, "wm_strict_decode_mixed: both logit vectors are required");
+  if (m.n_sources < 1 || m.n_sources > kMaxMixSources) return fail(WM_EINVAL, "wm_strict_decode_mixed: between 1 and %d sources", kMaxMixSources);
+  const size_t es = a.dtype == WM_F32 ? 4 : 2;
+  if ((m.k_source_stride * es) % 16 || (m.v_source_stride * es) % 16)
+    return fail(WM_EUNSUPPORTED, "wm_strict_decode_mixed: sources must be 16-byte aligned");
+  size_t need = decode_workspace(a);
+  if (a.workspace == nullptr || a.workspace_bytes < need)
+    return fail(WM_EWORKSPACE, "decode needs %zu workspace bytes, got %zu", need, a.workspace_bytes);
+  const SourceMix mix = {m.k_logits, m.v_logits, m.k_source_stride, m.v_source_stride, m.n_sources};
+  float* scratch = static_cast<float*>(a.workspace);
+  return a.dtype == WM_F32 ? dispatch<float, true>(a, scratch, mix, stream) : dispatch<__nv_bfloat16, true>(a, scratch, mix, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -599,30 +599,38 @@ __global__ void __launch_bounds__(kFinishThreads) pool_finish_kernel(const wm_po
       other[i] = a.k_norm_weight[c * D + 8 * partner + i] * a.sin[cs + i] * sign;
     }
   }
-  for (int h0 = 0; h0 < a.kv_heads; h0 += kHeads) {
-    const int h = h0 + slot;
-    const bool live = h < a.kv_heads;
-    float x[8];
-    if (live) {
-      load8<TI>(in + h * D, x);
-    } else {
+  constexpr int kBatch = 4;  // warp passes whose loads are issued together
+  for (int h0 = 0; h0 < a.kv_heads; h0 += kBatch * kHeads) {
+    float x[kBatch][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = 0.f;
-    }
-    if (keys) {
-      float ss = 0.f;
+    for (int i = 0; i < kBatch; ++i) {
+      const int h = h0 + i * kHeads + slot;
+      if (h < a.kv_heads) {
+        load8<TI>(in + h * D, x[i]);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
-#pragma unroll
-      for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float r = rsqrtf(ss * (1.f / D) + a.eps);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float xp = __shfl_xor_sync(0xffffffffu, x[i], kLanes / 2);
-        x[i] = r * fmaf(x[i], own[i], xp * other[i]);
+        for (int e = 0; e < 8; ++e) x[i][e] = 0.f;
       }
     }
-    if (live) store8<TO>(out + static_cast<long long>(c * a.kv_heads + h) * a.out_strides[1], x);
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int h = h0 + i * kHeads + slot;
+      if (h0 + i * kHeads >= a.kv_heads) break;  // warp-uniform: the shuffles below need every lane
+      if (keys) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(x[i][e], x[i][e], ss);
+#pragma unroll
+        for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float r = rsqrtf(ss * (1.f / D) + a.eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xp = __shfl_xor_sync(0xffffffffu, x[i][e], kLanes / 2);
+          x[i][e] = r * fmaf(x[i][e], own[e], xp * other[e]);
+        }
+      }
+      if (h < a.kv_heads) store8<TO>(out + static_cast<long long>(c * a.kv_heads + h) * a.out_strides[1], x[i]);
+    }
   }
 }
 

@@ -705,6 +705,39 @@ def _qprep_backward(ctx, dq):
 query_prepare.register_autograd(_qprep_backward, setup_context=_qprep_setup)
 
 
+def strict_decode_mixed(
+    Q: Tensor,
+    K_sources: Tensor,
+    V_sources: Tensor,
+    k_logits: Tensor,
+    v_logits: Tensor,
+    query_start: Optional[Tensor],
+    query_start_value: int,
+    kv_lengths: Optional[Tensor],
+    key_mask: Optional[Tensor],
+    use_dummy: bool,
+    scale: float,
+) -> Tensor:
+    """Single-query read of K/V given as (S,B,HKV,N,D) stacks, mixed in the load path: (B,1,H,D)."""
+    a, keep = _strict_args(Q, K_sources[0], V_sources[0], query_start, query_start_value, kv_lengths, key_mask, use_dummy, scale, 0)
+    out, _ = _new_output(Q)
+    _set_out(a, out, None)
+    mix = _native.SourceMix()
+    kl, vl = k_logits.float().contiguous(), v_logits.float().contiguous()
+    mix.k_logits, mix.v_logits = kl.data_ptr(), vl.data_ptr()
+    mix.k_source_stride, mix.v_source_stride = K_sources.stride(0), V_sources.stride(0)
+    mix.n_sources = K_sources.shape[0]
+    nbytes = _native.load_library().wm_strict_decode_workspace_bytes(ctypes.byref(a))
+    ws = _attach_workspace(a, nbytes, Q.device)
+    lib = _native.load_library()
+    with torch.cuda.device(Q.device):
+        status = lib.wm_strict_decode_mixed(ctypes.byref(a), ctypes.byref(mix), _native.current_stream(Q.device))
+    if status != 0:
+        raise RuntimeError(f"wm_strict_decode_mixed failed ({status}): {lib.wm_last_error().decode(errors='replace')}")
+    del ws, keep, kl, vl
+    return out.transpose(1, 2)
+
+
 def strict_decode_no_alloc(
     Q: Tensor,
     K: Tensor,
