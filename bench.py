@@ -537,7 +537,7 @@ def bench_pool_projection(device, peaks, iters=5):
     rows = batch * tokens
     stack_bytes, pool_bytes = stacked.numel() * 2, 2 * rows * channels * heads * dim * 2
     mixed_bytes = 2 * channels * rows * hidden * 2
-    out = {"workload": "KV-pool projection (8,2048,25,1024) bf16 -> K,V (8,8,16,2048,64); 839 MB stack read, 268 MB pool written"}
+    out = {"workload": "KV-pool projection (8,2048,25,1024) bf16 -> K,V (8,8,16,2048,64); 839 MB stack read, 537 MB pool (K and V) written"}
     for name, dynamic in (("dynamic_router", True), ("static_router", False)):
         pool = KVPool(hidden, heads, dim, layers, channels, router_layer_stride=2, router_dynamic=dynamic, device=device)
         pool.k_router_weight.normal_(0, 0.004)
@@ -587,6 +587,47 @@ def bench_pool_projection(device, peaks, iters=5):
                             "roofline": {"bound": "hbm", "achieved": finish_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                          "frac": finish_gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get("pool_finish_kernel")}}
     return out
+
+
+def bench_mixed_decode(device, peaks, iters=5, batch=16):
+    """Decode over K/V that are mixtures of 25 stacked sources, both forms: the mixture formed in the K/V load path of
+    the decode kernel (every visible source row read once, nothing written), and the mixture materialised by the
+    streaming kernel over the whole pool followed by the plain decode read.  B=16, H=HKV=16, 8192 slots, D=64 bf16,
+    lengths uniform in [1, 8192]: 25 x 2 x 268 MB of sources."""
+    from white_matter_b200 import mix_kv_sources, mixed_pool_decode, strict_causal_attention
+
+    sources, heads, slots, dim = 25, 16, 8192, 64
+    gen = torch.Generator().manual_seed(0)
+    lengths = torch.randint(1, slots + 1, (batch,), generator=gen).to(device)
+    ksrc = torch.empty(sources, batch, heads, slots, dim, device=device, dtype=torch.bfloat16)
+    vsrc = torch.empty_like(ksrc)
+    for i in range(sources):
+        ksrc[i].normal_()
+        vsrc[i].normal_()
+    lk, lv = torch.randn(sources, device=device), torch.randn(sources, device=device)
+    q = torch.randn(batch, heads, 1, dim, device=device, dtype=torch.bfloat16)
+    fused = lambda: mixed_pool_decode(q, ksrc, vsrc, lk, lv, query_start=lengths, kv_lengths=lengths)
+    fused_ms = time_steps(fused, iters, 3, torch.cuda.synchronize) / iters
+    visible = int(lengths.sum().item()) * heads * dim * 2 * 2 * sources
+    fused_gbs = visible / (fused_ms * 1e-3) / 1e9
+
+    def two_step():
+        return strict_causal_attention(q, mix_kv_sources(ksrc, lk), mix_kv_sources(vsrc, lv), query_start=lengths, kv_lengths=lengths)
+
+    two_ms = time_steps(two_step, iters, 3, torch.cuda.synchronize) / iters
+    whole = 2 * (ksrc.numel() * 2 + ksrc[0].numel() * 2) + int(lengths.sum().item()) * heads * dim * 2 * 2
+    err = (fused().float() - two_step().float()).abs().max().item()
+    return {
+        "workload": f"decode over 25-source K/V mixtures, B={batch} H=16 slots=8192 D=64 bf16, lengths U[1,8192]",
+        "fused_in_load_path": {"ms": fused_ms, "bytes": visible, "value": fused_gbs, "unit": "GB/s",
+                               "roofline": {"bound": "hbm", "achieved": fused_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                            "frac": fused_gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get("decode_split_kernel_mixed")}},
+        "materialised_then_decode": {"ms": two_ms, "bytes": whole, "value": whole / (two_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                     "note": "mixes the whole pool capacity (the streaming kernel does not know the lengths), writes both mixtures, then reads them"},
+        "max_abs_difference": err,
+        "note": "per decode step the fused form re-reads all sources; a server that keeps the mixture resident pays the "
+                "materialisation once per token and then reads 1/25 of these bytes per step",
+    }
 
 
 def bench_incumbents(device, iters=10):
@@ -752,6 +793,16 @@ def eager_step_us(work, steps=5):
     return (time.perf_counter() - t0) / (steps * 2 * STRIDE) * 1e6
 
 
+LEGS = {
+    "decode": lambda device, peaks, small: dict(zip(("decode", "prefill128"), bench_decode(device, peaks))),
+    "jacobi": lambda device, peaks, small: bench_jacobi(device, peaks),
+    "mixing": lambda device, peaks, small: bench_mixing(device, peaks),
+    "query_prepare": lambda device, peaks, small: bench_query_prepare(device, peaks),
+    "pool_projection": lambda device, peaks, small: bench_pool_projection(device, peaks),
+    "mixed_decode": lambda device, peaks, small: bench_mixed_decode(device, peaks, batch=4 if small else 16),
+}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -763,6 +814,9 @@ def main():
                         help="weak: every rank runs its own B=16 rows; strong: the B=16 rows are split over the ranks")
     parser.add_argument("--no-graph", action="store_true", help="issue the operator calls eagerly instead of replaying a CUDA graph")
     parser.add_argument("--skip-extras", action="store_true", help="only the headline workload (used for profiling)")
+    parser.add_argument("--leg", action="append", choices=sorted(LEGS), default=None,
+                        help="run only the named secondary leg(s) and print their results (used for profiling)")
+    parser.add_argument("--small", action="store_true", help="with --leg mixed_decode: 4 batch rows instead of 16")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -785,6 +839,13 @@ def main():
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
+
+    if args.leg:
+        peaks_only, _ = load_peaks()
+        results = {name: LEGS[name](device, peaks_only, args.small) for name in args.leg}
+        torch.cuda.synchronize()
+        print(json.dumps(results), flush=True)
+        return
 
     from white_matter_b200 import _native
     from white_matter_b200.replicas import aggregate_throughput, shard_batch_heads
@@ -893,6 +954,9 @@ def main():
         extras["query_prepare"] = bench_query_prepare(device, peaks)
         torch.cuda.empty_cache()
         extras["pool_projection"] = bench_pool_projection(device, peaks)
+        torch.cuda.empty_cache()
+        extras["mixed_decode"] = bench_mixed_decode(device, peaks)
+        torch.cuda.empty_cache()
         check("extras")
         if world == 1:
             torch.cuda.empty_cache()
