@@ -30,6 +30,7 @@ from __future__ import annotations
 
 import argparse
 import ctypes
+import datetime
 import json
 import os
 import statistics
@@ -50,11 +51,16 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels on exactly these
 # workloads, from the ncu captures summarised under profiles/ (one capture each; the bench cannot run ncu itself).
 NCU_TRAFFIC_BYTES = {
-    "attn_bwd_resident_kernel": 252.0e6,
-    "attn_fwd_tc_kernel": 177.8e6,
-    "decode_split_kernel": 1086.4e6,
-    "mix_fwd_kernel": 432.8e6,
-    "query_prepare_fwd_bf16_kernel": 226.7e6,
+    "attn_bwd_resident_kernel": 255.0e6,
+    "attn_fwd_tc_kernel": 178.2e6,
+    "decode_split_kernel": 1083.7e6,
+    # captured on 4 of the 16 batch rows (1 053.8 MB for 1 050.6 MB of visible source rows) and scaled by the visible
+    # rows of the full launch, which is how this kernel's traffic grows
+    "decode_split_kernel_mixed": 8205.5e6 * 1053.8 / 1050.6,
+    "mix_fwd_kernel": 1730.0e6,
+    "query_prepare_fwd_bf16_kernel": 225.1e6,
+    "pool_mix_mma_kernel": 1335.9e6,
+    "pool_finish_kernel": 1014.4e6,
 }
 
 
@@ -97,10 +103,12 @@ def visible_pairs_per_head(docs, residue, stride):
 
 
 class ClockSampler:
-    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    """nvidia-smi queried every 25 ms in a child process.  Samples carry nvidia-smi's own timestamp; ``stop`` keeps
+    those between ``mark_load`` (the same work starts running, untimed) and the end of the timed region, and says
+    how many of them fell inside the timed region itself (a default run times 20 steps, about 40 ms)."""
 
     QUERY = (
-        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+        "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
         "clocks_event_reasons.sw_power_cap"
     )
@@ -108,6 +116,7 @@ class ClockSampler:
     def __init__(self, index):
         self.index = index
         self.proc = None
+        self.load_from = self.timed_from = self.timed_to = None
 
     def start(self):
         try:
@@ -118,6 +127,15 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def mark_load(self):
+        self.load_from = datetime.datetime.now()
+
+    def mark_timed(self, begin):
+        if begin:
+            self.timed_from = datetime.datetime.now()
+        else:
+            self.timed_to = datetime.datetime.now()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -127,17 +145,22 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             text, _ = self.proc.communicate()
-        clocks, top, reasons = [], None, set()
+        clocks, top, reasons, timed = [], None, set(), 0
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in text.strip().splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
-                clocks.append(float(parts[1]))
-                top = float(parts[2])
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                clock, top_now = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
+            if self.load_from is not None and not (self.load_from <= stamp <= (self.timed_to or stamp)):
+                continue
+            clocks.append(clock)
+            top = top_now
+            timed += int(self.timed_from is not None and self.timed_from <= stamp <= (self.timed_to or stamp))
             for name, flag in zip(names, parts[5:9]):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
@@ -146,6 +169,8 @@ class ClockSampler:
             "sm_max_mhz": top,
             "reasons": sorted(reasons),
             "samples": len(clocks),
+            "samples_in_timed_region": timed,
+            "window": "the same steps run untimed for 0.4 s before the warm-up; samples from there to the end of the timed region",
         }
 
 
@@ -896,12 +921,20 @@ def main():
         turn[0] += 1
 
     sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)  # nvidia-smi takes a moment to deliver its first sample
+    sampler.mark_load()
+    settle = time.perf_counter()
+    while time.perf_counter() - settle < 0.4:  # the timed region is short: give the sampler the same load for longer
+        step()
+        torch.cuda.synchronize()
     for _ in range(args.warmup):
         step()
     sync()
-    sampler.start()
     launches0 = lib.wm_kernel_launch_count()
+    sampler.mark_timed(True)
     ms = time_steps(step, args.steps, 0, sync)
+    sampler.mark_timed(False)
     launches = lib.wm_kernel_launch_count() - launches0
     if per_step_launches is not None:
         launches = per_step_launches * args.steps  # kernels inside the replayed graphs
