@@ -463,6 +463,17 @@ def bench_decode(device, peaks, iters=20):
         "roofline": {"bound": "hbm", "achieved": gbs128, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs128 / peaks["hbm_gbs"], "traffic": None},
     }
+    # the same prefill with a document key mask (70 % of the slots kept): tensor-core forward against the SIMT family
+    key_mask = torch.rand(batch, slots, device=device) < 0.7
+    with torch.no_grad():
+        masked = {}
+        for name, backend in (("tcgen05", "sm100"), ("simt", "sm100_simt")):
+            call = lambda: strict_causal_attention(q128, k, v, query_start=starts, kv_lengths=lengths, key_mask=key_mask, backend=backend)
+            masked[name] = time_steps(call, max(3, iters // 4), 2, torch.cuda.synchronize) / max(3, iters // 4)
+    prefill["with_key_mask"] = {
+        "ms": masked["tcgen05"], "value": nbytes / (masked["tcgen05"] * 1e-3) / 1e9, "unit": "GB/s",
+        "simt_ms": masked["simt"], "note": "K/V bytes as above (masked rows are loaded with their tile)",
+    }
     return result, prefill
 
 

@@ -213,7 +213,7 @@ def test_gradients_with_nan_in_unused_capacity(length, masked, backend):
     """Cached-prefix prefill with gradients: slots at or beyond kv_lengths hold NaN; the gradients must be finite,
     match the oracle, and be exactly zero for the slots nobody sees."""
     if masked and backend == "sm100_tcgen05":
-        pytest.skip("key_mask problems run on the SIMT kernels")
+        pytest.skip("the tcgen05 gradient kernels take no key_mask (the forward does, see the test below)")
     torch.manual_seed(41)
     B, H, N, D = 2, 2, 333, 64
     lengths = torch.tensor([150, 290])
@@ -243,3 +243,48 @@ def test_gradients_with_nan_in_unused_capacity(length, masked, backend):
     for b in range(B):
         assert grads[1][b, :, int(lengths[b]):].abs().max().item() == 0
         assert grads[2][b, :, int(lengths[b]):].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("dummy", [False, True])
+@pytest.mark.parametrize("heads,kv_heads", [(4, 4), (4, 2)])
+@pytest.mark.parametrize("length", [128, 200, 37])
+def test_key_mask_prefill_on_the_tcgen05_forward(length, heads, kv_heads, dummy):
+    """Document-masked cached-prefix prefill: the key mask is applied per tile inside the tensor-core forward.  Slots
+    the mask removes and slots beyond the committed lengths hold NaN in K and V; nothing of it may reach the result."""
+    torch.manual_seed(77)
+    B, N, D = 3, 700, 64
+    lead = int(dummy)
+    lengths = torch.tensor([650, 300, 129])
+    starts = (lengths - length).clamp_min(0)
+    q = torch.randn(B, heads, length, D).bfloat16()
+    k, v = (torch.randn(B, kv_heads, N + lead, D).bfloat16() for _ in range(2))
+    key_mask = torch.rand(B, N + lead) > 0.3
+    key_mask[:, 0] = True
+    key_mask[0, 128:256] = False  # a whole tile removed
+    key_mask[1, :128] = True      # a whole tile kept
+    kn, vn = k.clone(), v.clone()
+    for b in range(B):
+        kn[b, :, lead + int(lengths[b]):] = float("nan")
+        vn[b, :, lead + int(lengths[b]):] = float("nan")
+        kn[b][:, ~key_mask[b]] = float("nan")
+        vn[b][:, ~key_mask[b]] = float("nan")
+    args = dict(query_start=starts.cuda(), kv_lengths=lengths.cuda(), use_dummy_token=dummy, key_mask=key_mask.cuda())
+    with torch.no_grad():
+        out = strict_causal_attention(q.cuda(), kn.cuda(), vn.cuda(), backend="sm100_tcgen05", **args)
+        simt = strict_causal_attention(q.cuda(), kn.cuda(), vn.cuda(), backend="sm100_simt", **args)
+    exp = oracle.strict_causal_oracle(
+        q.double(), k.double(), v.double(), query_start=starts, kv_lengths=lengths, use_dummy_token=dummy, key_mask=key_mask
+    )
+    assert torch.isfinite(out).all()
+    assert_parity(out.float(), exp, what="tcgen05 forward with key_mask", **BF16_TOL)
+    assert_parity(out.float(), simt.float(), what="tcgen05 vs simt", **BF16_TOL)
+    # with gradients the default backend runs this forward and the SIMT gradient kernels: one function
+    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, k, v))
+    out2 = strict_causal_attention(qq, kk, vv, **args)
+    probe = torch.randn_like(out2)
+    grads = torch.autograd.grad(out2, (qq, kk, vv), probe)
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp2 = oracle.strict_causal_oracle(qo, ko, vo, query_start=starts, kv_lengths=lengths, use_dummy_token=dummy, key_mask=key_mask)
+    exp_grads = torch.autograd.grad(exp2, (qo, ko, vo), probe.cpu().double())
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert_parity(g.float(), e, what=name, **BF16_TOL)

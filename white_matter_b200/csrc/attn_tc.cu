@@ -335,7 +335,7 @@ int next_epoch() {
 
 bool tc_fwd_supported(const wm_attn_args& a) {
   if (a.dtype != WM_BF16 || a.head_dim != kHeadDim) return false;
-  if (a.mask == WM_MASK_PACKED || a.key_mask != nullptr) return false;
+  if (a.mask == WM_MASK_PACKED) return false;
   if (!tma_ok(a.q, a.q_strides, a.batch, a.q_heads, a.q_len)) return false;
   if (!tma_ok(a.k, a.k_strides, a.batch, a.kv_heads, a.k_len)) return false;
   if (!tma_ok(a.v, a.v_strides, a.batch, a.kv_heads, a.k_len)) return false;
@@ -412,7 +412,7 @@ int tc_device_status(bool reset) {
 }
 
 bool tc_bwd_supported(const wm_attn_args& a) {
-  if (!tc_fwd_supported(a)) return false;
+  if (!tc_fwd_supported(a) || a.key_mask != nullptr) return false;  // the gradient kernels take no key mask
   if (a.dout == nullptr) return true;  // shape query before the tensors exist
   if (!tma_ok(a.dout, a.dout_strides, a.batch, a.q_heads, a.q_len)) return false;
   if (!tma_ok(a.dk, a.dk_strides, a.batch, a.kv_heads, a.k_len)) return false;

@@ -199,8 +199,22 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
         }
       }
     }
+    // the caller's key mask of this tile as four words (bit c of word w: slot j0 + 32w + c may be seen)
+    uint32_t km0 = 0xffffffffu, km1 = 0xffffffffu, km2 = 0xffffffffu, km3 = 0xffffffffu;
+    if (a.key_mask != nullptr) {
+      const unsigned char* mrow = a.key_mask + static_cast<long long>(batch) * a.k_len;
+      auto kept = [&](int col) -> bool {
+        const int j = j0 + col + lane;
+        return j < a.k_len && mrow[j] != 0;
+      };
+      km0 = __ballot_sync(0xffffffffu, kept(0));
+      km1 = __ballot_sync(0xffffffffu, kept(32));
+      km2 = __ballot_sync(0xffffffffu, kept(64));
+      km3 = __ballot_sync(0xffffffffu, kept(96));
+    }
+    const bool km_all = (km0 & km1 & km2 & km3) == 0xffffffffu;
     // whole-warp shortcuts: nothing to mask, or nothing to see
-    const bool warp_full = __all_sync(0xffffffffu, cls == kTileFull);
+    const bool warp_full = km_all && __all_sync(0xffffffffu, cls == kTileFull);
     const bool warp_none = __all_sync(0xffffffffu, cls == kTileNone);
     const int lim = rb.hi - j0;
     const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
@@ -215,10 +229,10 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
         const int left = lim_eff - col0;
         return left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
       };
-      vis0 = causal_mask(0) & dm[0];
-      vis1 = causal_mask(32) & dm[1];
-      vis2 = causal_mask(64) & dm[2];
-      vis3 = causal_mask(96) & dm[3];
+      vis0 = causal_mask(0) & dm[0] & km0;
+      vis1 = causal_mask(32) & dm[1] & km1;
+      vis2 = causal_mask(64) & dm[2] & km2;
+      vis3 = causal_mask(96) & dm[3] & km3;
     }
     const uint32_t s_tmem = tmem + static_cast<uint32_t>(sb) * kTileN + lane_base;
     if (!wait_or_abort(sm, &sm.s_full[sb], (n / kScoreBuffers) & 1, 31)) return;
@@ -386,11 +400,14 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     }
     ptx::tmem_wait_st();
     WM_TRACE(900 + n);
-    // last tile: value rows at or beyond the largest visible slot may hold anything (unused cache capacity)
-    if (n == w.n_tiles - 1 && w.kmax < j0 + kTileN) {
+    // last tile: value rows at or beyond the largest visible slot may hold anything (unused cache capacity); so
+    // may rows that the caller's key mask removes: their weights are zero, but zero times NaN is not
+    const bool last_ragged = n == w.n_tiles - 1 && w.kmax < j0 + kTileN;
+    if (last_ragged || !km_all) {
       const int s = n % kStages;
       if (!wait_or_abort(sm, &sm.v_full[s], (n / kStages) & 1, 34)) return;
-      if (j0 + row >= w.kmax) {
+      const uint32_t km_word = row < 32 ? km0 : (row < 64 ? km1 : (row < 96 ? km2 : km3));
+      if ((last_ragged && j0 + row >= w.kmax) || !((km_word >> (row & 31)) & 1u)) {
         uint4* vrow = reinterpret_cast<uint4*>(sm.v[s] + row * 128);
 #pragma unroll
         for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
