@@ -288,3 +288,35 @@ def test_key_mask_prefill_on_the_tcgen05_forward(length, heads, kv_heads, dummy)
     exp_grads = torch.autograd.grad(exp2, (qo, ko, vo), probe.cpu().double())
     for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
         assert_parity(g.float(), e, what=name, **BF16_TOL)
+
+
+@pytest.mark.parametrize("dummy", [False, True])
+@pytest.mark.parametrize("backend", ["sm100_tcgen05", "sm100_simt"])
+def test_padded_jacobi_schedule_on_the_tensor_core_kernels(backend, dummy):
+    """Rows with padding (negative ids) at the end, in the middle of a document and at the start: padding is neither a
+    query nor a key and does not end a run of equal ids.  Forward and gradients against the oracle's packed path."""
+    torch.manual_seed(63)
+    B, H, T, D = 3, 2, 300, 64
+    lead = int(dummy)
+    docs = torch.zeros(B, T, dtype=torch.long)
+    docs[0, 120:] = 1
+    docs[0, 250:] = -1                 # padded tail
+    docs[1, 40:200] = 2
+    docs[1, 90:110] = -1               # padding inside document 2: the run goes on behind it
+    docs[1, 200:] = 0                  # id 0 again: a new run
+    docs[2, :17] = -1                  # padded head
+    docs[2, 17:] = 5
+    q, probe = (torch.randn(B, H, T, D).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, H, T + lead, D).bfloat16() for _ in range(2))
+    schedule = prepare_strict_causal_metadata(docs.cuda(), T, use_dummy_token=dummy)
+    assert schedule.dense_documents is not None  # whole rows: eligible for the stride-1 cyclic form
+    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = strict_causal_attention(qq, kk, vv, metadata=schedule, use_dummy_token=dummy, backend=backend)
+    grads = torch.autograd.grad(out, (qq, kk, vv), probe.transpose(1, 2).cuda())
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp = oracle.strict_causal_oracle(qo, ko, vo, metadata=prepare_strict_causal_metadata(docs, T, use_dummy_token=dummy), use_dummy_token=dummy)
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.transpose(1, 2).double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    assert out[0, 250:].abs().max().item() == 0 and out[1, 90:110].abs().max().item() == 0 and out[2, :17].abs().max().item() == 0
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert_parity(g.float(), e, what=name, **BF16_TOL)

@@ -160,6 +160,32 @@ def prepare_feedback_metadata(
     return tuple(result)
 
 
+def _padded_jacobi_tables(ids: np.ndarray, key_length: int, lead: int, device) -> CyclicAttentionMetadata:
+    """The four tables of stride-1 cyclic attention for rows with padding: labels are the ids of the present tokens
+    (-3 for padded queries, -2 for padded keys, -1 for the dummy slot), a query starts at the first present slot of
+    its run of equal ids among the present tokens, and a key is open to the queries up to its run's last token."""
+    batch, length = ids.shape
+    q_seg = np.full((batch, length), -3, dtype=np.int32)
+    k_seg = np.full((batch, length), -2, dtype=np.int32)
+    q_start = np.zeros((batch, length), dtype=np.int32)
+    k_end = np.zeros((batch, length), dtype=np.int32)
+    for b in range(batch):
+        slots = np.flatnonzero(ids[b] >= 0)
+        if not slots.size:
+            continue
+        labels = ids[b][slots]
+        first, stop = _runs(labels)  # in ranks among the present tokens
+        run = np.repeat(np.arange(first.size), stop - first)
+        q_seg[b, slots] = labels
+        k_seg[b, slots] = labels
+        q_start[b, slots] = slots[first][run] + lead
+        k_end[b, slots] = slots[stop - 1][run] + 1
+    key_ids = np.concatenate((np.full((batch, lead), -1, dtype=np.int32), k_seg), axis=1)[:, :key_length]
+    query_end = np.concatenate((np.full((batch, lead), length, dtype=np.int32), k_end), axis=1)[:, :key_length]
+    as_device = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(device)
+    return CyclicAttentionMetadata(as_device(q_seg), as_device(key_ids), as_device(q_start), as_device(query_end))
+
+
 class StrictCausalMetadata:
     """Reusable packed schedule for strict-past attention over documents.
 
@@ -207,9 +233,9 @@ class StrictCausalMetadata:
             k = cu_keys.tolist()
             segments = tuple(zip(q[:-1], q[1:], k[:-1], k[1:], strict=True))
         self.segments = segments
-        # (document ids (B,T) int32, use_dummy_token) when the schedule is plain Jacobi packing: every token is a
-        # query, no padding, no truncation.  Such a schedule equals stride-1 cyclic attention with document
-        # metadata, which the tensor-core kernels take directly.
+        # (document ids (B,T) int32, use_dummy_token) when the schedule is Jacobi packing over whole rows: every
+        # position is a query (padding included, whose result is zero), no truncation.  Such a schedule equals
+        # stride-1 cyclic attention with document metadata, which the tensor-core kernels take directly.
         self.dense_documents = None
         self._cache: dict = {}
 
@@ -236,18 +262,33 @@ class StrictCausalMetadata:
         return cached
 
     def cyclic_equivalent(self, device: torch.device, key_length: int) -> "CyclicAttentionMetadata | None":
-        """Stride-1 cyclic metadata of a plain Jacobi schedule (None when the schedule is not of that form)."""
+        """Stride-1 cyclic metadata of a Jacobi schedule over every token of the rows (None when the schedule is not
+        of that form).  Padding slots (negative ids) become keys of a document no query has and queries of a document
+        no key has; a run of equal ids goes on across padding, as in the packed schedule."""
         if self.dense_documents is None:
             return None
         key = ("cyclic", str(device), key_length)
         cached = self._cache.get(key)
         if cached is None:
             docs, dummy = self.dense_documents
-            docs = docs.to(device)
-            slots = torch.arange(docs.shape[1], device=device)
-            cached = prepare_feedback_metadata(docs, [slots], key_length, use_dummy_token=dummy)[0]
+            if bool((docs >= 0).all()):
+                docs = docs.to(device)
+                slots = torch.arange(docs.shape[1], device=device)
+                cached = prepare_feedback_metadata(docs, [slots], key_length, use_dummy_token=dummy)[0]
+            else:
+                cached = _padded_jacobi_tables(docs.cpu().numpy().astype(np.int64), key_length, int(dummy), device)
             self._cache[key] = cached
         return cached
+
+    def padded_queries(self, device: torch.device) -> "torch.Tensor | None":
+        """(B,T) bool, True where the token is padding (its result is zero), or None without padding."""
+        if self.dense_documents is None:
+            return None
+        key = ("padding", str(device))
+        if key not in self._cache:
+            pad = self.dense_documents[0] < 0
+            self._cache[key] = pad.to(device) if bool(pad.any()) else None
+        return self._cache[key]
 
     def device_tables(self, device: torch.device, q_rows: int, k_rows: int):
         """Device copies of the group table, index lists and tile tables.
@@ -399,7 +440,7 @@ def prepare_strict_causal_metadata(
         and int(query_start) == 0
         and query_length == extent
         and extent > 0
-        and bool((docs >= 0).all())
+        and int(np.abs(docs).max()) < 2**31 - 1
     )
     if plain:
         schedule.dense_documents = (document_ids.detach().to(torch.int32), bool(use_dummy_token))

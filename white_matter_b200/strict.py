@@ -104,7 +104,12 @@ def strict_causal_attention(
             out = operators.cyclic_attn_doc_fwd(
                 query, key[..., :length, :], value[..., :length, :], *cyc, 1, lead_slots - 1, kernel, scale
             )[0]
-            return out.transpose(1, 2)
+            out = out.transpose(1, 2)
+            padded = metadata.padded_queries(query.device)
+            if padded is not None and use_dummy_token:
+                # the shared dummy key is open to every query row; padding rows are not part of the schedule
+                out = out.masked_fill(padded[:, :, None, None], 0)
+            return out
         fwd_q, bwd_q, bwd_k = operators.packed_tile_rows(query, key, kernel)
         if fwd_q != bwd_q:
             raise RuntimeError("forward and backward kernels disagree on the query tile height")
