@@ -112,6 +112,7 @@ typedef struct wm_attn_args {
   /* WM_MASK_CYCLIC */
   int32_t query_stride;
   int32_t query_offset; /* already lowered by one for strict_past; may be -1 */
+  /* document tables: WM_MASK_CYCLIC, and WM_MASK_STRICT on top of its dense bounds (cached-prefix Jacobi) */
   const int32_t* q_seg;       /* (batch, q_len) document of each query, or NULL */
   const int32_t* k_seg;       /* (batch, k_len) document of each key slot; -1 marks the shared dummy */
   const int32_t* q_key_start; /* (batch, q_len) first key slot of the query's document */

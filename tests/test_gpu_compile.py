@@ -111,6 +111,17 @@ def test_opcheck_of_the_registered_operators():
     _opcheck(operators.cyclic_attn_doc_fwd, (q, k, v, *md, 4, 1, 0))
     lengths = torch.tensor([5, 100], device=dev, dtype=torch.int32)
     _opcheck(operators.strict_attn_fwd, (q, k, v, lengths, 0, lengths, None, False, 0.125, 0))
+    # strict family with document tables: 33 queries at per-row positions over 132 key slots
+    from white_matter_b200 import prepare_strict_causal_metadata
+
+    starts = torch.tensor([10, 90], device=dev, dtype=torch.int32)
+    schedule = prepare_strict_causal_metadata(seg.to(dev), 33, query_start=starts, kv_lengths=lengths + 20)
+    tables = schedule.document_tables(torch.device(dev), 132)
+    start_t, limit_t = schedule.dense_bounds(torch.device(dev))
+    _opcheck(operators.strict_doc_fwd, (q, k, v, *tables, start_t, 0, limit_t, False, 0.125, 0))
+    sout, slse = operators.strict_doc_fwd(q, k, v, *tables, start_t, 0, limit_t, False, 0.125, 0)
+    _opcheck(operators.strict_doc_bwd, (q.detach(), k.detach(), v.detach(), *tables, start_t, 0, limit_t, sout.detach(),
+                                        slse.detach(), torch.randn_like(sout).detach(), False, 0.125, 0))
     q1 = torch.randn(2, 4, 1, 64, device=dev, dtype=bf)
     _opcheck(operators.strict_decode, (q1, k.detach(), v.detach(), lengths, 0, lengths, None, False, 0.125))
     src = torch.randn(5, 2, 2, 16, 64, device=dev, dtype=bf, requires_grad=True)

@@ -320,3 +320,39 @@ def test_padded_jacobi_schedule_on_the_tensor_core_kernels(backend, dummy):
     assert out[0, 250:].abs().max().item() == 0 and out[1, 90:110].abs().max().item() == 0 and out[2, :17].abs().max().item() == 0
     for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
         assert_parity(g.float(), e, what=name, **BF16_TOL)
+
+
+@pytest.mark.parametrize("dummy", [False, True])
+@pytest.mark.parametrize("backend", ["sm100_tcgen05", "sm100_simt"])
+def test_cached_prefix_jacobi_with_documents_on_the_tensor_core_kernels(backend, dummy):
+    """Jacobi over the last 150 tokens of rows whose earlier tokens are committed history: per-row first query
+    position, per-row key limits, packed documents and padding, forward and gradients against the oracle's packed
+    path (the tensor-core route takes the schedule as dense bounds plus document tables)."""
+    torch.manual_seed(64)
+    B, H, T, Q, D = 3, 2, 400, 150, 64
+    lead = int(dummy)
+    docs = torch.zeros(B, T, dtype=torch.long)
+    docs[0, 130:] = 1
+    docs[0, 300:] = 2
+    docs[1, 60:390] = 4
+    docs[1, 200:215] = -1              # padding inside the document, among the queries
+    docs[1, 390:] = -1
+    docs[2, :250] = 7
+    docs[2, 250:] = 8                  # the queries of row 2 begin exactly at a document start
+    starts = torch.tensor([250, 180, 250])
+    limits = torch.tensor([400, 260, 333])  # row 1 and 2: keys stop before the last queries
+    q, probe = (torch.randn(B, H, Q, D).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, H, T + lead, D).bfloat16() for _ in range(2))
+    schedule = prepare_strict_causal_metadata(docs.cuda(), Q, query_start=starts.cuda(), kv_lengths=limits.cuda(), use_dummy_token=dummy)
+    assert schedule.dense_documents is not None
+    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = strict_causal_attention(qq, kk, vv, metadata=schedule, use_dummy_token=dummy, backend=backend)
+    grads = torch.autograd.grad(out, (qq, kk, vv), probe.transpose(1, 2).cuda())
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    host_schedule = prepare_strict_causal_metadata(docs, Q, query_start=starts, kv_lengths=limits, use_dummy_token=dummy)
+    exp = oracle.strict_causal_oracle(qo, ko, vo, metadata=host_schedule, use_dummy_token=dummy)
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.transpose(1, 2).double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    assert out[1, 20:35].abs().max().item() == 0  # the padded queries of row 1
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert_parity(g.float(), e, what=name, **BF16_TOL)

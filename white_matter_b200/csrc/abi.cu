@@ -56,7 +56,9 @@ int validate_attn(const wm_attn_args* a, bool backward, const char* who) {
     if (have != 0 && have != 4) return fail(WM_EINVAL, "%s: document metadata requires four tensors", who);
   } else if (a->mask == WM_MASK_STRICT) {
     if (a->use_dummy != 0 && a->use_dummy != 1) return fail(WM_EINVAL, "%s: use_dummy must be 0 or 1", who);
-    if (a->q_seg != nullptr) return fail(WM_EINVAL, "%s: document tensors belong to the cyclic family", who);
+    int have = (a->q_seg != nullptr) + (a->k_seg != nullptr) + (a->q_key_start != nullptr) + (a->k_query_end != nullptr);
+    if (have != 0 && have != 4) return fail(WM_EINVAL, "%s: document metadata requires four tensors", who);
+    if (have != 0 && a->key_mask != nullptr) return fail(WM_EINVAL, "%s: document metadata and key_mask are mutually exclusive", who);
   } else if (a->mask == WM_MASK_PACKED) {
     if (a->n_groups < 0 || (a->n_groups > 0 && (a->groups == nullptr || a->query_indices == nullptr ||
                                                 a->key_indices == nullptr || a->query_tiles == nullptr)))

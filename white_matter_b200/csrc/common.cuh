@@ -166,6 +166,11 @@ __device__ __forceinline__ RowBound row_bound(const wm_attn_args& a, const Group
     }
     if (pos < 0) pos = 0;
     r.hi = clampi(pos + a.use_dummy, 0, a.k_len);
+    if (a.q_seg != nullptr) {  // packed documents on top of the dense bounds (cached-prefix Jacobi)
+      long long at = static_cast<long long>(batch) * a.q_len + i;
+      r.lo = a.q_key_start[at];
+      r.seg = a.q_seg[at];
+    }
   } else {
     r.hi = clampi(static_cast<long long>(g.nk) - g.nq + 1 + i, 0, g.nk);
   }

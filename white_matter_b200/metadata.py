@@ -160,28 +160,35 @@ def prepare_feedback_metadata(
     return tuple(result)
 
 
-def _padded_jacobi_tables(ids: np.ndarray, key_length: int, lead: int, device) -> CyclicAttentionMetadata:
-    """The four tables of stride-1 cyclic attention for rows with padding: labels are the ids of the present tokens
-    (-3 for padded queries, -2 for padded keys, -1 for the dummy slot), a query starts at the first present slot of
-    its run of equal ids among the present tokens, and a key is open to the queries up to its run's last token."""
+def _jacobi_tables(ids: np.ndarray, starts: np.ndarray, query_length: int, key_length: int, lead: int, device) -> CyclicAttentionMetadata:
+    """The four document tables of a Jacobi schedule over ``query_length`` queries per row, query i of row b being the
+    token at position starts[b] + i, against the row's key slots: labels are the ids of the present tokens (-3 for
+    padded queries, -2 for padded keys, -1 for the dummy slot), a query starts at the first present slot of its run
+    of equal ids among the present tokens, and a key is open to the queries up to its run's last token."""
     batch, length = ids.shape
-    q_seg = np.full((batch, length), -3, dtype=np.int32)
+    q_seg = np.full((batch, query_length), -3, dtype=np.int32)
+    q_start = np.zeros((batch, query_length), dtype=np.int32)
     k_seg = np.full((batch, length), -2, dtype=np.int32)
-    q_start = np.zeros((batch, length), dtype=np.int32)
     k_end = np.zeros((batch, length), dtype=np.int32)
+    steps = np.arange(query_length, dtype=np.int64)
     for b in range(batch):
-        slots = np.flatnonzero(ids[b] >= 0)
+        present = ids[b] >= 0
+        slots = np.flatnonzero(present)
         if not slots.size:
             continue
         labels = ids[b][slots]
         first, stop = _runs(labels)  # in ranks among the present tokens
         run = np.repeat(np.arange(first.size), stop - first)
-        q_seg[b, slots] = labels
+        run_of_slot = np.zeros(length, dtype=np.int64)
+        run_of_slot[slots] = run
         k_seg[b, slots] = labels
-        q_start[b, slots] = slots[first][run] + lead
-        k_end[b, slots] = slots[stop - 1][run] + 1
+        k_end[b, slots] = np.clip(slots[stop - 1][run] + 1 - starts[b], 0, query_length)
+        pos = starts[b] + steps
+        live = present[pos]
+        q_seg[b, live] = ids[b][pos[live]]
+        q_start[b, live] = slots[first][run_of_slot[pos[live]]] + lead
     key_ids = np.concatenate((np.full((batch, lead), -1, dtype=np.int32), k_seg), axis=1)[:, :key_length]
-    query_end = np.concatenate((np.full((batch, lead), length, dtype=np.int32), k_end), axis=1)[:, :key_length]
+    query_end = np.concatenate((np.full((batch, lead), query_length, dtype=np.int32), k_end), axis=1)[:, :key_length]
     as_device = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(device)
     return CyclicAttentionMetadata(as_device(q_seg), as_device(key_ids), as_device(q_start), as_device(query_end))
 
@@ -207,6 +214,7 @@ class StrictCausalMetadata:
         "key_extent",
         "segments",
         "dense_documents",
+        "max_queries_per_row",
         "_cache",
     )
 
@@ -233,10 +241,11 @@ class StrictCausalMetadata:
             k = cu_keys.tolist()
             segments = tuple(zip(q[:-1], q[1:], k[:-1], k[1:], strict=True))
         self.segments = segments
-        # (document ids (B,T) int32, use_dummy_token) when the schedule is Jacobi packing over whole rows: every
-        # position is a query (padding included, whose result is zero), no truncation.  Such a schedule equals
-        # stride-1 cyclic attention with document metadata, which the tensor-core kernels take directly.
+        # (document ids (B,T) int32, use_dummy_token, per-row first query position, per-row key limits or None) when
+        # the schedule came from rows of document ids: it then equals strict-past attention with dense per-row
+        # bounds plus document tables, which the tensor-core kernels take directly.
         self.dense_documents = None
+        self.max_queries_per_row = 0
         self._cache: dict = {}
 
     def with_key_extent(self, key_extent: int) -> "StrictCausalMetadata":
@@ -258,35 +267,45 @@ class StrictCausalMetadata:
                 self.segments,
             )
             cached.dense_documents = self.dense_documents
+            cached.max_queries_per_row = self.max_queries_per_row
             self._cache[("extent", key_extent)] = cached
         return cached
 
-    def cyclic_equivalent(self, device: torch.device, key_length: int) -> "CyclicAttentionMetadata | None":
-        """Stride-1 cyclic metadata of a Jacobi schedule over every token of the rows (None when the schedule is not
-        of that form).  Padding slots (negative ids) become keys of a document no query has and queries of a document
-        no key has; a run of equal ids goes on across padding, as in the packed schedule."""
+    def document_tables(self, device: torch.device, key_length: int) -> "CyclicAttentionMetadata | None":
+        """The schedule as dense per-row bounds plus document tables (None when it was not built from whole rows of
+        document ids): the form the tensor-core kernels take.  Query i of row b is the token at position start_b + i
+        and sees the present slots of its run of equal ids in front of min(position, limit_b).  Padding slots
+        (negative ids) become keys of a document no query has and queries of a document no key has; a run goes on
+        across padding, as in the packed schedule."""
         if self.dense_documents is None:
             return None
-        key = ("cyclic", str(device), key_length)
+        key = ("tables", str(device), key_length)
         cached = self._cache.get(key)
         if cached is None:
-            docs, dummy = self.dense_documents
-            if bool((docs >= 0).all()):
-                docs = docs.to(device)
-                slots = torch.arange(docs.shape[1], device=device)
-                cached = prepare_feedback_metadata(docs, [slots], key_length, use_dummy_token=dummy)[0]
-            else:
-                cached = _padded_jacobi_tables(docs.cpu().numpy().astype(np.int64), key_length, int(dummy), device)
+            docs, dummy, starts, _ = self.dense_documents
+            cached = _jacobi_tables(docs.cpu().numpy().astype(np.int64), starts, self.max_queries_per_row, key_length, int(dummy), device)
             self._cache[key] = cached
         return cached
 
+    def dense_bounds(self, device: torch.device):
+        """(query_start int32 (B,) or None when every row starts at 0, kv_lengths int32 (B,) or None) on ``device``."""
+        key = ("bounds", str(device))
+        if key not in self._cache:
+            _, _, starts, limits = self.dense_documents
+            start_t = None if not starts.any() else torch.from_numpy(starts.astype(np.int32)).to(device)
+            limit_t = None if limits is None else torch.from_numpy(limits.astype(np.int32)).to(device)
+            self._cache[key] = (start_t, limit_t)
+        return self._cache[key]
+
     def padded_queries(self, device: torch.device) -> "torch.Tensor | None":
-        """(B,T) bool, True where the token is padding (its result is zero), or None without padding."""
+        """(B,T) bool, True where the query token is padding (its result is zero), or None without padding."""
         if self.dense_documents is None:
             return None
         key = ("padding", str(device))
         if key not in self._cache:
-            pad = self.dense_documents[0] < 0
+            docs, _, starts, _ = self.dense_documents
+            pos = torch.from_numpy(starts)[:, None] + torch.arange(self.max_queries_per_row)[None, :]
+            pad = torch.gather(docs.cpu().long(), 1, pos) < 0
             self._cache[key] = pad.to(device) if bool(pad.any()) else None
         return self._cache[key]
 
@@ -434,14 +453,7 @@ def prepare_strict_causal_metadata(
         width,
         width,
     )
-    plain = (
-        limits is None
-        and not isinstance(query_start, torch.Tensor)
-        and int(query_start) == 0
-        and query_length == extent
-        and extent > 0
-        and int(np.abs(docs).max()) < 2**31 - 1
-    )
-    if plain:
-        schedule.dense_documents = (document_ids.detach().to(torch.int32), bool(use_dummy_token))
+    if extent > 0 and query_length > 0 and int(np.abs(docs).max()) < 2**31 - 1:
+        schedule.dense_documents = (document_ids.detach().to(torch.int32), bool(use_dummy_token), starts.copy(), None if limits is None else limits.copy())
+        schedule.max_queries_per_row = query_length
     return schedule

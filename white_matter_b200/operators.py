@@ -368,6 +368,108 @@ def _strict_backward(ctx, dOut, dLse):
 strict_attn_fwd.register_autograd(_strict_backward, setup_context=_strict_setup)
 
 
+def _strict_doc_args(Q, K, V, tables, query_start, query_start_value, kv_lengths, use_dummy, scale, kernel):
+    a, keep = _strict_args(Q, K, V, query_start, query_start_value, kv_lengths, None, use_dummy, scale, kernel)
+    tables = [_int32(t) for t in tables]
+    a.q_seg, a.k_seg, a.q_key_start, a.k_query_end = (t.data_ptr() for t in tables)
+    return a, keep + tables
+
+
+@torch.library.custom_op("wm_b200::strict_doc_fwd", mutates_args=())
+def strict_doc_fwd(
+    Q: Tensor,
+    K: Tensor,
+    V: Tensor,
+    QSeg: Tensor,
+    KSeg: Tensor,
+    QStart: Tensor,
+    KQEnd: Tensor,
+    query_start: Optional[Tensor],
+    query_start_value: int,
+    kv_lengths: Optional[Tensor],
+    use_dummy: bool,
+    scale: float,
+    kernel: int,
+) -> tuple[Tensor, Tensor]:
+    """Strict-past attention with dense per-row bounds and packed documents (cached-prefix Jacobi): Out (B,H,T,D)
+    view of (B,T,H,D) storage and Lse.  The tables are those of the cyclic document operators, over the query rows
+    and the key slots of this call."""
+    a, keep = _strict_doc_args(Q, K, V, (QSeg, KSeg, QStart, KQEnd), query_start, query_start_value, kv_lengths, use_dummy, scale, kernel)
+    out, lse = _new_output(Q)
+    _set_out(a, out, lse)
+    _native.call("wm_strict_attn_fwd", a, Q.device)
+    del keep
+    return out, lse
+
+
+@strict_doc_fwd.register_fake
+def _(Q, K, V, QSeg, KSeg, QStart, KQEnd, query_start, query_start_value, kv_lengths, use_dummy, scale, kernel):
+    return _fake_output(Q)
+
+
+@torch.library.custom_op("wm_b200::strict_doc_bwd", mutates_args=())
+def strict_doc_bwd(
+    Q: Tensor,
+    K: Tensor,
+    V: Tensor,
+    QSeg: Tensor,
+    KSeg: Tensor,
+    QStart: Tensor,
+    KQEnd: Tensor,
+    query_start: Optional[Tensor],
+    query_start_value: int,
+    kv_lengths: Optional[Tensor],
+    Out: Tensor,
+    Lse: Tensor,
+    dOut: Tensor,
+    use_dummy: bool,
+    scale: float,
+    kernel: int,
+) -> tuple[Tensor, Tensor, Tensor]:
+    a, keep = _strict_doc_args(Q, K, V, (QSeg, KSeg, QStart, KQEnd), query_start, query_start_value, kv_lengths, use_dummy, scale, kernel)
+    out = _unit_inner(Out, Q.dtype)
+    dout = _unit_inner(dOut, Q.dtype)
+    lse = Lse.contiguous()
+    _set_out(a, out, lse)
+    dq, dk, dv = _new_grads(Q, K, V)
+    _set_grads(a, dout, dq, dk, dv)
+    ws = _bwd_workspace(a, Q.device)
+    _native.call("wm_strict_attn_bwd", a, Q.device)
+    del ws, keep
+    return dq, dk, dv
+
+
+@strict_doc_bwd.register_fake
+def _(Q, K, V, QSeg, KSeg, QStart, KQEnd, query_start, query_start_value, kv_lengths, Out, Lse, dOut, use_dummy, scale, kernel):
+    return _fake_grads(Q, K, V)
+
+
+def _strict_doc_setup(ctx, inputs, output):
+    *tensors, ctx.query_start_value, kv_lengths, ctx.use_dummy, ctx.scale, ctx.kernel = inputs
+    ctx.has_start = tensors[7] is not None
+    ctx.has_limit = kv_lengths is not None
+    saved = tensors[:7] + ([tensors[7]] if ctx.has_start else []) + ([kv_lengths] if ctx.has_limit else [])
+    ctx.save_for_backward(*saved, *output)
+    ctx.set_materialize_grads(False)
+
+
+def _strict_doc_backward(ctx, dOut, dLse):
+    saved = list(ctx.saved_tensors)
+    out, lse = saved[-2:]
+    tensors = saved[:7]
+    at = 7
+    start = saved[at] if ctx.has_start else None
+    at += int(ctx.has_start)
+    limit = saved[at] if ctx.has_limit else None
+    if dOut is None:
+        dOut = torch.zeros_like(out)
+    grads = strict_doc_bwd(*tensors, start, ctx.query_start_value, limit, out, lse, dOut, ctx.use_dummy, ctx.scale, ctx.kernel)
+    return (*grads, *((None,) * 10))
+
+
+strict_doc_fwd.register_autograd(_strict_doc_backward, setup_context=_strict_doc_setup)
+
+
 @torch.library.custom_op("wm_b200::strict_decode", mutates_args=())
 def strict_decode(
     Q: Tensor,

@@ -90,19 +90,20 @@ def strict_causal_attention(
         if metadata.query_indices.numel() == 0:
             zero = (query[..., :0, :].sum() + key[..., :0, :].sum() + value[..., :0, :].sum()).to(query.dtype)
             return query.new_zeros(batch, length, heads, dim) + zero
-        # A plain Jacobi schedule (every token a query, no padding or truncation) is stride-1 cyclic attention
-        # with document metadata; that form runs on the tensor-core kernels without gathering.
-        lead_slots = int(use_dummy_token)
+        # A schedule built from rows of document ids is strict-past attention with dense per-row bounds plus document
+        # tables; that form runs on the tensor-core kernels without gathering.
         if (
             metadata.dense_documents is not None
             and metadata.dense_documents[1] == use_dummy_token
-            and metadata.dense_documents[0].shape == (batch, length)
-            and key.shape[-2] >= length
+            and metadata.dense_documents[0].shape[0] == batch
+            and metadata.max_queries_per_row == length
             and _BACKENDS[backend] != "simt"
         ):
-            cyc = metadata.cyclic_equivalent(query.device, length)
-            out = operators.cyclic_attn_doc_fwd(
-                query, key[..., :length, :], value[..., :length, :], *cyc, 1, lead_slots - 1, kernel, scale
+            slots = min(key.shape[-2], metadata.dense_documents[0].shape[1] + int(use_dummy_token))
+            tables = metadata.document_tables(query.device, slots)
+            start_t, limit_t = metadata.dense_bounds(query.device)
+            out = operators.strict_doc_fwd(
+                query, key[..., :slots, :], value[..., :slots, :], *tables, start_t, 0, limit_t, use_dummy_token, scale, kernel
             )[0]
             out = out.transpose(1, 2)
             padded = metadata.padded_queries(query.device)
