@@ -496,12 +496,34 @@ def bench_jacobi(device, peaks, iters=10):
             run = run + 1 if t and row[t] == row[t - 1] else 1
             pairs += run - 1  # strictly earlier tokens of the same document
     tf = 4 * dim * pairs * heads / (ms * 1e-3) / 1e12
-    return {
+    result = {
         "workload": "strict Jacobi prefill forward B=8 H=16 T=2048 D=64 bf16, packed documents (geometric, mean 512)",
         "ms": ms, "value": tf, "unit": "TFLOP/s",
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_kind": "bf16_tflops (kernel timed alone)"},
     }
+    # cached-prefix Jacobi with documents: the last 512 tokens of 4096-token rows are the queries, the rest is
+    # committed history; the schedule runs as dense per-row bounds plus document tables on the tensor-core kernel,
+    # and as gathered index lists on the SIMT kernels
+    rows, new = 4096, 512
+    docs = geometric_documents(batch, rows, 512, seed=11)
+    schedule = prepare_strict_causal_metadata(docs.to(device), new, query_start=rows - new)
+    qn = (torch.randn(batch, heads, new, dim, generator=gen) * dim ** -0.5).to(device, torch.bfloat16)
+    kn, vn = (torch.randn(batch, heads, rows, dim, generator=gen).to(device, torch.bfloat16) for _ in range(2))
+    nq = (schedule.cu_queries[1:] - schedule.cu_queries[:-1]).cpu().long()
+    nk = (schedule.cu_keys[1:] - schedule.cu_keys[:-1]).cpu().long()
+    visible = int((nq * (nk - nq + 1) + nq * (nq - 1) // 2).sum().item())
+    with torch.no_grad():
+        timed = {}
+        for name, backend in (("tcgen05", "sm100"), ("simt", "sm100_simt")):
+            call = lambda: strict_causal_attention(qn, kn, vn, metadata=schedule, backend=backend)
+            timed[name] = time_steps(call, max(3, iters // 2), 2, torch.cuda.synchronize) / max(3, iters // 2)
+    result["cached_prefix_with_documents"] = {
+        "workload": "Jacobi over the last 512 of 4096 tokens per row, B=8 H=16 D=64 bf16, documents of mean 512",
+        "ms": timed["tcgen05"], "value": 4 * dim * visible * heads / (timed["tcgen05"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "simt_ms": timed["simt"],
+    }
+    return result
 
 
 def bench_mixing(device, peaks, iters=10):
