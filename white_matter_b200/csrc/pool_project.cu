@@ -248,8 +248,9 @@ constexpr int kCoefPitch = 20;  // words per channel row of the coefficient tile
 
 struct MmaLayout {
   int pitch;  // bytes per row of the tables and of the source tile
-  size_t tables, tile, coef, bias, red, inv, sums, bar, total;
-  __host__ __device__ MmaLayout(int sources, int channels, int hidden, int warps) {
+  size_t tables, tile, coef, bias, red, inv, sums, part, bar, total;
+  // `routed` > 0 reserves two buffers for the routing partials of a row (both sides, `routed` sources each)
+  __host__ __device__ MmaLayout(int sources, int channels, int hidden, int warps, int routed = 0) {
     const int padded = (channels + kChannelsPerPass - 1) / kChannelsPerPass * kChannelsPerPass;
     pitch = hidden * 2 + 16;
     tables = 0;
@@ -259,7 +260,8 @@ struct MmaLayout {
     red = bias + (static_cast<size_t>(2) * channels * sources * 4 + 15) / 16 * 16;
     inv = red + static_cast<size_t>(kMmaWarps) * kMmaSources * 4;
     sums = inv + kMmaSources * 4;
-    bar = sums + static_cast<size_t>(2) * warps * 2 * kChannelsPerPass * 4;
+    part = (sums + static_cast<size_t>(2) * warps * 2 * kChannelsPerPass * 4 + 15) / 16 * 16;
+    bar = part + static_cast<size_t>(2) * 2 * routed * channels * sources * 2;
     total = bar + 16;
   }
 };
@@ -308,17 +310,19 @@ constexpr int kMixWaitCode = 240;  // status code of a source tile that never ar
 
 // kL / kC / kDm fix sources, channels and hidden at compile time (0: taken from the arguments).
 template <int kL, int kC, int kDm>
-__global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_args a, const long long rows, int* status) {
+__global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_args a, const long long rows, int* status, const int staged_partials) {
   extern __shared__ __align__(128) unsigned char raw[];
   const int L = kL ? kL : a.sources, C = kC ? kC : a.channels, Dm = kDm ? kDm : a.hidden;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   const int g = lane >> 2, q = lane & 3;
   const int CL = C * L;
   const int Cpad = (C + kChannelsPerPass - 1) / kChannelsPerPass * kChannelsPerPass;
-  const MmaLayout lay(L, C, Dm, warps);
+  const MmaLayout lay(L, C, Dm, warps, staged_partials ? a.n_routed : 0);
   const int pitch = lay.pitch;
   unsigned char* tables = raw + lay.tables;
   unsigned char* tile = raw + lay.tile;
+  unsigned char* part_rooms = raw + lay.part;  // [row parity][side][routed source][channels * sources] bf16
+  const size_t part_room = staged_partials ? static_cast<size_t>(2) * a.n_routed * CL * 2 : 0;
   uint32_t* coef = reinterpret_cast<uint32_t*>(raw + lay.coef);
   float* bias = reinterpret_cast<float*>(raw + lay.bias);
   float* red = reinterpret_cast<float*>(raw + lay.red);
@@ -359,20 +363,31 @@ __global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_
   }
   __syncthreads();
 
-  const uint32_t tile_bytes = static_cast<uint32_t>(L) * Dm * 2;
-  auto fetch = [&](long long row) {  // first warp: the row's sources into the tile, one bulk copy per lane and source
+  const uint32_t tile_bytes = static_cast<uint32_t>(L) * Dm * 2 + static_cast<uint32_t>(part_room);
+  // first warp: the row's sources into the tile, one bulk copy per source, and (dynamic router) its routing
+  // partials into the room of the row's parity; `turn` counts the block's rows
+  auto fetch = [&](long long row, int turn) {
     const long long b = row / a.tokens, t = row - b * a.tokens;
     const bf16* x0 = static_cast<const bf16*>(a.stacked) + b * a.stacked_strides[0] + t * a.stacked_strides[1];
     if (lane == 0)
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(bar)), "r"(tile_bytes) : "memory");
     __syncwarp();
     if (lane < L) bulk_load(tile + lane * pitch, x0 + lane * a.stacked_strides[2], Dm * 2, bar);
+    if (staged_partials) {
+      unsigned char* room = part_rooms + (turn & 1) * part_room;
+      for (int i = lane; i < 2 * a.n_routed; i += 32) {
+        const int side = i / a.n_routed, j = i - side * a.n_routed;
+        const bf16* src = static_cast<const bf16*>(side ? a.partial_v : a.partial_k) + (j * rows + row) * CL;
+        bulk_load(room + static_cast<size_t>(i) * CL * 2, src, CL * 2, bar);
+      }
+    }
   };
-  if (warp == 0 && blockIdx.x < rows) fetch(blockIdx.x);
+  if (warp == 0 && blockIdx.x < rows) fetch(blockIdx.x, 0);
 
   const int off = (64 * warp + 8 * g) * 2;  // byte offset of this thread's eight columns in a row
   uint32_t parity = 0;
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+  int turn = 0;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x, ++turn) {
     const bool arrived = barrier_wait(bar, parity);
     parity ^= 1;
     if (!__syncthreads_and(arrived)) {
@@ -406,8 +421,8 @@ __global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_
     __syncthreads();  // the tile has been read by everyone: the next row may overwrite it
     const long long next = row + gridDim.x;
     if (next < rows) {
-      if (warp == 0) fetch(next);
-      if (a.partial_k != nullptr) {  // the next row's routing partials into L2
+      if (warp == 0) fetch(next, turn + 1);
+      if (a.partial_k != nullptr && !staged_partials) {  // the next row's routing partials into L2
         const int lines = (CL * 2 + 127) / 128;
         for (int i = tid - 32; i >= 0 && i < 2 * a.n_routed * lines; i += blockDim.x - 32) {
           const int side = i / (a.n_routed * lines), rem = i - side * a.n_routed * lines;
@@ -439,10 +454,15 @@ __global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_
         if (c < C && l < L) {
           const int o = c * L + l;
           float alpha = bias[side * CL + o];
-          const bf16* part = static_cast<const bf16*>(side ? a.partial_v : a.partial_k);
-          if (part != nullptr)
+          if (staged_partials) {
+            const bf16* part = reinterpret_cast<const bf16*>(part_rooms + (turn & 1) * part_room) + static_cast<size_t>(side) * a.n_routed * CL + o;
+            for (int j = 0; j < a.n_routed; ++j)
+              alpha = fmaf(inv[a.route_start + j * a.route_stride], __bfloat162float(part[j * CL]), alpha);
+          } else if (a.partial_k != nullptr) {
+            const bf16* part = static_cast<const bf16*>(side ? a.partial_v : a.partial_k);
             for (int j = 0; j < a.n_routed; ++j)
               alpha = fmaf(inv[a.route_start + j * a.route_stride], __bfloat162float(part[(j * rows + row) * CL + o]), alpha);
+          }
           v[h] = alpha * inv[l];
         }
       }
@@ -690,7 +710,13 @@ int launch_mix(const wm_pool_mix_args& a, cudaStream_t stream) {
   WM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
   if (mma_path(a)) {
     const int mma_warps = a.hidden / 64;
-    const MmaLayout mma(a.sources, a.channels, a.hidden, mma_warps);
+    // the routing partials of a row travel with its sources when their rows can be bulk-copied (16-byte multiples)
+    const bool routed = a.partial_k != nullptr;
+    const size_t partial_row = static_cast<size_t>(a.channels) * a.sources * 2;
+    bool staged = routed && partial_row % 16 == 0 && reinterpret_cast<uintptr_t>(a.partial_k) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(a.partial_v) % 16 == 0;
+    if (staged && MmaLayout(a.sources, a.channels, a.hidden, mma_warps, a.n_routed).total > kSharedLimit) staged = false;
+    const MmaLayout mma(a.sources, a.channels, a.hidden, mma_warps, staged ? a.n_routed : 0);
     static std::atomic<bool> configured[kMaxDevices];
     if (device < 0 || device >= kMaxDevices || !configured[device].load(std::memory_order_acquire)) {
       WM_CUDA(cudaFuncSetAttribute(pool_mix_mma_kernel<0, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSharedLimit)));
@@ -702,9 +728,9 @@ int launch_mix(const wm_pool_mix_args& a, cudaStream_t stream) {
     if (got != WM_OK) return got;
     const unsigned blocks_mma = static_cast<unsigned>(rows < sms ? rows : sms);
     if (a.sources == 25 && a.channels == 8 && a.hidden == 1024)  // the pool of the 24-layer model
-      pool_mix_mma_kernel<25, 8, 1024><<<blocks_mma, mma_warps * 32, mma.total, stream>>>(a, rows, status);
+      pool_mix_mma_kernel<25, 8, 1024><<<blocks_mma, mma_warps * 32, mma.total, stream>>>(a, rows, status, staged ? 1 : 0);
     else
-      pool_mix_mma_kernel<0, 0, 0><<<blocks_mma, mma_warps * 32, mma.total, stream>>>(a, rows, status);
+      pool_mix_mma_kernel<0, 0, 0><<<blocks_mma, mma_warps * 32, mma.total, stream>>>(a, rows, status, staged ? 1 : 0);
     count_launch();
     return cuda_check(cudaGetLastError(), "pool_mix_mma_kernel");
   }
