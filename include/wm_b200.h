@@ -206,7 +206,8 @@ typedef struct wm_qprep_args {
  * pre_mix[s_j])^T, one plain GEMM per routed source that the caller runs on the raw layer stack; n_routed = 0 (or
  * NULL partials) gives the static router whose logits are the bias alone.  `stacked` is (batch, tokens, sources,
  * hidden) with element strides for (batch, token, source) and unit stride in hidden; the partials are
- * (n_routed, batch*tokens, channels*sources) contiguous; the results are (channels, batch*tokens, hidden)
+ * (n_routed, batch*tokens, channels*sources) with partial_row_stride elements between rows (so that one GEMM
+ * against the K- and V-side router weights side by side can produce both, partial_v = partial_k + channels*sources); the results are (channels, batch*tokens, hidden)
  * contiguous, the A operand of the per-channel projection.  stacked, partials and results share `dtype`; gains,
  * biases are float32.  hidden must be a multiple of 128 and at most 2048; sources at most 32. */
 typedef struct wm_pool_mix_args {
@@ -226,6 +227,7 @@ typedef struct wm_pool_mix_args {
   int32_t batch, tokens, sources, channels, hidden;
   int32_t route_start, route_stride, n_routed;
   float source_eps, mix_eps;
+  int64_t partial_row_stride; /* elements between consecutive rows of a partial; 0 stands for channels*sources */
 } wm_pool_mix_args;
 
 /* Publication of projected channels into the KV pool (modules/kv_pool.py:147-176 of the reference: the permute of

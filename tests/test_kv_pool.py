@@ -188,8 +188,9 @@ def test_mix_entry_point_applies_the_post_mix_gain_when_given(case, dtype):
     keep = []
     if pool.router_dynamic:
         flat = x[:, :, pool.source_start :: pool.router_layer_stride].reshape(rows, pool.num_sources, hidden).transpose(0, 1)
-        keep = [torch.bmm(flat, pool._route_k), torch.bmm(flat, pool._route_v)]
-        a.partial_k, a.partial_v = keep[0].data_ptr(), keep[1].data_ptr()
+        both = torch.bmm(flat, pool._route)  # K side and V side in every row
+        keep = [both[..., : k * layers].contiguous(), both[..., k * layers :].contiguous()]
+        a.partial_k, a.partial_v = keep[0].data_ptr(), keep[1].data_ptr()  # separate tensors: the default row stride
         a.route_start, a.route_stride, a.n_routed = pool.source_start, pool.router_layer_stride, pool.num_sources
     a.gain_k, a.gain_v = pool.k_gain.data_ptr(), pool.v_gain.data_ptr()
     a.mixed_k, a.mixed_v = mixed[0].data_ptr(), mixed[1].data_ptr()

@@ -181,6 +181,7 @@ class PoolMixArgs(ctypes.Structure):
         ("n_routed", ctypes.c_int32),
         ("source_eps", ctypes.c_float),
         ("mix_eps", ctypes.c_float),
+        ("partial_row_stride", ctypes.c_int64),
     ]
 
 

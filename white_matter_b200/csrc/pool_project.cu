@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(512) pool_mix_kernel(const wm_pool_mix_args a,
   const int lane = tid & 31, warp = tid >> 5, warps = group_threads >> 5;
   const int col = tid * 4;
   const int CL = C * L;
+  const long long PS = a.partial_row_stride ? a.partial_row_stride : CL;  // elements between rows of a partial
   const int Cpad = (C + kChannelsPerPass - 1) / kChannelsPerPass * kChannelsPerPass;
   const MixLayout lay(warps, L, Cpad);
   const size_t staged_bytes = kStaged ? (static_cast<size_t>(2) * (L + C) * Dm * sizeof(T) + 15) / 16 * 16 : 0;
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(512) pool_mix_kernel(const wm_pool_mix_args a,
       const T* part = static_cast<const T*>(side ? a.partial_v : a.partial_k);
       if (part != nullptr)
         for (int j = 0; j < a.n_routed; ++j)
-          alpha = fmaf(inv[a.route_start + j * a.route_stride], to_float(part[(j * rows + row) * CL + o]), alpha);
+          alpha = fmaf(inv[a.route_start + j * a.route_stride], to_float(part[(j * rows + row) * PS + o]), alpha);
       coef[(side * L + l) * Cpad + c] = alpha * inv[l];
     }
     group_barrier(group, group_threads);
@@ -316,6 +317,7 @@ __global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   const int g = lane >> 2, q = lane & 3;
   const int CL = C * L;
+  const long long PS = a.partial_row_stride ? a.partial_row_stride : CL;  // elements between rows of a partial
   const int Cpad = (C + kChannelsPerPass - 1) / kChannelsPerPass * kChannelsPerPass;
   const MmaLayout lay(L, C, Dm, warps, staged_partials ? a.n_routed : 0);
   const int pitch = lay.pitch;
@@ -377,7 +379,7 @@ __global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_
       unsigned char* room = part_rooms + (turn & 1) * part_room;
       for (int i = lane; i < 2 * a.n_routed; i += 32) {
         const int side = i / a.n_routed, j = i - side * a.n_routed;
-        const bf16* src = static_cast<const bf16*>(side ? a.partial_v : a.partial_k) + (j * rows + row) * CL;
+        const bf16* src = static_cast<const bf16*>(side ? a.partial_v : a.partial_k) + (j * rows + row) * PS;
         bulk_load(room + static_cast<size_t>(i) * CL * 2, src, CL * 2, bar);
       }
     }
@@ -427,7 +429,7 @@ __global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_
         for (int i = tid - 32; i >= 0 && i < 2 * a.n_routed * lines; i += blockDim.x - 32) {
           const int side = i / (a.n_routed * lines), rem = i - side * a.n_routed * lines;
           const int j = rem / lines, line = rem - j * lines;
-          const char* p = static_cast<const char*>(side ? a.partial_v : a.partial_k) + ((j * rows + next) * CL) * 2 + line * 128;
+          const char* p = static_cast<const char*>(side ? a.partial_v : a.partial_k) + ((j * rows + next) * PS) * 2 + line * 128;
           asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
         }
       }
@@ -461,7 +463,7 @@ __global__ void __launch_bounds__(512, 1) pool_mix_mma_kernel(const wm_pool_mix_
           } else if (a.partial_k != nullptr) {
             const bf16* part = static_cast<const bf16*>(side ? a.partial_v : a.partial_k);
             for (int j = 0; j < a.n_routed; ++j)
-              alpha = fmaf(inv[a.route_start + j * a.route_stride], __bfloat162float(part[(j * rows + row) * CL + o]), alpha);
+              alpha = fmaf(inv[a.route_start + j * a.route_stride], __bfloat162float(part[(j * rows + row) * PS + o]), alpha);
           }
           v[h] = alpha * inv[l];
         }
@@ -713,8 +715,8 @@ int launch_mix(const wm_pool_mix_args& a, cudaStream_t stream) {
     // the routing partials of a row travel with its sources when their rows can be bulk-copied (16-byte multiples)
     const bool routed = a.partial_k != nullptr;
     const size_t partial_row = static_cast<size_t>(a.channels) * a.sources * 2;
-    bool staged = routed && partial_row % 16 == 0 && reinterpret_cast<uintptr_t>(a.partial_k) % 16 == 0 &&
-                  reinterpret_cast<uintptr_t>(a.partial_v) % 16 == 0;
+    bool staged = routed && partial_row % 16 == 0 && (a.partial_row_stride * 2) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(a.partial_k) % 16 == 0 && reinterpret_cast<uintptr_t>(a.partial_v) % 16 == 0;
     if (staged && MmaLayout(a.sources, a.channels, a.hidden, mma_warps, a.n_routed).total > kSharedLimit) staged = false;
     const MmaLayout mma(a.sources, a.channels, a.hidden, mma_warps, staged ? a.n_routed : 0);
     static std::atomic<bool> configured[kMaxDevices];
@@ -767,6 +769,8 @@ int pool_mix_launch(const wm_pool_mix_args& a, cudaStream_t stream) {
   const bool routed = a.partial_k != nullptr || a.partial_v != nullptr;
   if (routed) {
     if (!a.partial_k || !a.partial_v) return fail(WM_EINVAL, "wm_pool_mix: partial_k and partial_v come together");
+    if (a.partial_row_stride != 0 && a.partial_row_stride < static_cast<long long>(a.channels) * a.sources)
+      return fail(WM_EINVAL, "wm_pool_mix: partial_row_stride is shorter than a row");
     if (a.n_routed < 1 || a.route_stride < 1 || a.route_start < 0 || a.route_start + (a.n_routed - 1) * a.route_stride >= a.sources)
       return fail(WM_EINVAL, "wm_pool_mix: routed sources must lie inside the stack");
   }

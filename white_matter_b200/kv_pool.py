@@ -128,8 +128,10 @@ class KVPool:
             w = weight.view(k * layers, self.num_sources, hidden) * pre_mix[routed][None]
             return w.permute(1, 2, 0).to(self.dtype).contiguous()
 
-        self._route_k = folded(self.k_router_weight, self.pre_mix_k_weight)
-        self._route_v = folded(self.v_router_weight, self.pre_mix_v_weight)
+        # K- and V-side router weights side by side: one GEMM over the routed sources yields both sides' partials
+        self._route = torch.cat(
+            (folded(self.k_router_weight, self.pre_mix_k_weight), folded(self.v_router_weight, self.pre_mix_v_weight)), dim=2
+        ).contiguous()
         # the post-mix gain scales the columns of the projection's input: folded into the projection weights
         self._proj_k = (self.k_proj_weight * self.k_gain[:, None, :]).transpose(1, 2).to(self.dtype).contiguous()
         self._proj_v = (self.v_proj_weight * self.v_gain[:, None, :]).transpose(1, 2).to(self.dtype).contiguous()
@@ -152,21 +154,22 @@ class KVPool:
         k, hidden, layers = self.num_kv_channels, self.hidden_size, self.num_layers
         rows = batch * tokens
         device = stacked.device
-        partial_k = partial_v = None
+        partial = None
         if self.router_dynamic:
             # (n, rows, Dm) view of the routed sources as they lie in the stack (callers pass rows one stride apart)
             routed = stacked[:, :, self.source_start :: self.router_layer_stride]
             flat = routed.reshape(rows, self.num_sources, hidden).transpose(0, 1)
-            partial_k = torch.bmm(flat, self._route_k)
-            partial_v = torch.bmm(flat, self._route_v)
+            partial = torch.bmm(flat, self._route)  # (n, rows, 2*k*L): K side, then V side, in every row
         mixed = torch.empty(2, k, rows, hidden, device=device, dtype=self.dtype)
         a = _native.PoolMixArgs()
         a.stacked = stacked.data_ptr()
         a.stacked_strides = _native._Strides(stacked.stride(0), stacked.stride(1), stacked.stride(2))
         a.pre_mix_k, a.pre_mix_v = self.pre_mix_k_weight.data_ptr(), self.pre_mix_v_weight.data_ptr()
         a.bias_k, a.bias_v = self.k_router_bias.data_ptr(), self.v_router_bias.data_ptr()
-        if partial_k is not None:
-            a.partial_k, a.partial_v = partial_k.data_ptr(), partial_v.data_ptr()
+        if partial is not None:
+            a.partial_k = partial.data_ptr()
+            a.partial_v = partial.data_ptr() + k * layers * partial.element_size()
+            a.partial_row_stride = 2 * k * layers
             a.route_start, a.route_stride, a.n_routed = self.source_start, self.router_layer_stride, self.num_sources
         a.mixed_k, a.mixed_v = mixed[0].data_ptr(), mixed[1].data_ptr()
         a.dtype = _native.dtype_code(self.dtype)
