@@ -235,7 +235,7 @@ typedef struct wm_pool_mix_args {
  * the copy into the pool).  `k_proj` and `v_proj` are the per-channel projections (channels, batch*tokens,
  * kv_heads*head_dim) contiguous in `in_dtype`.  Keys get rms_norm(eps) over head_dim, the channel's gain
  * k_norm_weight[c] and the rotary embedding of row rope_offset + t of cos / sin; values are moved unchanged.  Both
- * land at slot token_offset + t of head c*kv_heads + h of `k_out` / `v_out`, which are (batch, channels*kv_heads,
+ * land at slot token_offset + t * slot_stride of head c*kv_heads + h of `k_out` / `v_out`, which are (batch, channels*kv_heads,
  * capacity, head_dim) in `out_dtype` with element strides out_strides for (batch, head, slot) -- the wire format of
  * the decode cache, or a fresh (batch, channels, kv_heads, tokens, head_dim) tensor.  cos / sin are float32
  * (batch, >= rope_offset + tokens, head_dim) with element strides cs_strides for (batch, row); a batch stride of 0
@@ -254,6 +254,7 @@ typedef struct wm_pool_finish_args {
   int32_t batch, tokens, channels, kv_heads, head_dim; /* head_dim 64 or 128 */
   int32_t token_offset, rope_offset;
   float eps;
+  int32_t slot_stride; /* token t lands at slot token_offset + t * slot_stride; 0 stands for 1 */
 } wm_pool_finish_args;
 
 /* Commit of new tokens to a static KV pool (models/cache.py:43-60 of the reference: the update of a static cache

@@ -5,6 +5,7 @@ live in ``libwm_b200.so`` behind the C ABI of ``include/wm_b200.h``.
 """
 
 from .cyclic import cyclic_attention
+from .cyclic_prefill import FeedbackBlock
 from .decode_step import DecodeStepGraph, KVPoolCache, document_key_mask
 from .metadata import (
     CyclicAttentionMetadata,
@@ -30,6 +31,7 @@ __all__ = [
     "prepare_feedback_metadata",
     "mix_kv_sources",
     "mixed_pool_decode",
+    "FeedbackBlock",
     "KVPool",
     "KVPoolCache",
     "DecodeStepGraph",

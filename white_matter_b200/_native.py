@@ -208,6 +208,7 @@ class PoolFinishArgs(ctypes.Structure):
         ("token_offset", ctypes.c_int32),
         ("rope_offset", ctypes.c_int32),
         ("eps", ctypes.c_float),
+        ("slot_stride", ctypes.c_int32),
     ]
 
 
@@ -320,8 +321,11 @@ def current_stream(device: torch.device) -> int:
 def call(name: str, args, device: torch.device) -> None:
     """Invoke an entry point on the current stream of ``device``; raise on failure."""
     lib = load_library()
-    with torch.cuda.device(device):
+    if device.index is None or device.index == torch.cuda.current_device():
         status = getattr(lib, name)(ctypes.byref(args), current_stream(device))
+    else:  # the library launches on the current device: make the tensors' device current for the call
+        with torch.cuda.device(device):
+            status = getattr(lib, name)(ctypes.byref(args), current_stream(device))
     if status != 0:
         message = lib.wm_last_error().decode(errors="replace")
         raise RuntimeError(f"{name} failed ({status}): {message}")

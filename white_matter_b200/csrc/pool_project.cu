@@ -609,7 +609,7 @@ __global__ void __launch_bounds__(kFinishThreads) pool_finish_kernel(const wm_po
   const long long rows = static_cast<long long>(a.batch) * a.tokens;
   const TI* in = static_cast<const TI*>(keys ? a.k_proj : a.v_proj) + (c * rows + row) * a.kv_heads * D + 8 * sub;
   TO* out = static_cast<TO*>(keys ? a.k_out : a.v_out) + b * a.out_strides[0] +
-            static_cast<long long>(a.token_offset + t) * a.out_strides[2] + 8 * sub;
+            (a.token_offset + static_cast<long long>(t) * (a.slot_stride ? a.slot_stride : 1)) * a.out_strides[2] + 8 * sub;
   float own[8], other[8];  // factor of this lane's elements, factor of the rotation partner's
   if (keys) {
     const long long cs = b * a.cs_strides[0] + static_cast<long long>(a.rope_offset + t) * a.cs_strides[1] + 8 * sub;
@@ -794,7 +794,7 @@ int pool_finish_launch(const wm_pool_finish_args& a, cudaStream_t stream) {
   if (a.in_dtype == WM_BF16 && a.out_dtype == WM_F32) return fail(WM_EUNSUPPORTED, "wm_pool_finish: bfloat16 projections give a bfloat16 pool");
   if (a.batch < 1 || a.tokens < 1 || a.channels < 1 || a.kv_heads < 1) return fail(WM_EINVAL, "wm_pool_finish: sizes must be positive");
   if (a.head_dim != 64 && a.head_dim != 128) return fail(WM_EUNSUPPORTED, "wm_pool_finish: head_dim must be 64 or 128");
-  if (a.token_offset < 0 || a.rope_offset < 0) return fail(WM_EINVAL, "wm_pool_finish: offsets must not be negative");
+  if (a.token_offset < 0 || a.rope_offset < 0 || a.slot_stride < 0) return fail(WM_EINVAL, "wm_pool_finish: offsets and the slot stride must not be negative");
   if (static_cast<long long>(a.batch) * a.channels > 65535) return fail(WM_EUNSUPPORTED, "wm_pool_finish: batch * channels above 65535");
   const int osize = a.out_dtype == WM_F32 ? 4 : 2;
   if (!aligned16(a.k_proj) || !aligned16(a.v_proj) || !aligned16(a.k_out) || !aligned16(a.v_out))

@@ -147,7 +147,7 @@ class KVPool:
         if stacked.stride(3) != 1:
             raise ValueError("the layer stack must have unit stride in the hidden dimension")
 
-    def _project_rows(self, stacked, cos, sin, keys, values, token_offset: int, rope_offset: int) -> None:
+    def _project_rows(self, stacked, cos, sin, keys, values, token_offset: int, rope_offset: int, slot_stride: int = 1) -> None:
         """Project every token of ``stacked`` (B,T,L,Dm) into slots token_offset.. of ``keys`` / ``values``
         (B, k*HKV, slots, D) views."""
         batch, tokens = stacked.shape[:2]
@@ -188,7 +188,7 @@ class KVPool:
         f.in_dtype = f.out_dtype = _native.dtype_code(self.dtype)
         f.batch, f.tokens, f.channels = batch, tokens, k
         f.kv_heads, f.head_dim = self.num_key_value_heads, self.head_dim
-        f.token_offset, f.rope_offset = token_offset, rope_offset
+        f.token_offset, f.rope_offset, f.slot_stride = token_offset, rope_offset, slot_stride
         f.eps = self.rms_norm_eps
         _native.call("wm_pool_finish", f, device)
 
@@ -214,17 +214,19 @@ class KVPool:
         values: torch.Tensor,
         *,
         token_offset: int = 0,
+        slot_stride: int = 1,
     ) -> None:
-        """Project (B,T,L,Dm) and publish the rows into slots ``token_offset .. token_offset+T`` of a pool in the
-        decode wire format: ``keys`` / ``values`` are (B, k*HKV, slots, D) with unit stride in D.  The position
-        embeddings are (B|1, T, D), row t for the token that lands in slot token_offset + t."""
+        """Project (B,T,L,Dm) and publish row t into slot ``token_offset + t * slot_stride`` of a pool in the decode
+        wire format: ``keys`` / ``values`` are (B, k*HKV, slots, D) with unit stride in D.  The position embeddings
+        are (B|1, T, D), row t for the token that lands in that slot.  A slot stride above one publishes a residue
+        group of a cyclic pass (tokens c, c+G, ...) in place."""
         self._check(stacked)
         batch, tokens = stacked.shape[:2]
         heads = self.num_kv_channels * self.num_key_value_heads
         for pool in (keys, values):
             if pool.ndim != 4 or pool.shape[0] != batch or pool.shape[1] != heads or pool.shape[3] != self.head_dim:
                 raise ValueError(f"pool tensors must be ({batch}, {heads}, slots, {self.head_dim})")
-            if pool.shape[2] < token_offset + tokens or token_offset < 0:
+            if token_offset < 0 or slot_stride < 1 or (tokens and pool.shape[2] <= token_offset + (tokens - 1) * slot_stride):
                 raise ValueError("the projected rows do not fit the pool")
             if pool.dtype != self.dtype or pool.stride(3) != 1 or pool.device != stacked.device:
                 raise ValueError("pool tensors must share the stack's device and dtype, with unit stride in head_dim")
@@ -235,7 +237,7 @@ class KVPool:
         cos, sin = self._tables(position_embeddings, batch, tokens)
         whole = batch * tokens <= self.chunk_rows and (batch == 1 or stacked.stride(0) == tokens * stacked.stride(1))
         if whole:
-            self._project_rows(stacked, cos, sin, keys, values, token_offset, 0)
+            self._project_rows(stacked, cos, sin, keys, values, token_offset, 0, slot_stride)
             return
         # one batch row at a time, so that a chunk's rows are one stride apart in the stack
         for b in range(batch):
@@ -244,7 +246,7 @@ class KVPool:
                 stop = min(tokens, start + self.chunk_rows)
                 self._project_rows(
                     stacked[b : b + 1, start:stop], cos[table], sin[table], keys[b : b + 1], values[b : b + 1],
-                    token_offset + start, start,
+                    token_offset + start * slot_stride, start, slot_stride,
                 )
 
     def project_sequence(
