@@ -688,6 +688,61 @@ def bench_mixed_decode(device, peaks, iters=5, batch=16):
     }
 
 
+def bench_cyclic_prefill(device, peaks, reps=3):
+    """Full cyclic prefill of the 24-layer model, random-initialised (weights ~ N(0, 0.02)): d_model 1024, 16 heads of
+    64, SwiGLU 3072, RoPE base 1e6, vocabulary 151936, 25 pool sources into 8 channels of 16 KV heads, no dummy token;
+    token ids uniform over the vocabulary, B=8, T=2048, 8 passes of 8 residue groups, bf16.  Embedding lookup, the
+    block's passes (linear layers and norms are library calls; query preparation, attention, pool mixing and
+    publication are this library's kernels), final norm and the last token's logits, replayed from one CUDA graph."""
+    from white_matter_b200 import FeedbackBlock
+
+    batch, tokens, hidden, layers, heads, dim, mlp, vocab, channels, passes, groups = 8, 2048, 1024, 24, 16, 64, 3072, 151936, 8, 8, 8
+    gen = torch.Generator(device=device).manual_seed(4)
+    block = FeedbackBlock(hidden, layers, heads, dim, mlp, heads, channels, rope_theta=1e6, use_dummy_token=False,
+                          router_layer_stride=2, num_passes=passes, device=device)
+    block.kv_pool.k_router_weight.normal_(0, 0.02, generator=gen)
+    block.kv_pool.v_router_weight.normal_(0, 0.02, generator=gen)
+    block.kv_pool.refresh()
+    embedding = (torch.randn(vocab, hidden, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+    final_norm = torch.ones(hidden, device=device, dtype=torch.bfloat16)
+    ids = torch.randint(0, vocab, (batch, tokens), device=device, generator=gen)
+
+    def prefill():
+        x = embedding[ids]
+        h, _ = block(x, cyclic_groups=groups)
+        last = torch.nn.functional.rms_norm(h[:, -1], (hidden,), final_norm, 1e-6)
+        return torch.nn.functional.linear(last, embedding)  # tied head, last position only
+
+    prefill()  # warm-up outside the capture: one-time attribute and symbol look-ups
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        prefill()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        logits = prefill()
+    ms = time_steps(graph.replay, reps, 1, torch.cuda.synchronize) / reps
+    t0 = time.perf_counter()
+    prefill()
+    torch.cuda.synchronize()
+    eager_ms = (time.perf_counter() - t0) * 1e3
+    rows = batch * tokens
+    linear = 2 * rows * (2 * hidden * heads * dim + 3 * hidden * mlp) * layers * passes
+    attention = 4 * dim * (tokens * (tokens - 1) // 2) * heads * batch * layers * passes
+    pool = 2 * rows * (2 * channels * hidden * heads * dim + 2 * 13 * hidden * channels * (layers + 1)) * (passes + 1)
+    flops = linear + attention + pool
+    return {
+        "workload": "full cyclic prefill, 24 layers d_model=1024 16 heads x 64, SwiGLU 3072, 25 sources -> 8 channels, "
+                    "B=8 T=2048, 8 passes x 8 groups, bf16, random-init, CUDA-graph replay",
+        "ms": ms, "value": rows / (ms * 1e-3), "unit": "prefill tokens/s", "eager_ms": eager_ms,
+        "tflops": flops / (ms * 1e-3) / 1e12, "flops": {"linear": linear, "attention_visible": attention, "pool": pool},
+        "finite": bool(torch.isfinite(logits.float()).all().item()),
+    }
+
+
 def bench_incumbents(device, iters=10):
     """The library kernels the upstream GPU backends call (src/white_matter/ops/flash_attention.py:15-36,52-103), timed
     on the same GPU as comparators: FlashAttention-2 (flash_attn package) and PyTorch's flash SDPA.  Labelled extras:
@@ -858,6 +913,7 @@ LEGS = {
     "query_prepare": lambda device, peaks, small: bench_query_prepare(device, peaks),
     "pool_projection": lambda device, peaks, small: bench_pool_projection(device, peaks),
     "mixed_decode": lambda device, peaks, small: bench_mixed_decode(device, peaks, batch=4 if small else 16),
+    "cyclic_prefill": lambda device, peaks, small: bench_cyclic_prefill(device, peaks),
 }
 
 
@@ -1022,6 +1078,8 @@ def main():
         extras["pool_projection"] = bench_pool_projection(device, peaks)
         torch.cuda.empty_cache()
         extras["mixed_decode"] = bench_mixed_decode(device, peaks)
+        torch.cuda.empty_cache()
+        extras["cyclic_prefill"] = bench_cyclic_prefill(device, peaks)
         torch.cuda.empty_cache()
         check("extras")
         if world == 1:

@@ -13,9 +13,8 @@ What runs where: the linear layers, the SwiGLU product and the RMS norms of the 
 (plain GEMMs and pointwise kernels); query norm + rotary embedding + layout (``wm_query_prepare``), the attention
 (``wm_cyclic_attn*``), the pool mixing (``wm_pool_mix``) and the publication into the strided slots of the group
 (``wm_pool_finish`` with a slot stride) are this library's kernels.  The pool is kept in the decode wire format
-(B, k*HKV, T[+1], D); channel c is a strided view of it, read in place.  The layer inputs of a group are written
-straight into the (B, Tc, L+1, Dm) stack the pool reads (each layer's residual sum lands in the next layer's slice),
-so no stacking copy is made.
+(B, k*HKV, T[+1], D); channel c is a strided view of it, read in place.  The residual sums of a layer ride in the
+epilogues of its two output GEMMs; every layer input is copied once into the (B, Tc, L+1, Dm) stack the pool reads.
 """
 
 from __future__ import annotations
@@ -131,8 +130,9 @@ class FeedbackBlock:
         k_pos = torch.cat((q_pos.new_zeros(batch, lead), q_pos), dim=1)
         return q_pos, k_pos
 
-    def _layer(self, layer: dict, hidden: torch.Tensor, out: torch.Tensor, keys, values, cos, sin, groups, residue, metadata) -> None:
-        """One decoder layer on a residue group: ``out`` receives hidden + attention + MLP (decoder_layer.py:46-69)."""
+    def _layer(self, layer: dict, hidden: torch.Tensor, keys, values, cos, sin, groups, residue, metadata) -> torch.Tensor:
+        """One decoder layer on a residue group: hidden + attention + MLP (decoder_layer.py:46-69); ``hidden`` is
+        (B, Tc, Dm) contiguous and so is the result."""
         eps = self.rms_norm_eps
         normed = F.rms_norm(hidden, (self.hidden_size,), layer["input_layernorm"], eps)
         projected = F.linear(normed, layer["q_proj"])
@@ -144,11 +144,13 @@ class FeedbackBlock:
             queries, keys, values, query_stride=groups, query_offset=residue, strict_past=not self.use_dummy_token, metadata=metadata
         )
         batch, heads, length, dim = attended.shape
-        attended = attended.transpose(1, 2).reshape(batch, length, heads * dim)  # a view of the (B,T,H,D) storage
-        after = hidden + F.linear(attended, layer["o_proj"])
+        rows = batch * length
+        attended = attended.transpose(1, 2).reshape(rows, heads * dim)  # a view of the (B,T,H,D) storage
+        # the residual sums ride in the GEMM epilogues (addmm)
+        after = torch.addmm(hidden.view(rows, self.hidden_size), attended, layer["o_proj"].t())
         normed = F.rms_norm(after, (self.hidden_size,), layer["post_attention_layernorm"], eps)
-        mlp = F.linear(F.silu(F.linear(normed, layer["gate_proj"])) * F.linear(normed, layer["up_proj"]), layer["down_proj"])
-        torch.add(after, mlp, out=out)
+        gated = F.silu(F.linear(normed, layer["gate_proj"])) * F.linear(normed, layer["up_proj"])
+        return torch.addmm(after, gated, layer["down_proj"].t()).view(batch, length, self.hidden_size)
 
     # ------------------------------------------------------------------ entry point
     @torch.no_grad()
@@ -211,16 +213,18 @@ class FeedbackBlock:
                 group = x[:, c::groups]
                 length = group.shape[1]
                 stack = torch.empty(batch, length, sources, hidden_size, device=x.device, dtype=self.dtype)
-                stack[:, :, 0].copy_(group)
+                hidden = group.contiguous()
                 cos, sin = q_cos[:, c::groups], q_sin[:, c::groups]
                 for index, layer in enumerate(self.layers):
+                    stack[:, :, index].copy_(hidden)  # the layer's input is a source of the pool
                     channel = index % k
-                    self._layer(
-                        layer, stack[:, :, index], stack[:, :, index + 1], channel_keys[channel], channel_values[channel], cos, sin,
-                        groups, c, None if metadata is None else metadata[c],
+                    hidden = self._layer(
+                        layer, hidden, channel_keys[channel], channel_values[channel], cos, sin, groups, c,
+                        None if metadata is None else metadata[c],
                     )
+                stack[:, :, self.num_layers].copy_(hidden)
                 if last:
-                    output[:, c::groups] = stack[:, :, self.num_layers]
+                    output[:, c::groups] = hidden
                 # publish after the layer sweep: later groups read these refreshed rows
                 self.kv_pool.project_into(
                     stack, (k_cos[:, c + lead :: groups], k_sin[:, c + lead :: groups]), keys, values,
