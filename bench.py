@@ -853,18 +853,31 @@ def cpu_sample(rows=B, residues=tuple(range(STRIDE)), repeats=1, dtype=torch.flo
 # --------------------------------------------------------------------------- drivers
 
 
+REFERENCE_BUDGET_S = 150.0  # wall clock the timed steps of the reference arm may take together
+
+
 def run_reference_arm(args, rank, world):
-    """The upstream algorithm on the host cores (the CPU oracle port): one step is the whole workload step, all 16
-    batch rows and all 8 residues, in whichever of fp32 and bf16 the host runs faster (the configuration is bf16;
-    the upstream portable backend evaluates bf16 tensors in bf16 on the CPU)."""
+    """The upstream algorithm on the host cores (the CPU oracle port), in whichever of fp32 and bf16 the host runs
+    faster (the configuration is bf16; the upstream portable backend evaluates bf16 tensors in bf16 on the CPU).
+    A step is the whole workload step -- all 16 batch rows, all 8 residues -- when the requested number of steps
+    fits the time budget at that size, else a bounded sample of it (fewer batch rows, then fewer residues), which
+    the line names; TFLOP/s are over the sample's own visible pairs."""
     if rank != 0:
         return
     probes = {dt: cpu_sample(dtype=dt) for dt in (torch.float32, torch.bfloat16)}
     dtype = max(probes, key=lambda dt: probes[dt][0])
+    full_seconds = probes[dtype][1]
+    per_step = REFERENCE_BUDGET_S / max(args.steps + max(args.warmup - 1, 0), 1)
+    rows, residues = B, tuple(range(STRIDE))
+    if full_seconds > per_step:
+        rows = max(1, min(B, int(B * per_step / full_seconds)))
+        if full_seconds * rows / B > per_step:  # one row is still too much: fewer residues of it (first, last, ...)
+            keep = max(1, min(STRIDE, int(STRIDE * per_step / (full_seconds / B))))
+            residues = tuple(sorted({round(i * (STRIDE - 1) / max(keep - 1, 1)) for i in range(keep)}))
     for _ in range(max(args.warmup - 1, 0)):
-        cpu_sample(dtype=dtype)
+        cpu_sample(rows=rows, residues=residues, dtype=dtype)
     t0 = time.perf_counter()
-    values = [cpu_sample(dtype=dtype) for _ in range(args.steps)]
+    values = [cpu_sample(rows=rows, residues=residues, dtype=dtype) for _ in range(args.steps)]
     wall = time.perf_counter() - t0
     tflops = statistics.median(v[0] for v in values)
     line = {
@@ -874,7 +887,8 @@ def run_reference_arm(args, rank, world):
         "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
         "config": workload_config(args.gpus, args.scaling),
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": values[0][2], "kind": "port", "sample": values[0][3],
-                         "fp32_tflops": probes[torch.float32][0], "bf16_tflops": probes[torch.bfloat16][0]},
+                         "fp32_tflops": probes[torch.float32][0], "bf16_tflops": probes[torch.bfloat16][0],
+                         "whole_step_seconds": full_seconds},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
