@@ -944,6 +944,9 @@ def main():
     parser.add_argument("--skip-extras", action="store_true", help="only the headline workload (used for profiling)")
     parser.add_argument("--leg", action="append", choices=sorted(LEGS), default=None,
                         help="run only the named secondary leg(s) and print their results (used for profiling)")
+    parser.add_argument("--skip-leg", action="append", choices=sorted(LEGS), default=[],
+                        help="leave the named secondary leg(s) out of the full run (the launch-list capture leaves out the "
+                             "full-model prefill, tens of thousands of launches)")
     parser.add_argument("--small", action="store_true", help="with --leg mixed_decode: 4 batch rows instead of 16")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -1084,16 +1087,15 @@ def main():
     extras = {}
     if not args.skip_extras:
         torch.cuda.empty_cache()
-        extras["decode"], extras["prefill128"] = bench_decode(device, peaks)
-        extras["jacobi"] = bench_jacobi(device, peaks)
-        extras["mixing"] = bench_mixing(device, peaks)
-        extras["query_prepare"] = bench_query_prepare(device, peaks)
-        torch.cuda.empty_cache()
-        extras["pool_projection"] = bench_pool_projection(device, peaks)
-        torch.cuda.empty_cache()
-        extras["mixed_decode"] = bench_mixed_decode(device, peaks)
-        torch.cuda.empty_cache()
-        extras["cyclic_prefill"] = bench_cyclic_prefill(device, peaks)
+        for name in ("decode", "jacobi", "mixing", "query_prepare", "pool_projection", "mixed_decode", "cyclic_prefill"):
+            if name in args.skip_leg:
+                continue
+            torch.cuda.empty_cache()
+            result = LEGS[name](device, peaks, False)
+            if name == "decode":
+                extras.update(result)  # decode and the cached-prefix prefill over the same pool
+            else:
+                extras[name] = result
         torch.cuda.empty_cache()
         check("extras")
         if world == 1:
