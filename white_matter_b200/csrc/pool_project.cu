@@ -2,12 +2,13 @@
 //
 // pool_mix: for one token row, the `sources` layer inputs are normalised, gained, mixed into `channels` vectors
 // per side (K, V) with signed routing logits, normalised again and gained -- everything the pool does between the
-// layer stack and the projection GEMMs, in one pass: the row's sources are read from HBM once into registers (four
-// adjacent columns of every source per thread), the source norms and the routing logits are formed in shared
-// memory, and the 2*channels mixtures leave as the rows of the GEMM's A operand.  Algorithmic bytes per token row:
-// sources*hidden*sizeof(T) read + 2*channels*hidden*sizeof(T) written (+ the routing partials when the router is
-// dynamic); bound by HBM bandwidth, with 2*sources*channels FMAs per loaded element as the second limit, which is
-// why the mixing runs on the packed two-wide FP32 FMA.
+// layer stack and the projection GEMMs, in one pass: the row's sources are read from HBM once, the source norms and
+// the routing coefficients are formed in shared memory, and the 2*channels mixtures leave as the rows of the GEMM's
+// A operand.  Algorithmic bytes per token row: sources*hidden*sizeof(T) read + 2*channels*hidden*sizeof(T) written
+// (+ the routing partials when the router is dynamic).  Two kernels: BF16 stacks of width <= 1024 mix on the
+// warp-level tensor-core instruction (further down); FP32 stacks and other widths keep the sources in registers and
+// mix on the packed two-wide FP32 FMA (2*sources*channels FMAs per loaded element, which bound that kernel far
+// below HBM bandwidth).
 //
 // pool_finish: the projected channels get the per-channel key norm, the rotary embedding and the move into the
 // pool's (batch, channel*head, slot, dim) layout; values only move.  One read and one write of K and V.
@@ -231,12 +232,12 @@ __global__ void __launch_bounds__(512) pool_mix_kernel(const wm_pool_mix_args a,
 // with every row, so it cannot share an operand tile across rows the way tcgen05 wants; it is small enough for the
 // warp-level tensor-core instruction instead (mma.sync m16n8k16, BF16 in, FP32 out): sixteen columns of the row are
 // the M side, eight channels the N side, the sources the contraction (two steps of 16), and every warp sweeps 64
-// columns of the row as four such tiles per side.  Against the FP32 kernel above this removes the 2*channels FMAs per loaded element from
-// the FP32 pipe, which bounded that kernel at a sixth of HBM bandwidth.
+// columns of the row as four such tiles per side.  Against the FP32 kernel above this removes the 2*channels FMAs
+// per loaded element from the FP32 pipe, which bounded that kernel at a sixth of HBM bandwidth.
 //
-// A block of hidden/64 warps stays resident (one per SM) and walks over the rows.  The four gain tables live in
-// shared memory in BF16; the next row's sources arrive by bulk copies (cp.async.bulk, completion on an mbarrier)
-// while the current row is mixed.  Rows of the tables and of the source tile are 16 bytes longer than the data so
+// A block of hidden/64 warps stays resident (one per SM) and walks over the rows.  The gain tables live in shared
+// memory in BF16; the next row's sources, and the rows of the routing partials that belong to it, arrive by bulk
+// copies (cp.async.bulk, completion on an mbarrier) while the current row is mixed.  Rows of the tables and of the source tile are 16 bytes longer than the data so
 // that the four source rows a quarter-warp reads at once fall into different banks.
 //
 // Thread (g = lane/4, q = lane%4) of warp w holds, as the A fragments want them, columns 64w+8g .. +8 of the eight
