@@ -743,6 +743,32 @@ def bench_cyclic_prefill(device, peaks, reps=3):
     }
 
 
+def bench_head_dim_128(device, peaks, iters=10):
+    """Heads of 128 on the tensor-core forward: the training configuration's call shape (B=16 H=16 K=2048 Q=256, stride
+    8, residue 7) with head_dim 128, against the SIMT family that served this head size before."""
+    from white_matter_b200 import cyclic_attention
+
+    dim = 128
+    gen = torch.Generator(device=device).manual_seed(8)
+    q = torch.randn(B, H, T // STRIDE, dim, device=device, generator=gen).to(torch.bfloat16)
+    k, v = (torch.randn(B, H, T, dim, device=device, generator=gen).to(torch.bfloat16) for _ in range(2))
+    residue = STRIDE - 1
+    pairs = sum(residue + STRIDE * i for i in range(T // STRIDE)) * B * H  # strict past: key slots below the query's
+    timed = {}
+    with torch.no_grad():
+        for name, backend in (("tcgen05", "sm100"), ("simt", "sm100_simt")):
+            call = lambda: cyclic_attention(q, k, v, query_stride=STRIDE, query_offset=residue, strict_past=True, backend=backend)
+            n = iters if name == "tcgen05" else 3
+            timed[name] = time_steps(call, n, 2, torch.cuda.synchronize) / n
+    tf = 4 * dim * pairs / (timed["tcgen05"] * 1e-3) / 1e12
+    return {
+        "workload": "cyclic_attention forward B=16 H=16 K=2048 Q=256 stride 8 residue 7, head_dim 128, bf16",
+        "ms": timed["tcgen05"], "value": tf, "unit": "TFLOP/s", "simt_ms": timed["simt"],
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_kind": "bf16_tflops (kernel timed alone)"},
+    }
+
+
 def bench_incumbents(device, iters=10):
     """The library kernels the upstream GPU backends call (src/white_matter/ops/flash_attention.py:15-36,52-103), timed
     on the same GPU as comparators: FlashAttention-2 (flash_attn package) and PyTorch's flash SDPA.  Labelled extras:
@@ -928,6 +954,7 @@ LEGS = {
     "pool_projection": lambda device, peaks, small: bench_pool_projection(device, peaks),
     "mixed_decode": lambda device, peaks, small: bench_mixed_decode(device, peaks, batch=4 if small else 16),
     "cyclic_prefill": lambda device, peaks, small: bench_cyclic_prefill(device, peaks),
+    "head_dim_128": lambda device, peaks, small: bench_head_dim_128(device, peaks),
 }
 
 
@@ -1087,7 +1114,7 @@ def main():
     extras = {}
     if not args.skip_extras:
         torch.cuda.empty_cache()
-        for name in ("decode", "jacobi", "mixing", "query_prepare", "pool_projection", "mixed_decode", "cyclic_prefill"):
+        for name in ("decode", "jacobi", "mixing", "query_prepare", "pool_projection", "mixed_decode", "cyclic_prefill", "head_dim_128"):
             if name in args.skip_leg:
                 continue
             torch.cuda.empty_cache()

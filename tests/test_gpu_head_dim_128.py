@@ -1,0 +1,88 @@
+"""Head size 128 on the tensor-core forward (the gradient kernels of that size are the SIMT family's)."""
+
+import pytest
+import torch
+
+from helpers import BF16_TOL, assert_parity, geometric_documents
+from oracle import attention_oracle as oracle
+from white_matter_b200 import (
+    _native,
+    cyclic_attention,
+    prepare_feedback_metadata,
+    prepare_strict_causal_metadata,
+    strict_causal_attention,
+)
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not torch.cuda.is_available(), reason="requires CUDA")]
+D = 128
+
+
+@pytest.mark.parametrize("documents", [False, True])
+@pytest.mark.parametrize("stride,residue,length", [(8, 3, 1100), (4, 0, 520), (1, 0, 300)])
+def test_cyclic_forward(stride, residue, length, documents):
+    torch.manual_seed(5)
+    B, H, HKV = 2, 4, 2
+    queries = len(range(residue, length, stride))
+    q = torch.randn(B, H, queries, D).bfloat16()
+    k, v = (torch.randn(B, HKV, length, D).bfloat16() for _ in range(2))
+    metadata = None
+    if documents:
+        docs = geometric_documents(B, length, 200, seed=3)
+        metadata = prepare_feedback_metadata(docs, [torch.arange(r, length, stride) for r in range(stride)], length, use_dummy_token=False)[residue]
+    args = dict(query_stride=stride, query_offset=residue, strict_past=True)
+    with torch.no_grad():
+        dev_md = None if metadata is None else tuple(t.cuda() for t in metadata)
+        out = cyclic_attention(q.cuda(), k.cuda(), v.cuda(), metadata=dev_md, backend="sm100_tcgen05", **args)
+        simt = cyclic_attention(q.cuda(), k.cuda(), v.cuda(), metadata=dev_md, backend="sm100_simt", **args)
+    assert _native.device_status(True) == 0
+    exp = oracle.cyclic_attention_oracle(q.double(), k.double(), v.double(), metadata=metadata, **args)
+    assert_parity(out.float(), exp, what="tcgen05 forward, head 128", **BF16_TOL)
+    assert_parity(out.float(), simt.float(), what="tcgen05 vs simt", **BF16_TOL)
+
+
+@pytest.mark.parametrize("masked", [False, True])
+@pytest.mark.parametrize("length", [128, 70])
+def test_cached_prefix_prefill_with_nan_capacity(length, masked):
+    torch.manual_seed(6)
+    B, H, HKV, N = 3, 4, 4, 900
+    lengths = torch.tensor([880, 400, 129])
+    starts = (lengths - length).clamp_min(0)
+    q = torch.randn(B, H, length, D).bfloat16()
+    k, v = (torch.randn(B, HKV, N, D).bfloat16() for _ in range(2))
+    key_mask = None
+    if masked:
+        key_mask = torch.rand(B, N) > 0.3
+    kn, vn = k.clone(), v.clone()
+    for b in range(B):
+        kn[b, :, int(lengths[b]):] = float("nan")
+        vn[b, :, int(lengths[b]):] = float("nan")
+        if masked:
+            kn[b][:, ~key_mask[b]] = float("nan")
+            vn[b][:, ~key_mask[b]] = float("nan")
+    with torch.no_grad():
+        out = strict_causal_attention(
+            q.cuda(), kn.cuda(), vn.cuda(), query_start=starts.cuda(), kv_lengths=lengths.cuda(),
+            key_mask=None if key_mask is None else key_mask.cuda(), backend="sm100_tcgen05",
+        )
+    assert torch.isfinite(out).all()
+    exp = oracle.strict_causal_oracle(q.double(), k.double(), v.double(), query_start=starts, kv_lengths=lengths, key_mask=key_mask)
+    assert_parity(out.float(), exp, what="prefill, head 128", **BF16_TOL)
+
+
+def test_jacobi_with_documents_and_gradients_through_both_families():
+    """Forward on the tensor cores, gradients on the SIMT kernels (the default backend's choice at this head size)."""
+    torch.manual_seed(7)
+    B, H, T = 2, 2, 384
+    docs = geometric_documents(B, T, 120, seed=4)
+    q, probe = (torch.randn(B, H, T, D).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, H, T, D).bfloat16() for _ in range(2))
+    schedule = prepare_strict_causal_metadata(docs.cuda(), T)
+    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = strict_causal_attention(qq, kk, vv, metadata=schedule)
+    grads = torch.autograd.grad(out, (qq, kk, vv), probe.transpose(1, 2).cuda())
+    qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
+    exp = oracle.strict_causal_oracle(qo, ko, vo, metadata=prepare_strict_causal_metadata(docs, T))
+    exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.transpose(1, 2).double())
+    assert_parity(out.float(), exp, what="out", **BF16_TOL)
+    for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
+        assert_parity(g.float(), e, what=name, **BF16_TOL)

@@ -127,11 +127,13 @@ int allow_shared_memory(Kernel kernel, std::atomic<bool> (&done)[kMaxDevices], s
   return WM_OK;
 }
 
-// (batch, heads, tokens, 64) bf16 tensor with element strides s[0..2]; boxes of `rows` tokens x 64.
-int make_map(CUtensorMap* map, const void* base, int batch, int heads, int tokens, const int64_t* s, int rows) {
+// (batch, heads, tokens, head_dim) bf16 tensor with element strides s[0..2]; boxes of `rows` tokens x 64 columns
+// (one 128-byte swizzle row per token: a head of 128 travels as two boxes).
+int make_map(CUtensorMap* map, const void* base, int batch, int heads, int tokens, const int64_t* s, int rows,
+             int head_dim = kHeadDim) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(WM_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(tokens),
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(tokens),
                         static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(s[2]) * 2, static_cast<cuuint64_t>(s[1]) * 2,
                            static_cast<cuuint64_t>(s[0]) * 2};
@@ -334,7 +336,7 @@ int next_epoch() {
 }
 
 bool tc_fwd_supported(const wm_attn_args& a) {
-  if (a.dtype != WM_BF16 || a.head_dim != kHeadDim) return false;
+  if (a.dtype != WM_BF16 || (a.head_dim != 64 && a.head_dim != 128)) return false;  // the forward takes either
   if (a.mask == WM_MASK_PACKED) return false;
   if (!tma_ok(a.q, a.q_strides, a.batch, a.q_heads, a.q_len)) return false;
   if (!tma_ok(a.k, a.k_strides, a.batch, a.kv_heads, a.k_len)) return false;
@@ -345,22 +347,27 @@ bool tc_fwd_supported(const wm_attn_args& a) {
   return true;
 }
 
-int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
+template <int D>
+int launch_fwd(const wm_attn_args& a, cudaStream_t stream) {
   CUtensorMap map_q, map_k, map_v;
-  int status = make_map(&map_q, a.q, a.batch, a.q_heads, a.q_len, a.q_strides, kTileM);
+  int status = make_map(&map_q, a.q, a.batch, a.q_heads, a.q_len, a.q_strides, kTileM, D);
   if (status != WM_OK) return status;
-  status = make_map(&map_k, a.k, a.batch, a.kv_heads, a.k_len, a.k_strides, kTileN);
+  status = make_map(&map_k, a.k, a.batch, a.kv_heads, a.k_len, a.k_strides, kTileN, D);
   if (status != WM_OK) return status;
-  status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN);
+  status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN, D);
   if (status != WM_OK) return status;
   dim3 grid(a.q_heads, a.batch, (a.q_len + kTileM - 1) / kTileM);
-  const size_t smem = sizeof(FwdShared) + 1024;
+  const size_t smem = sizeof(FwdShared<D>) + 1024;
   static std::atomic<bool> configured[kMaxDevices];
-  status = allow_shared_memory(attn_fwd_tc_kernel, configured, smem);
+  status = allow_shared_memory(attn_fwd_tc_kernel<D>, configured, smem);
   if (status != WM_OK) return status;
-  attn_fwd_tc_kernel<<<grid, kFwdThreads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
+  attn_fwd_tc_kernel<D><<<grid, kFwdThreads, smem, stream>>>(map_q, map_k, map_v, a, next_epoch());
   count_launch();
   return cuda_check(cudaGetLastError(), "attn_fwd_tc_kernel");
+}
+
+int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
+  return a.head_dim == 128 ? launch_fwd<128>(a, stream) : launch_fwd<64>(a, stream);
 }
 
 // Arms the trace for the launch after the next `arm_after` launches (negative: disarm) and fetches what was
@@ -412,7 +419,8 @@ int tc_device_status(bool reset) {
 }
 
 bool tc_bwd_supported(const wm_attn_args& a) {
-  if (!tc_fwd_supported(a) || a.key_mask != nullptr) return false;  // the gradient kernels take no key mask
+  // the gradient kernels take no key mask and heads of 64 only
+  if (!tc_fwd_supported(a) || a.key_mask != nullptr || a.head_dim != kHeadDim) return false;
   if (a.dout == nullptr) return true;  // shape query before the tensors exist
   if (!tma_ok(a.dout, a.dout_strides, a.batch, a.q_heads, a.q_len)) return false;
   if (!tma_ok(a.dk, a.dk_strides, a.batch, a.kv_heads, a.k_len)) return false;

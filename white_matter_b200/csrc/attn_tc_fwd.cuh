@@ -17,25 +17,45 @@
 constexpr int kFwdThreads = 352;
 constexpr int kFwdSoftmax = 256;
 constexpr int kFwdGroup = 128;      // threads of one softmax group
-constexpr int kScoreBuffers = 3;    // S buffers in TMEM: columns [0,384)
-constexpr uint32_t kOutCol = kScoreBuffers * kTileN;  // two output accumulators of 64 columns: [384,512)
+constexpr uint32_t kSubBytes = kTileN * 64 * 2;  // a tile travels as 64-column sub-tiles of 16 KB (one 128-byte swizzle row per token)
+
+// What depends on the head size D (64 or 128).  The K/V ring and the score buffers share their depth: three for
+// D = 64; two for D = 128, where a tile is twice as large and the two output accumulators take 256 of the 512 TMEM
+// columns (S0, S1 [0,256), O0 [256,384), O1 [384,512)).
+template <int D>
+struct FwdCfg {
+  static constexpr int kRing = D == 64 ? 3 : 2;
+  static constexpr int kSub = D / 64;
+  static constexpr uint32_t kBytes = kTileN * D * 2;
+  static constexpr uint32_t kOut = kRing * kTileN;
+};
+#define WM_FWD_CONSTANTS(D)                                   \
+  constexpr int kStages = FwdCfg<D>::kRing;                   \
+  constexpr int kScoreBuffers = FwdCfg<D>::kRing;             \
+  constexpr uint32_t kTileBytes = FwdCfg<D>::kBytes;          \
+  constexpr uint32_t kOutCol = FwdCfg<D>::kOut;               \
+  constexpr int kSub = FwdCfg<D>::kSub;                       \
+  (void)kStages, (void)kScoreBuffers, (void)kTileBytes, (void)kOutCol, (void)kSub
 
 // ------------------------------------------------------------------ producer (one lane of the producer warp)
-template <class Shared>
+template <int D, class Shared>
 __device__ __forceinline__ void producer_role(Shared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
                                               const CUtensorMap* map_v, const TileWalk& w, int q0, int head,
                                               int kv_head, int batch) {
+  WM_FWD_CONSTANTS(D);
   // K tiles are released by the score product, two tiles ahead of the PV product that releases V tiles: the K
   // loads run ahead of the V loads by the same distance so that a late V release never delays a score product
   auto load_k = [&](int n) -> bool {
     const int s = n % kStages;
     if (!wait_or_abort(sm, &sm.s_full[s], ((n / kStages) & 1) ^ 1, 11)) return false;  // score product n-3 has read the stage
     ptx::mbar_expect_tx(&sm.k_full[s], kTileBytes);
-    ptx::tma_load_4d(sm.k[s], map_k, &sm.k_full[s], 0, tile_first_key(n, w.first_tile, w.dummy_tile), kv_head, batch);
+#pragma unroll
+    for (int h = 0; h < kSub; ++h)
+      ptx::tma_load_4d(sm.k[s] + h * kSubBytes, map_k, &sm.k_full[s], 64 * h, tile_first_key(n, w.first_tile, w.dummy_tile), kv_head, batch);
     trace_event(sm, 100 + n);
     return true;
   };
-  constexpr int kAhead = 2;
+  constexpr int kAhead = kStages - 1;
   for (int n = 0; n < kAhead && n < w.n_tiles; ++n)
     if (!load_k(n)) return;
   for (int n = 0; n < w.n_tiles; ++n) {
@@ -43,7 +63,9 @@ __device__ __forceinline__ void producer_role(Shared& sm, const CUtensorMap* map
     const int s = n % kStages;
     if (!wait_or_abort(sm, &sm.pv_done[s], ((n / kStages) & 1) ^ 1, 12)) return;  // PV product n-3 has read the stage
     ptx::mbar_expect_tx(&sm.v_full[s], kTileBytes);
-    ptx::tma_load_4d(sm.v[s], map_v, &sm.v_full[s], 0, tile_first_key(n, w.first_tile, w.dummy_tile), kv_head, batch);
+#pragma unroll
+    for (int h = 0; h < kSub; ++h)
+      ptx::tma_load_4d(sm.v[s] + h * kSubBytes, map_v, &sm.v_full[s], 64 * h, tile_first_key(n, w.first_tile, w.dummy_tile), kv_head, batch);
     trace_event(sm, 200 + n);
   }
 }
@@ -52,8 +74,9 @@ __device__ __forceinline__ void producer_role(Shared& sm, const CUtensorMap* map
 // The tensor pipe accepts the next instruction only when it has started the previous one, so a thread that issues
 // is busy for as long as its products run.  Two threads issue: one the score products, as far ahead as the three
 // score buffers allow, one the PV products; either does its waiting while the other feeds the pipe.
-template <class Shared>
+template <int D, class Shared>
 __device__ __forceinline__ void score_mma_role(Shared& sm, uint32_t tmem, const TileWalk& w) {
+  WM_FWD_CONSTANTS(D);
   if (!wait_or_abort(sm, &sm.q_full, 0, 20)) return;
   constexpr uint32_t idesc = ptx::make_idesc_bf16(kTileM, kTileN, 0, 0);
   const uint32_t a_base = ptx::smem_u32(sm.q);
@@ -67,19 +90,21 @@ __device__ __forceinline__ void score_mma_role(Shared& sm, uint32_t tmem, const 
     const uint32_t b_base = ptx::smem_u32(sm.k[s]);
     const uint32_t d = tmem + static_cast<uint32_t>(s) * kTileN;
 #pragma unroll
-    for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-      // 16 elements of head_dim per instruction: 32 bytes inside the 128-byte swizzle row
-      ptx::mma_bf16_ss(d, ptx::make_smem_desc_sw128(a_base + kk * 32, 16, 1024),
-                       ptx::make_smem_desc_sw128(b_base + kk * 32, 16, 1024), idesc, kk > 0);
+    for (int kk = 0; kk < D / 16; ++kk) {
+      // 16 elements of head_dim per instruction: 32 bytes inside the 128-byte swizzle row of the element's sub-tile
+      const uint32_t at = (kk >> 2) * kSubBytes + (kk & 3) * 32;
+      ptx::mma_bf16_ss(d, ptx::make_smem_desc_sw128(a_base + at, 16, 1024), ptx::make_smem_desc_sw128(b_base + at, 16, 1024), idesc,
+                       kk > 0);
     }
     ptx::mma_commit(&sm.s_full[s]);
     trace_event(sm, 400 + n);
   }
 }
 
-template <class Shared>
+template <int D, class Shared>
 __device__ __forceinline__ void value_mma_role(Shared& sm, uint32_t tmem, const TileWalk& w) {
-  constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);
+  WM_FWD_CONSTANTS(D);
+  constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(kTileM, 64, 0, 1);  // one 64-column half of the output at a time
   for (int n = 0; n < w.n_tiles; ++n) {
     const int b = n & 1;
     const int s = n % kStages;
@@ -89,14 +114,17 @@ __device__ __forceinline__ void value_mma_role(Shared& sm, uint32_t tmem, const 
     if (!wait_or_abort(sm, &sm.v_full[s], (n / kStages) & 1, 23)) return;
     ptx::tc_fence_after();
     trace_event(sm, 1200 + n);
-    const uint32_t o_tmem = tmem + kOutCol + static_cast<uint32_t>(b) * kHeadDim;
+    const uint32_t o_tmem = tmem + kOutCol + static_cast<uint32_t>(b) * D;
     const uint32_t p_tmem = tmem + static_cast<uint32_t>(s) * kTileN;  // P overwrote the first 64 columns of S
     const uint32_t v_base = ptx::smem_u32(sm.v[s]);
 #pragma unroll
-    for (int kk = 0; kk < kTileN / 16; ++kk) {
-      // A = P from tensor memory, 16 keys = 8 columns; B = V: head_dim contiguous (MN-major), 16 keys = 2048 bytes
-      const uint64_t b_desc = ptx::make_smem_desc_sw128(v_base + kk * 2048, 1024, 1024);
-      ptx::mma_bf16_ts(o_tmem, p_tmem + kk * 8, b_desc, idesc_pv, (n > 1) || (kk > 0));
+    for (int h = 0; h < kSub; ++h) {
+#pragma unroll
+      for (int kk = 0; kk < kTileN / 16; ++kk) {
+        // A = P from tensor memory, 16 keys = 8 columns; B = V: head_dim contiguous (MN-major), 16 keys = 2048 bytes
+        const uint64_t b_desc = ptx::make_smem_desc_sw128(v_base + h * kSubBytes + kk * 2048, 1024, 1024);
+        ptx::mma_bf16_ts(o_tmem + h * 64, p_tmem + kk * 8, b_desc, idesc_pv, (n > 1) || (kk > 0));
+      }
     }
     ptx::mma_commit(&sm.pv_done[s]);
     trace_event(sm, 500 + n);
@@ -104,14 +132,15 @@ __device__ __forceinline__ void value_mma_role(Shared& sm, uint32_t tmem, const 
 }
 
 
+template <int D>
 struct FwdShared {
-  unsigned char q[kTileBytes];
-  unsigned char k[kStages][kTileBytes];
-  unsigned char v[kStages][kTileBytes];
+  unsigned char q[FwdCfg<D>::kBytes];
+  unsigned char k[FwdCfg<D>::kRing][FwdCfg<D>::kBytes];
+  unsigned char v[FwdCfg<D>::kRing][FwdCfg<D>::kBytes];
   uint64_t q_full;
   // s_full[i] and pv_done[i] also release K and V stage i (score buffers and stages share the ring size)
-  uint64_t k_full[kStages], v_full[kStages];
-  uint64_t s_full[kScoreBuffers], pv_done[kStages], p_full[2], p_seen[2], docs_full[2], sum_full;
+  uint64_t k_full[FwdCfg<D>::kRing], v_full[FwdCfg<D>::kRing];
+  uint64_t s_full[FwdCfg<D>::kRing], pv_done[FwdCfg<D>::kRing], p_full[2], p_seen[2], docs_full[2], sum_full;
   int key_seg[2][2][kTileN];  // [group][tile of the group & 1]
   int key_end[2][2][kTileN];
   int tile_summary[2][2][4][3];
@@ -129,8 +158,10 @@ struct FwdShared {
 // drift out of phase, one in its exponentials while the other reads scores.  The two partial results are merged
 // once, in the epilogue.  A tile is read from TMEM twice (row maximum, then exponentials) in pieces of 64 columns
 // so that the scores never occupy more than 64 registers.
-__device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& a, uint32_t tmem, const TileWalk& w,
+template <int D>
+__device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_args& a, uint32_t tmem, const TileWalk& w,
                                              const RowBound& rb, bool live, int batch, int head) {
+  WM_FWD_CONSTANTS(D);
   const int t = threadIdx.x;
   const int row = t & 127;
   const int grp = t >> 7;
@@ -141,7 +172,7 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
   float m_ref = -INFINITY, l = 0.f;
   float pending = 1.f;  // factor the accumulator still has to be multiplied by
   constexpr float kGuard = 64.f;  // log2 units a tile may exceed its reference by before it is read twice
-  const uint32_t o_mine = tmem + kOutCol + grp * kHeadDim + lane_base;
+  const uint32_t o_mine = tmem + kOutCol + grp * D + lane_base;
   const int b = grp;  // P buffer, output accumulator and document tables of this group
 
   // document id / query bound of key slot (tile start + row), loaded one tile of this group ahead
@@ -244,7 +275,7 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       if (n >= 2 && !wait_or_abort(sm, &sm.pv_done[(n - 2) % kStages], ((n - 2) / kStages) & 1, 32)) return false;
       ptx::tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t raw[32];
         ptx::tmem_ld32(o_mine + 32 * c, raw);
         ptx::tmem_wait_ld();
@@ -408,9 +439,12 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
       if (!wait_or_abort(sm, &sm.v_full[s], (n / kStages) & 1, 34)) return;
       const uint32_t km_word = row < 32 ? km0 : (row < 64 ? km1 : (row < 96 ? km2 : km3));
       if ((last_ragged && j0 + row >= w.kmax) || !((km_word >> (row & 31)) & 1u)) {
-        uint4* vrow = reinterpret_cast<uint4*>(sm.v[s] + row * 128);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
+        for (int h = 0; h < kSub; ++h) {
+          uint4* vrow = reinterpret_cast<uint4*>(sm.v[s] + h * kSubBytes + row * 128);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
+        }
       }
       ptx::fence_async_shared();
     }
@@ -446,45 +480,54 @@ __device__ __forceinline__ void softmax_role(FwdShared& sm, const wm_attn_args& 
     if (last1 >= 0 && !wait_or_abort(sm, &sm.pv_done[last1 % kStages], (last1 / kStages) & 1, 38)) return;
   }
   ptx::tc_fence_after();
-  uint32_t acc0[32], acc1[32];
-  ptx::tmem_ld32(tmem + kOutCol + lane_base + grp * 32, acc0);
-  if (last >= 1) ptx::tmem_ld32(tmem + kOutCol + kHeadDim + lane_base + grp * 32, acc1);
-  ptx::tmem_wait_ld();
-  if (live) {
-    __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(a.out) + batch * a.out_strides[0] + head * a.out_strides[1] +
-                          static_cast<long long>(rb.qi) * a.out_strides[2] + grp * 32;
-    const bool use0 = w0 > 0.f, use1 = last >= 1 && w1 > 0.f;
-    // whole 32-byte sectors where the caller's rows allow it: rows of different lanes are far apart, and partial
-    // sectors are what makes such stores slow
-    const bool sectors = (reinterpret_cast<uintptr_t>(orow) & 31) == 0;
+  // this thread writes half of the row's D columns (the group picks the half), 32 at a time
+  __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(a.out) + batch * a.out_strides[0] + head * a.out_strides[1] +
+                        static_cast<long long>(rb.qi) * a.out_strides[2] + grp * (D / 2);
+  const bool use0 = w0 > 0.f, use1 = last >= 1 && w1 > 0.f;
+  // whole 32-byte sectors where the caller's rows allow it: rows of different lanes are far apart, and partial
+  // sectors are what makes such stores slow
+  const bool sectors = (reinterpret_cast<uintptr_t>(orow) & 31) == 0;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      uint32_t pk[8];
+  for (int part = 0; part < D / 64; ++part) {
+    uint32_t acc0[32], acc1[32];
+    ptx::tmem_ld32(tmem + kOutCol + lane_base + grp * (D / 2) + 32 * part, acc0);
+    if (last >= 1) ptx::tmem_ld32(tmem + kOutCol + D + lane_base + grp * (D / 2) + 32 * part, acc1);
+    ptx::tmem_wait_ld();
+    if (live) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int i = 16 * u + 2 * e;
-        const float lo = (use0 ? __uint_as_float(acc0[i]) * w0 : 0.f) + (use1 ? __uint_as_float(acc1[i]) * w1 : 0.f);
-        const float hi = (use0 ? __uint_as_float(acc0[i + 1]) * w0 : 0.f) + (use1 ? __uint_as_float(acc1[i + 1]) * w1 : 0.f);
-        pk[e] = pack_bf16(lo, hi);
-      }
-      if (sectors) {
-        ptx::st_global_v8(orow + 16 * u, pk);
-      } else {
-        reinterpret_cast<uint4*>(orow)[2 * u] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        reinterpret_cast<uint4*>(orow)[2 * u + 1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      for (int u = 0; u < 2; ++u) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int i = 16 * u + 2 * e;
+          const float lo = (use0 ? __uint_as_float(acc0[i]) * w0 : 0.f) + (use1 ? __uint_as_float(acc1[i]) * w1 : 0.f);
+          const float hi = (use0 ? __uint_as_float(acc0[i + 1]) * w0 : 0.f) + (use1 ? __uint_as_float(acc1[i + 1]) * w1 : 0.f);
+          pk[e] = pack_bf16(lo, hi);
+        }
+        __nv_bfloat16* dst = orow + 32 * part + 16 * u;
+        if (sectors) {
+          ptx::st_global_v8(dst, pk);
+        } else {
+          reinterpret_cast<uint4*>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          reinterpret_cast<uint4*>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
       }
     }
+  }
+  if (live) {
     if (grp == 0 && a.lse != nullptr)
       a.lse[(static_cast<long long>(batch) * a.q_heads + head) * a.q_len + rb.qi] =
           l_all > 0.f ? (m_all + log2f(l_all)) * kLn2 : INFINITY;
   }
 }
 
+template <int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
     attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const wm_attn_args a, const int epoch) {
+  WM_FWD_CONSTANTS(D);
   extern __shared__ unsigned char smem_raw[];
-  FwdShared& sm = *reinterpret_cast<FwdShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  FwdShared<D>& sm = *reinterpret_cast<FwdShared<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int q_tile = gridDim.z - 1 - blockIdx.z;  // slowest grid dimension: the longest key walks start first
@@ -545,7 +588,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     ptx::prefetch_tmap(&map_k);
     ptx::prefetch_tmap(&map_v);
     ptx::mbar_expect_tx(&sm.q_full, kTileBytes);
-    ptx::tma_load_4d(sm.q, &map_q, &sm.q_full, 0, q0, head, batch);
+#pragma unroll
+    for (int h = 0; h < kSub; ++h) ptx::tma_load_4d(sm.q + h * kSubBytes, &map_q, &sm.q_full, 64 * h, q0, head, batch);
   }
   // (a thread that has no row waits for this load, beside the rows' own loads)
   if (tid == kFwdThreads - 1) sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
@@ -565,9 +609,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     // no row of the tile sees a key: zeros and +inf, then the common exit (the query tile still has to land)
     if (live) {
       __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(a.out) + batch * a.out_strides[0] + head * a.out_strides[1] +
-                            static_cast<long long>(rb.qi) * a.out_strides[2] + (tid >> 7) * 32;
+                            static_cast<long long>(rb.qi) * a.out_strides[2] + (tid >> 7) * (D / 2);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < D / 16; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0, 0, 0, 0);
       if (tid < kTileM && a.lse != nullptr)
         a.lse[(static_cast<long long>(batch) * a.q_heads + head) * a.q_len + rb.qi] = INFINITY;
     }
@@ -578,11 +622,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     w.dummy_tile = (a.q_seg != nullptr && sm.has_dummy && w.first_tile > 0) ? 1 : 0;
     w.n_tiles = end_tile - w.first_tile + w.dummy_tile;
     if (warp < 8) {
-      softmax_role(sm, a, tmem, w, rb, live, batch, head);
+      softmax_role<D>(sm, a, tmem, w, rb, live, batch, head);
     } else if (lane == 0) {
-      if (warp == 8) producer_role(sm, &map_q, &map_k, &map_v, w, q0, head, kv_head, batch);
-      if (warp == 9) score_mma_role(sm, tmem, w);
-      if (warp == 10) value_mma_role(sm, tmem, w);
+      if (warp == 8) producer_role<D>(sm, &map_q, &map_k, &map_v, w, q0, head, kv_head, batch);
+      if (warp == 9) score_mma_role<D>(sm, tmem, w);
+      if (warp == 10) value_mma_role<D>(sm, tmem, w);
     }
   }
   ptx::tc_fence_before();
