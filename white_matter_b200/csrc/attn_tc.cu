@@ -1,8 +1,8 @@
-// tcgen05 / TMEM attention kernels for bf16, head_dim 64: host side (tensor maps, kernel selection, launches), the
+// tcgen05 / TMEM attention kernels for bf16, head_dim 64 (the forward also 128): host side (tensor maps, kernel selection, launches), the
 // helpers the pipelines share (bounded waits, the device status word, document masks), and the three pipelines
 // themselves, each in a header of its own:
-//   attn_tc_fwd.cuh       forward: one block per 128 query rows, two softmax groups on alternate key tiles, P kept
-//                         in tensor memory as the A operand of the PV product
+//   attn_tc_fwd.cuh       forward (a template over the head size): one block per 128 query rows, two softmax groups
+//                         on alternate key tiles, P kept in tensor memory as the A operand of the PV product
 //   attn_tc_bwd_resident.cuh  backward for at most 256 queries per (batch, head) without grouped heads: one block
 //                         per (batch, head), both query tiles and their dQ accumulators resident
 //   attn_tc_bwd.cuh       backward for every other shape: one block per key tile, dQ through fp32 atomics

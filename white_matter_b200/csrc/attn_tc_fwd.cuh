@@ -1,17 +1,17 @@
-// Forward pipeline of the tcgen05 attention kernel (included by attn_tc.cu).
+// Forward pipeline of the tcgen05 attention kernel (included by attn_tc.cu), a template over the head size.
 //
 // One block owns 128 query rows of one (batch, head) and walks over tiles of 128 key slots.
-// 320 threads: warps 0-7 softmax, warp 8 TMA producer (Q once, K and V through 3-deep rings,
-// per-block loads, no multicast), warp 9 issues tcgen05.mma: S = Q K^T into one of three TMEM
-// buffers, O += P V into the accumulator of the tile's parity; completion is signalled by
-// tcgen05.commit on mbarriers.
+// 352 threads: warps 0-7 softmax, warp 8 TMA producer (Q once, K and V through rings, per-block loads, no
+// multicast), warps 9 and 10 issue tcgen05.mma (one lane each): S = Q K^T into one of the score buffers in TMEM,
+// O += P V into the accumulator of the tile's parity; completion is signalled by tcgen05.commit on mbarriers.
 // The softmax warps form two groups of 128 threads (thread = query row = TMEM lane).  Group g
 // owns the key tiles of parity g with its own running reference, row sum, P buffer and output
 // accumulator, so the groups exchange nothing per tile and run out of phase; their partial
 // results are merged in the epilogue like the splits of a split-KV reduction.
 // P never touches shared memory: it is written as packed bf16 over the first 64 columns of its own
 // score buffer and the PV product takes it from there as its A operand.
-// TMEM: S0..S2 [0,384) (P aliases the tile's S), O0 [384,448), O1 [448,512) columns; 512 allocated.
+// TMEM (512 columns), head size 64: S0..S2 [0,384) (P aliases the tile's S), O0 [384,448), O1 [448,512);
+// head size 128: S0, S1 [0,256), O0 [256,384), O1 [384,512).
 #pragma once
 
 constexpr int kFwdThreads = 352;
