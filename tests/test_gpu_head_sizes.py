@@ -1,4 +1,4 @@
-"""Head size 128 on the tensor-core forward (the gradient kernels of that size are the SIMT family's)."""
+"""Head sizes 128 and 96 on the tensor-core forward (the gradient kernels of those sizes are the SIMT family's)."""
 
 import pytest
 import torch
@@ -14,12 +14,12 @@ from white_matter_b200 import (
 )
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not torch.cuda.is_available(), reason="requires CUDA")]
-D = 128
 
 
+@pytest.mark.parametrize("D", [128, 96])
 @pytest.mark.parametrize("documents", [False, True])
 @pytest.mark.parametrize("stride,residue,length", [(8, 3, 1100), (4, 0, 520), (1, 0, 300)])
-def test_cyclic_forward(stride, residue, length, documents):
+def test_cyclic_forward(stride, residue, length, documents, D):
     torch.manual_seed(5)
     B, H, HKV = 2, 4, 2
     queries = len(range(residue, length, stride))
@@ -36,13 +36,14 @@ def test_cyclic_forward(stride, residue, length, documents):
         simt = cyclic_attention(q.cuda(), k.cuda(), v.cuda(), metadata=dev_md, backend="sm100_simt", **args)
     assert _native.device_status(True) == 0
     exp = oracle.cyclic_attention_oracle(q.double(), k.double(), v.double(), metadata=metadata, **args)
-    assert_parity(out.float(), exp, what="tcgen05 forward, head 128", **BF16_TOL)
+    assert_parity(out.float(), exp, what=f"tcgen05 forward, head {D}", **BF16_TOL)
     assert_parity(out.float(), simt.float(), what="tcgen05 vs simt", **BF16_TOL)
 
 
+@pytest.mark.parametrize("D", [128, 96])
 @pytest.mark.parametrize("masked", [False, True])
 @pytest.mark.parametrize("length", [128, 70])
-def test_cached_prefix_prefill_with_nan_capacity(length, masked):
+def test_cached_prefix_prefill_with_nan_capacity(length, masked, D):
     torch.manual_seed(6)
     B, H, HKV, N = 3, 4, 4, 900
     lengths = torch.tensor([880, 400, 129])
@@ -66,10 +67,11 @@ def test_cached_prefix_prefill_with_nan_capacity(length, masked):
         )
     assert torch.isfinite(out).all()
     exp = oracle.strict_causal_oracle(q.double(), k.double(), v.double(), query_start=starts, kv_lengths=lengths, key_mask=key_mask)
-    assert_parity(out.float(), exp, what="prefill, head 128", **BF16_TOL)
+    assert_parity(out.float(), exp, what=f"prefill, head {D}", **BF16_TOL)
 
 
-def test_jacobi_with_documents_and_gradients_through_both_families():
+@pytest.mark.parametrize("D", [128, 96])
+def test_jacobi_with_documents_and_gradients_through_both_families(D):
     """Forward on the tensor cores, gradients on the SIMT kernels (the default backend's choice at this head size)."""
     torch.manual_seed(7)
     B, H, T = 2, 2, 384

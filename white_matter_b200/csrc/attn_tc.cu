@@ -1,4 +1,4 @@
-// tcgen05 / TMEM attention kernels for bf16, head_dim 64 (the forward also 128): host side (tensor maps, kernel selection, launches), the
+// tcgen05 / TMEM attention kernels for bf16, head_dim 64 (the forward also 96 and 128): host side (tensor maps, kernel selection, launches), the
 // helpers the pipelines share (bounded waits, the device status word, document masks), and the three pipelines
 // themselves, each in a header of its own:
 //   attn_tc_fwd.cuh       forward (a template over the head size): one block per 128 query rows, two softmax groups
@@ -336,7 +336,8 @@ int next_epoch() {
 }
 
 bool tc_fwd_supported(const wm_attn_args& a) {
-  if (a.dtype != WM_BF16 || (a.head_dim != 64 && a.head_dim != 128)) return false;  // the forward takes either
+  // the forward takes heads of 64, 96 and 128 (96 runs as 128 with columns the copies fill with zeros)
+  if (a.dtype != WM_BF16 || (a.head_dim != 64 && a.head_dim != 96 && a.head_dim != 128)) return false;
   if (a.mask == WM_MASK_PACKED) return false;
   if (!tma_ok(a.q, a.q_strides, a.batch, a.q_heads, a.q_len)) return false;
   if (!tma_ok(a.k, a.k_strides, a.batch, a.kv_heads, a.k_len)) return false;
@@ -350,11 +351,11 @@ bool tc_fwd_supported(const wm_attn_args& a) {
 template <int D>
 int launch_fwd(const wm_attn_args& a, cudaStream_t stream) {
   CUtensorMap map_q, map_k, map_v;
-  int status = make_map(&map_q, a.q, a.batch, a.q_heads, a.q_len, a.q_strides, kTileM, D);
+  int status = make_map(&map_q, a.q, a.batch, a.q_heads, a.q_len, a.q_strides, kTileM, a.head_dim);
   if (status != WM_OK) return status;
-  status = make_map(&map_k, a.k, a.batch, a.kv_heads, a.k_len, a.k_strides, kTileN, D);
+  status = make_map(&map_k, a.k, a.batch, a.kv_heads, a.k_len, a.k_strides, kTileN, a.head_dim);
   if (status != WM_OK) return status;
-  status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN, D);
+  status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN, a.head_dim);
   if (status != WM_OK) return status;
   dim3 grid(a.q_heads, a.batch, (a.q_len + kTileM - 1) / kTileM);
   const size_t smem = sizeof(FwdShared<D>) + 1024;
@@ -367,7 +368,7 @@ int launch_fwd(const wm_attn_args& a, cudaStream_t stream) {
 }
 
 int tc_attn_fwd(const wm_attn_args& a, cudaStream_t stream) {
-  return a.head_dim == 128 ? launch_fwd<128>(a, stream) : launch_fwd<64>(a, stream);
+  return a.head_dim > 64 ? launch_fwd<128>(a, stream) : launch_fwd<64>(a, stream);
 }
 
 // Arms the trace for the launch after the next `arm_after` launches (negative: disarm) and fetches what was

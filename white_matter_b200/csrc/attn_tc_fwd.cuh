@@ -493,7 +493,7 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
     ptx::tmem_ld32(tmem + kOutCol + lane_base + grp * (D / 2) + 32 * part, acc0);
     if (last >= 1) ptx::tmem_ld32(tmem + kOutCol + D + lane_base + grp * (D / 2) + 32 * part, acc1);
     ptx::tmem_wait_ld();
-    if (live) {
+    if (live && grp * (D / 2) + 32 * part < a.head_dim) {  // (a head of 96 ends inside the second group's half)
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         uint32_t pk[8];
@@ -611,7 +611,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(a.out) + batch * a.out_strides[0] + head * a.out_strides[1] +
                             static_cast<long long>(rb.qi) * a.out_strides[2] + (tid >> 7) * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 16; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < D / 16; ++c)
+        if ((tid >> 7) * (D / 2) + 8 * c < a.head_dim) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0, 0, 0, 0);
       if (tid < kTileM && a.lse != nullptr)
         a.lse[(static_cast<long long>(batch) * a.q_heads + head) * a.q_len + rb.qi] = INFINITY;
     }
