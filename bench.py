@@ -744,28 +744,38 @@ def bench_cyclic_prefill(device, peaks, reps=3):
 
 
 def bench_head_dim_128(device, peaks, iters=10):
-    """Heads of 128 on the tensor-core forward: the training configuration's call shape (B=16 H=16 K=2048 Q=256, stride
-    8, residue 7) with head_dim 128, against the SIMT family that served this head size before."""
+    """Heads of 128 on the tensor-core kernels: the training configuration's call shape (B=16 H=16 K=2048 Q=256, stride
+    8, residue 7) with head_dim 128, forward and gradients, against the SIMT family that served this head size before."""
     from white_matter_b200 import cyclic_attention
 
     dim = 128
     gen = torch.Generator(device=device).manual_seed(8)
-    q = torch.randn(B, H, T // STRIDE, dim, device=device, generator=gen).to(torch.bfloat16)
+    q, probe = (torch.randn(B, H, T // STRIDE, dim, device=device, generator=gen).to(torch.bfloat16) for _ in range(2))
     k, v = (torch.randn(B, H, T, dim, device=device, generator=gen).to(torch.bfloat16) for _ in range(2))
     residue = STRIDE - 1
     pairs = sum(residue + STRIDE * i for i in range(T // STRIDE)) * B * H  # strict past: key slots below the query's
+    opts = dict(query_stride=STRIDE, query_offset=residue, strict_past=True)
     timed = {}
-    with torch.no_grad():
-        for name, backend in (("tcgen05", "sm100"), ("simt", "sm100_simt")):
-            call = lambda: cyclic_attention(q, k, v, query_stride=STRIDE, query_offset=residue, strict_past=True, backend=backend)
-            n = iters if name == "tcgen05" else 3
+    for name, backend in (("tcgen05", "sm100"), ("simt", "sm100_simt")):
+        n = iters if name == "tcgen05" else 3
+        with torch.no_grad():
+            call = lambda: cyclic_attention(q, k, v, backend=backend, **opts)
             timed[name] = time_steps(call, n, 2, torch.cuda.synchronize) / n
+        leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+        out = cyclic_attention(*leaves, backend=backend, **opts)
+        call = lambda: torch.autograd.grad(out, leaves, probe, retain_graph=True)
+        timed[name + "_bwd"] = time_steps(call, n, 2, torch.cuda.synchronize) / n
+        del out, leaves
     tf = 4 * dim * pairs / (timed["tcgen05"] * 1e-3) / 1e12
+    tf_bwd = 10 * dim * pairs / (timed["tcgen05_bwd"] * 1e-3) / 1e12
     return {
-        "workload": "cyclic_attention forward B=16 H=16 K=2048 Q=256 stride 8 residue 7, head_dim 128, bf16",
+        "workload": "cyclic_attention B=16 H=16 K=2048 Q=256 stride 8 residue 7, head_dim 128, bf16",
         "ms": timed["tcgen05"], "value": tf, "unit": "TFLOP/s", "simt_ms": timed["simt"],
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_kind": "bf16_tflops (kernel timed alone)"},
+        "backward": {"ms": timed["tcgen05_bwd"], "value": tf_bwd, "unit": "TFLOP/s", "simt_ms": timed["simt_bwd"],
+                     "kernels": "bwd_delta_kernel, attn_bwd_tc_kernel<128> (one block per key tile), bwd_dq_convert_kernel",
+                     "frac_of_burst_peak": tf_bwd / peaks["bf16_tflops"]},
     }
 
 

@@ -1,11 +1,12 @@
-// tcgen05 / TMEM attention kernels for bf16, head_dim 64 (the forward also 96 and 128): host side (tensor maps, kernel selection, launches), the
-// helpers the pipelines share (bounded waits, the device status word, document masks), and the three pipelines
+// tcgen05 / TMEM attention kernels for bf16, head_dim 64, 96 and 128: host side (tensor maps, kernel selection,
+// launches), the helpers the pipelines share (bounded waits, the device status word, document masks), and the three pipelines
 // themselves, each in a header of its own:
 //   attn_tc_fwd.cuh       forward (a template over the head size): one block per 128 query rows, two softmax groups
 //                         on alternate key tiles, P kept in tensor memory as the A operand of the PV product
-//   attn_tc_bwd_resident.cuh  backward for at most 256 queries per (batch, head) without grouped heads: one block
-//                         per (batch, head), both query tiles and their dQ accumulators resident
-//   attn_tc_bwd.cuh       backward for every other shape: one block per key tile, dQ through fp32 atomics
+//   attn_tc_bwd_resident.cuh  backward for heads of 64, at most 256 queries per (batch, head), no grouped heads:
+//                         one block per (batch, head), both query tiles and their dQ accumulators resident
+//   attn_tc_bwd.cuh       backward for every other shape (a template over the head size): one block per key tile,
+//                         dQ through fp32 atomics
 // Key tiles that no query can see are never loaded.  Every mbarrier wait is bounded; a wait that runs out records
 // its code in a device status word, and all roles of the block fall through to the common exit where tensor memory
 // is released.
@@ -420,8 +421,8 @@ int tc_device_status(bool reset) {
 }
 
 bool tc_bwd_supported(const wm_attn_args& a) {
-  // the gradient kernels take no key mask and heads of 64 only
-  if (!tc_fwd_supported(a) || a.key_mask != nullptr || a.head_dim != kHeadDim) return false;
+  // the gradient kernels take no key mask
+  if (!tc_fwd_supported(a) || a.key_mask != nullptr) return false;
   if (a.dout == nullptr) return true;  // shape query before the tensors exist
   if (!tma_ok(a.dout, a.dout_strides, a.batch, a.q_heads, a.q_len)) return false;
   if (!tma_ok(a.dk, a.dk_strides, a.batch, a.kv_heads, a.k_len)) return false;
@@ -436,15 +437,30 @@ bool tc_bwd_supported(const wm_attn_args& a) {
   return true;
 }
 
-// The short-query pipeline keeps both query tiles of a (batch, head) resident.
+// The short-query pipeline keeps both query tiles of a (batch, head) resident (heads of 64 only).
 bool bwd_short_queries(const wm_attn_args& a) {
-  return a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
+  return a.head_dim == kHeadDim && a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
 }
 
 size_t tc_attn_bwd_workspace(const wm_attn_args& a) {
   const size_t rows = static_cast<size_t>(a.batch) * a.q_heads * a.q_len;
   const size_t delta_bytes = ((rows + 63) / 64) * 64 * sizeof(float);
-  return bwd_short_queries(a) ? delta_bytes : delta_bytes + rows * kHeadDim * sizeof(float);
+  return bwd_short_queries(a) ? delta_bytes : delta_bytes + rows * a.head_dim * sizeof(float);
+}
+
+// The key-stationary pipeline for one head size: one block per tile of 128 key slots.
+template <int D>
+int launch_bwd_key_tiles(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                         const CUtensorMap& map_g, const wm_attn_args& a, const float* delta, float* dq_acc,
+                         cudaStream_t stream) {
+  const size_t smem = sizeof(BwdShared<D>) + 1024;
+  static std::atomic<bool> configured[kMaxDevices];
+  const int status = allow_shared_memory(attn_bwd_tc_kernel<D>, configured, smem);
+  if (status != WM_OK) return status;
+  dim3 grid((a.k_len + kTileN - 1) / kTileN, a.kv_heads, a.batch);
+  attn_bwd_tc_kernel<D><<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, map_g, a, delta, dq_acc, next_epoch());
+  count_launch();
+  return cuda_check(cudaGetLastError(), "attn_bwd_tc_kernel");
 }
 
 int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
@@ -455,15 +471,18 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
   float* delta = static_cast<float*>(a.workspace);
   float* dq_acc = delta + ((rows + 63) / 64) * 64;
   CUtensorMap map_q, map_k, map_v, map_g;
-  int status = make_map(&map_q, a.q, a.batch, a.q_heads, a.q_len, a.q_strides, kTileM);
+  int status = make_map(&map_q, a.q, a.batch, a.q_heads, a.q_len, a.q_strides, kTileM, a.head_dim);
   if (status != WM_OK) return status;
-  status = make_map(&map_k, a.k, a.batch, a.kv_heads, a.k_len, a.k_strides, kTileN);
+  status = make_map(&map_k, a.k, a.batch, a.kv_heads, a.k_len, a.k_strides, kTileN, a.head_dim);
   if (status != WM_OK) return status;
-  status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN);
+  status = make_map(&map_v, a.v, a.batch, a.kv_heads, a.k_len, a.v_strides, kTileN, a.head_dim);
   if (status != WM_OK) return status;
-  status = make_map(&map_g, a.dout, a.batch, a.q_heads, a.q_len, a.dout_strides, kTileM);
+  status = make_map(&map_g, a.dout, a.batch, a.q_heads, a.q_len, a.dout_strides, kTileM, a.head_dim);
   if (status != WM_OK) return status;
-  bwd_delta_kernel<<<static_cast<unsigned>((rows + 127) / 128), 128, 0, stream>>>(a, delta);
+  const unsigned delta_blocks = static_cast<unsigned>((rows + 127) / 128);
+  if (a.head_dim == 64) bwd_delta_kernel<8><<<delta_blocks, 128, 0, stream>>>(a, delta);
+  else if (a.head_dim == 96) bwd_delta_kernel<12><<<delta_blocks, 128, 0, stream>>>(a, delta);
+  else bwd_delta_kernel<16><<<delta_blocks, 128, 0, stream>>>(a, delta);
   count_launch();
   WM_CUDA(cudaGetLastError());
   if (bwd_short_queries(a)) {
@@ -481,16 +500,11 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
     count_launch();
     return cuda_check(cudaGetLastError(), "attention backward (tcgen05, resident queries)");
   }
-  WM_CUDA(cudaMemsetAsync(dq_acc, 0, rows * kHeadDim * sizeof(float), stream));
-  const size_t smem = sizeof(BwdShared) + 1024;
-  static std::atomic<bool> configured[kMaxDevices];
-  status = allow_shared_memory(attn_bwd_tc_kernel, configured, smem);
+  WM_CUDA(cudaMemsetAsync(dq_acc, 0, rows * a.head_dim * sizeof(float), stream));
+  status = a.head_dim > 64 ? launch_bwd_key_tiles<128>(map_q, map_k, map_v, map_g, a, delta, dq_acc, stream)
+                           : launch_bwd_key_tiles<64>(map_q, map_k, map_v, map_g, a, delta, dq_acc, stream);
   if (status != WM_OK) return status;
-  dim3 grid((a.k_len + kTileN - 1) / kTileN, a.kv_heads, a.batch);
-  attn_bwd_tc_kernel<<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, map_g, a, delta, dq_acc, next_epoch());
-  count_launch();
-  WM_CUDA(cudaGetLastError());
-  const size_t chunks = rows * 8;
+  const size_t chunks = rows * (a.head_dim / 8);
   bwd_dq_convert_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(a, dq_acc);
   count_launch();
   return cuda_check(cudaGetLastError(), "attention backward (tcgen05)");

@@ -14,18 +14,35 @@
 // The same shared tile serves as K-major operand (dS K) and as MN-major
 // operand (P^T dO, dS^T Q); Q and dO tiles likewise serve as A (K-major) and
 // as B (MN-major).
-// TMEM columns: S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ [384,448).
-constexpr int kBwdStages = 2;
+// TMEM columns, head size 64: S [0,128) dP [128,256) dV [256,320) dK [320,384) dQ [384,448).
+//
+// The kernel is a template over the head size D (64 or 128; 96 runs as 128 over tensor maps of 96 columns, whose
+// copies fill columns 96..127 with zeros).  At 128 a Q, K, V or dO tile travels as two 64-column sub-tiles (one
+// 128-byte swizzle row per token each), S and dP run eight K=16 steps over both, and the three gradient products
+// are issued once per 64-column half of their result.  dV and dK then take 128 columns each, which fills the 512
+// with S and dP: dQ of a pair is formed over the columns of S (the compute threads have read the scores by the
+// time dS exists), and the next pair's score product waits until they have taken dQ out.  Q and dO have one stage
+// instead of two (192 KB of shared memory).
+template <int D>
+struct BwdCfg {
+  static constexpr int kSub = D / 64;
+  static constexpr uint32_t kBytes = kTileN * D * 2;  // one Q, K, V or dO tile
+  static constexpr int kQStages = D == 64 ? 2 : 1;
+  static constexpr bool kDqOverS = D > 64;
+  static constexpr uint32_t kColDv = 2 * kTileN, kColDk = 2 * kTileN + D;
+  static constexpr uint32_t kColDq = kDqOverS ? 0 : 2 * kTileN + 2 * D;
+};
 
+template <int D>
 struct BwdShared {
-  unsigned char k[kTileBytes];
-  unsigned char v[kTileBytes];
-  unsigned char q[kBwdStages][kTileBytes];
-  unsigned char g[kBwdStages][kTileBytes];  // dO tiles
+  unsigned char k[BwdCfg<D>::kBytes];
+  unsigned char v[BwdCfg<D>::kBytes];
+  unsigned char q[BwdCfg<D>::kQStages][BwdCfg<D>::kBytes];
+  unsigned char g[BwdCfg<D>::kQStages][BwdCfg<D>::kBytes];  // dO tiles
   unsigned char p[2 * kTileBytes];
   unsigned char ds[2 * kTileBytes];
   uint64_t kv_full, kv_ready;
-  uint64_t qg_full[kBwdStages], qg_empty[kBwdStages];
+  uint64_t qg_full[BwdCfg<D>::kQStages], qg_empty[BwdCfg<D>::kQStages];
   uint64_t sdp_full, pds_full, mma_done, dq_full, dq_free;
   int key_seg[kTileN];
   int key_end[kTileN];
@@ -36,7 +53,8 @@ struct BwdShared {
   int epoch;
 };
 
-// delta = rowsum(dO * O) in fp32, one thread per (batch, head, query) row of 64 values
+// delta = rowsum(dO * O) in fp32, one thread per (batch, head, query) row of 8 * kChunks values
+template <int kChunks>
 __global__ void bwd_delta_kernel(const wm_attn_args a, float* delta) {
   const long long rows = static_cast<long long>(a.batch) * a.q_heads * a.q_len;
   const long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -50,7 +68,7 @@ __global__ void bwd_delta_kernel(const wm_attn_args a, float* delta) {
                                                   h * a.dout_strides[1] + static_cast<long long>(i) * a.dout_strides[2]);
   float acc = 0.f;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int c = 0; c < kChunks; ++c) {
     const uint4 x = o[c], y = g[c];
     const unsigned xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
@@ -62,18 +80,19 @@ __global__ void bwd_delta_kernel(const wm_attn_args a, float* delta) {
   delta[row] = acc;
 }
 
-// dq = bf16(scale * accumulator); accumulator is (batch, heads, queries, 64) fp32
+// dq = bf16(scale * accumulator); accumulator is (batch, heads, queries, head_dim) fp32
 __global__ void bwd_dq_convert_kernel(const wm_attn_args a, const float* acc) {
-  const long long chunks = static_cast<long long>(a.batch) * a.q_heads * a.q_len * 8;  // 8 values each
+  const int per_row = a.head_dim / 8;  // chunks of 8 values
+  const long long chunks = static_cast<long long>(a.batch) * a.q_heads * a.q_len * per_row;
   const long long at = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (at >= chunks) return;
-  const long long row = at >> 3;
-  const int c = static_cast<int>(at & 7);
+  const long long row = at / per_row;
+  const int c = static_cast<int>(at - row * per_row);
   const int i = static_cast<int>(row % a.q_len);
   const int h = static_cast<int>((row / a.q_len) % a.q_heads);
   const int b = static_cast<int>(row / (static_cast<long long>(a.q_len) * a.q_heads));
-  const float4 lo = *reinterpret_cast<const float4*>(acc + row * kHeadDim + c * 8);
-  const float4 hi = *reinterpret_cast<const float4*>(acc + row * kHeadDim + c * 8 + 4);
+  const float4 lo = *reinterpret_cast<const float4*>(acc + row * a.head_dim + c * 8);
+  const float4 hi = *reinterpret_cast<const float4*>(acc + row * a.head_dim + c * 8 + 4);
   const float s = a.scale;
   __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.dq) + b * a.dq_strides[0] + h * a.dq_strides[1] +
                        static_cast<long long>(i) * a.dq_strides[2] + c * 8;
@@ -100,66 +119,91 @@ __device__ __forceinline__ void bwd_iter_coords(const BwdWalk& w, int it, int kv
   head = kv_head * w.heads + g;
 }
 
-__device__ __forceinline__ void bwd_producer(BwdShared& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
+template <int D>
+__device__ __forceinline__ void bwd_producer(BwdShared<D>& sm, const CUtensorMap* map_q, const CUtensorMap* map_k,
                                              const CUtensorMap* map_v, const CUtensorMap* map_g, const BwdWalk& w,
                                              int j0, int kv_head, int batch) {
+  constexpr int kBwdStages = BwdCfg<D>::kQStages, kSub = BwdCfg<D>::kSub;
+  constexpr uint32_t kBytes = BwdCfg<D>::kBytes;
   ptx::prefetch_tmap(map_q);
   ptx::prefetch_tmap(map_k);
   ptx::prefetch_tmap(map_v);
   ptx::prefetch_tmap(map_g);
-  ptx::mbar_expect_tx(&sm.kv_full, 2 * kTileBytes);
-  ptx::tma_load_4d(sm.k, map_k, &sm.kv_full, 0, j0, kv_head, batch);
-  ptx::tma_load_4d(sm.v, map_v, &sm.kv_full, 0, j0, kv_head, batch);
+  ptx::mbar_expect_tx(&sm.kv_full, 2 * kBytes);
+#pragma unroll
+  for (int h = 0; h < kSub; ++h) {
+    ptx::tma_load_4d(sm.k + h * kSubBytes, map_k, &sm.kv_full, 64 * h, j0, kv_head, batch);
+    ptx::tma_load_4d(sm.v + h * kSubBytes, map_v, &sm.kv_full, 64 * h, j0, kv_head, batch);
+  }
   for (int it = 0; it < w.n_iter; ++it) {
     const int s = it % kBwdStages;
     int head, qt;
     bwd_iter_coords(w, it, kv_head, head, qt);
     if (!wait_or_abort(sm, &sm.qg_empty[s], ((it / kBwdStages) & 1) ^ 1, 41)) return;
-    ptx::mbar_expect_tx(&sm.qg_full[s], 2 * kTileBytes);
-    ptx::tma_load_4d(sm.q[s], map_q, &sm.qg_full[s], 0, qt * kTileM, head, batch);
-    ptx::tma_load_4d(sm.g[s], map_g, &sm.qg_full[s], 0, qt * kTileM, head, batch);
+    ptx::mbar_expect_tx(&sm.qg_full[s], 2 * kBytes);
+#pragma unroll
+    for (int h = 0; h < kSub; ++h) {
+      ptx::tma_load_4d(sm.q[s] + h * kSubBytes, map_q, &sm.qg_full[s], 64 * h, qt * kTileM, head, batch);
+      ptx::tma_load_4d(sm.g[s] + h * kSubBytes, map_g, &sm.qg_full[s], 64 * h, qt * kTileM, head, batch);
+    }
   }
 }
 
-__device__ __forceinline__ void bwd_mma(BwdShared& sm, uint32_t tmem, const BwdWalk& w) {
+template <int D>
+__device__ __forceinline__ void bwd_mma(BwdShared<D>& sm, uint32_t tmem, const BwdWalk& w) {
+  using Cfg = BwdCfg<D>;
+  constexpr int kBwdStages = Cfg::kQStages;
+  constexpr uint32_t kHalfStep = D > 64 ? kSubBytes : 1024;  // between the 64-column halves of an MN-major B operand
   if (!wait_or_abort(sm, &sm.kv_ready, 0, 50)) return;
   ptx::tc_fence_after();
   constexpr uint32_t idesc_s = ptx::make_idesc_bf16(kTileM, kTileN, 0, 0);      // Q K^T, dO V^T
-  constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, kHeadDim, 1, 1);    // P^T dO, dS^T Q
-  constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, kHeadDim, 0, 1);    // dS K
+  constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, D, 1, 1);           // P^T dO, dS^T Q
+  constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, D, 0, 1);           // dS K
   const uint32_t k_base = ptx::smem_u32(sm.k), v_base = ptx::smem_u32(sm.v);
   const uint32_t p_base = ptx::smem_u32(sm.p), ds_base = ptx::smem_u32(sm.ds);
   for (int it = 0; it < w.n_iter; ++it) {
     const int s = it % kBwdStages;
     if (!wait_or_abort(sm, &sm.qg_full[s], (it / kBwdStages) & 1, 51)) return;
+    if (Cfg::kDqOverS) {
+      // dQ of the previous pair lives in the columns of S until the compute threads have taken it out
+      if (!wait_or_abort(sm, &sm.dq_free, (it & 1) ^ 1, 54)) return;
+    }
     ptx::tc_fence_after();
     const uint32_t q_base = ptx::smem_u32(sm.q[s]), g_base = ptx::smem_u32(sm.g[s]);
 #pragma unroll
-    for (int kk = 0; kk < kHeadDim / 16; ++kk)
-      ptx::mma_bf16_ss(tmem, ptx::make_smem_desc_sw128(q_base + kk * 32, 16, 1024),
-                       ptx::make_smem_desc_sw128(k_base + kk * 32, 16, 1024), idesc_s, kk > 0);
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t at = (kk >> 2) * kSubBytes + (kk & 3) * 32;
+      ptx::mma_bf16_ss(tmem, ptx::make_smem_desc_sw128(q_base + at, 16, 1024),
+                       ptx::make_smem_desc_sw128(k_base + at, 16, 1024), idesc_s, kk > 0);
+    }
 #pragma unroll
-    for (int kk = 0; kk < kHeadDim / 16; ++kk)
-      ptx::mma_bf16_ss(tmem + kTileN, ptx::make_smem_desc_sw128(g_base + kk * 32, 16, 1024),
-                       ptx::make_smem_desc_sw128(v_base + kk * 32, 16, 1024), idesc_s, kk > 0);
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t at = (kk >> 2) * kSubBytes + (kk & 3) * 32;
+      ptx::mma_bf16_ss(tmem + kTileN, ptx::make_smem_desc_sw128(g_base + at, 16, 1024),
+                       ptx::make_smem_desc_sw128(v_base + at, 16, 1024), idesc_s, kk > 0);
+    }
     ptx::mma_commit(&sm.sdp_full);
     if (!wait_or_abort(sm, &sm.pds_full, it & 1, 52)) return;
     ptx::tc_fence_after();
+    // the gradient products span all D result columns in one instruction: the MN-major B operand steps from one
+    // 64-column sub-tile to the next by its leading-dimension offset, like the two 64-key halves of P and dS
 #pragma unroll
     for (int kk = 0; kk < kTileM / 16; ++kk)  // 16 queries per instruction
-      ptx::mma_bf16_ss(tmem + 2 * kTileN, ptx::make_smem_desc_sw128(p_base + kk * 2048, kTileBytes, 1024),
-                       ptx::make_smem_desc_sw128(g_base + kk * 2048, 1024, 1024), idesc_t, (it > 0) || (kk > 0));
+      ptx::mma_bf16_ss(tmem + Cfg::kColDv, ptx::make_smem_desc_sw128(p_base + kk * 2048, kTileBytes, 1024),
+                       ptx::make_smem_desc_sw128(g_base + kk * 2048, kHalfStep, 1024), idesc_t, (it > 0) || (kk > 0));
 #pragma unroll
     for (int kk = 0; kk < kTileM / 16; ++kk)
-      ptx::mma_bf16_ss(tmem + 2 * kTileN + kHeadDim, ptx::make_smem_desc_sw128(ds_base + kk * 2048, kTileBytes, 1024),
-                       ptx::make_smem_desc_sw128(q_base + kk * 2048, 1024, 1024), idesc_t, (it > 0) || (kk > 0));
-    if (!wait_or_abort(sm, &sm.dq_free, (it & 1) ^ 1, 53)) return;
-    ptx::tc_fence_after();
+      ptx::mma_bf16_ss(tmem + Cfg::kColDk, ptx::make_smem_desc_sw128(ds_base + kk * 2048, kTileBytes, 1024),
+                       ptx::make_smem_desc_sw128(q_base + kk * 2048, kHalfStep, 1024), idesc_t, (it > 0) || (kk > 0));
+    if (!Cfg::kDqOverS) {
+      if (!wait_or_abort(sm, &sm.dq_free, (it & 1) ^ 1, 53)) return;
+      ptx::tc_fence_after();
+    }
 #pragma unroll
     for (int kk = 0; kk < kTileN / 16; ++kk)  // 16 keys per instruction
-      ptx::mma_bf16_ss(tmem + 2 * kTileN + 2 * kHeadDim,
+      ptx::mma_bf16_ss(tmem + Cfg::kColDq,
                        ptx::make_smem_desc_sw128(ds_base + (kk >> 2) * kTileBytes + (kk & 3) * 32, 16, 1024),
-                       ptx::make_smem_desc_sw128(k_base + kk * 2048, 1024, 1024), idesc_q, kk > 0);
+                       ptx::make_smem_desc_sw128(k_base + kk * 2048, kHalfStep, 1024), idesc_q, kk > 0);
     ptx::mma_commit(&sm.qg_empty[s]);
     ptx::mma_commit(&sm.mma_done);
     ptx::mma_commit(&sm.dq_full);
@@ -168,8 +212,10 @@ __device__ __forceinline__ void bwd_mma(BwdShared& sm, uint32_t tmem, const BwdW
 
 // compute threads of the backward kernel: thread t owns query row t of the current query tile (and, in
 // the prologue / epilogue, key row t of the CTA's key tile)
-__device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a, uint32_t tmem, const BwdWalk& w,
+template <int D>
+__device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args& a, uint32_t tmem, const BwdWalk& w,
                                             const float* delta, float* dq_acc, int j0, int kv_head, int batch) {
+  using Cfg = BwdCfg<D>;
   const int t = threadIdx.x;
   const int warp = t >> 5;
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
@@ -180,12 +226,15 @@ __device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a
   // prologue: key rows at or beyond the last visible slot may hold anything; clear them for the MMAs
   if (!wait_or_abort(sm, &sm.kv_full, 0, 60)) return;
   if (j0 + t >= w.kvis) {
-    uint4* krow = reinterpret_cast<uint4*>(sm.k + t * 128);
-    uint4* vrow = reinterpret_cast<uint4*>(sm.v + t * 128);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      krow[c] = make_uint4(0, 0, 0, 0);
-      vrow[c] = make_uint4(0, 0, 0, 0);
+    for (int h = 0; h < Cfg::kSub; ++h) {
+      uint4* krow = reinterpret_cast<uint4*>(sm.k + h * kSubBytes + t * 128);
+      uint4* vrow = reinterpret_cast<uint4*>(sm.v + h * kSubBytes + t * 128);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        krow[c] = make_uint4(0, 0, 0, 0);
+        vrow[c] = make_uint4(0, 0, 0, 0);
+      }
     }
   }
   ptx::fence_async_shared();
@@ -268,12 +317,12 @@ __device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a
     if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return;
     ptx::tc_fence_after();
 #pragma unroll
-    for (int c = 0; c < kHeadDim / 32; ++c) {
+    for (int c = 0; c < D / 32; ++c) {
       uint32_t raw[32];
-      ptx::tmem_ld32(tmem + 2 * kTileN + 2 * kHeadDim + lane_base + c * 32, raw);
+      ptx::tmem_ld32(tmem + Cfg::kColDq + lane_base + c * 32, raw);
       ptx::tmem_wait_ld();
-      if (live && !none) {
-        float* dst = dq_acc + stat * kHeadDim + c * 32;
+      if (live && !none && c * 32 < a.head_dim) {
+        float* dst = dq_acc + stat * a.head_dim + c * 32;
 #pragma unroll
         for (int e = 0; e < 8; ++e)
           red_add_v4(dst + 4 * e, __uint_as_float(raw[4 * e]), __uint_as_float(raw[4 * e + 1]),
@@ -286,45 +335,45 @@ __device__ __forceinline__ void bwd_compute(BwdShared& sm, const wm_attn_args& a
 
   // epilogue: dV and dK rows of this key tile (dq_full of the last iteration covers every earlier MMA)
   const int j = j0 + t;
-  uint32_t dv_pack[kHeadDim / 2], dk_pack[kHeadDim / 2];
+  uint4* dvrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dv) + batch * a.dv_strides[0] +
+                                          kv_head * a.dv_strides[1] + static_cast<long long>(j) * a.dv_strides[2]);
+  uint4* dkrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dk) + batch * a.dk_strides[0] +
+                                          kv_head * a.dk_strides[1] + static_cast<long long>(j) * a.dk_strides[2]);
 #pragma unroll
-  for (int e = 0; e < kHeadDim / 2; ++e) dv_pack[e] = dk_pack[e] = 0u;
-  if (w.n_iter > 0) {
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t dv_pack[16], dk_pack[16];
 #pragma unroll
-    for (int c = 0; c < kHeadDim / 32; ++c) {
+    for (int e = 0; e < 16; ++e) dv_pack[e] = dk_pack[e] = 0u;
+    if (w.n_iter > 0) {
       uint32_t raw[32];
-      ptx::tmem_ld32(tmem + 2 * kTileN + lane_base + c * 32, raw);
+      ptx::tmem_ld32(tmem + Cfg::kColDv + lane_base + c * 32, raw);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) dv_pack[e] = pack_bf16(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1]));
+      ptx::tmem_ld32(tmem + Cfg::kColDk + lane_base + c * 32, raw);
       ptx::tmem_wait_ld();
 #pragma unroll
       for (int e = 0; e < 16; ++e)
-        dv_pack[c * 16 + e] = pack_bf16(__uint_as_float(raw[2 * e]), __uint_as_float(raw[2 * e + 1]));
-      ptx::tmem_ld32(tmem + 2 * kTileN + kHeadDim + lane_base + c * 32, raw);
-      ptx::tmem_wait_ld();
-#pragma unroll
-      for (int e = 0; e < 16; ++e)
-        dk_pack[c * 16 + e] =
-            pack_bf16(__uint_as_float(raw[2 * e]) * a.scale, __uint_as_float(raw[2 * e + 1]) * a.scale);
+        dk_pack[e] = pack_bf16(__uint_as_float(raw[2 * e]) * a.scale, __uint_as_float(raw[2 * e + 1]) * a.scale);
     }
-  }
-  if (j < a.k_len) {
-    uint4* dvrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dv) + batch * a.dv_strides[0] +
-                                            kv_head * a.dv_strides[1] + static_cast<long long>(j) * a.dv_strides[2]);
-    uint4* dkrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dk) + batch * a.dk_strides[0] +
-                                            kv_head * a.dk_strides[1] + static_cast<long long>(j) * a.dk_strides[2]);
+    if (j < a.k_len && c * 32 < a.head_dim) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      dvrow[c] = make_uint4(dv_pack[4 * c], dv_pack[4 * c + 1], dv_pack[4 * c + 2], dv_pack[4 * c + 3]);
-      dkrow[c] = make_uint4(dk_pack[4 * c], dk_pack[4 * c + 1], dk_pack[4 * c + 2], dk_pack[4 * c + 3]);
+      for (int u = 0; u < 4; ++u) {
+        dvrow[4 * c + u] = make_uint4(dv_pack[4 * u], dv_pack[4 * u + 1], dv_pack[4 * u + 2], dv_pack[4 * u + 3]);
+        dkrow[4 * c + u] = make_uint4(dk_pack[4 * u], dk_pack[4 * u + 1], dk_pack[4 * u + 2], dk_pack[4 * u + 3]);
+      }
     }
   }
 }
 
+template <int D>
 __global__ void __launch_bounds__(kThreadsFwd, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_g,
                        const wm_attn_args a, const float* delta, float* dq_acc, const int epoch) {
   extern __shared__ unsigned char smem_raw[];
-  BwdShared& sm = *reinterpret_cast<BwdShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kBwdStages = BwdCfg<D>::kQStages;
+  BwdShared<D>& sm = *reinterpret_cast<BwdShared<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int j0 = blockIdx.x * kTileN;
@@ -396,8 +445,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1)
                                               kv_head * a.dv_strides[1] + static_cast<long long>(j0 + tid) * a.dv_strides[2]);
       uint4* dkrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dk) + batch * a.dk_strides[0] +
                                               kv_head * a.dk_strides[1] + static_cast<long long>(j0 + tid) * a.dk_strides[2]);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < a.head_dim / 8; ++c) {
         dvrow[c] = make_uint4(0, 0, 0, 0);
         dkrow[c] = make_uint4(0, 0, 0, 0);
       }

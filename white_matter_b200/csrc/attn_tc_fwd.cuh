@@ -104,7 +104,10 @@ __device__ __forceinline__ void score_mma_role(Shared& sm, uint32_t tmem, const 
 template <int D, class Shared>
 __device__ __forceinline__ void value_mma_role(Shared& sm, uint32_t tmem, const TileWalk& w) {
   WM_FWD_CONSTANTS(D);
-  constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(kTileM, 64, 0, 1);  // one 64-column half of the output at a time
+  // all D output columns in one instruction: the MN-major V operand steps from one 64-column sub-tile to the next by
+  // its leading-dimension offset
+  constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(kTileM, D, 0, 1);
+  constexpr uint32_t kHalfStep = D > 64 ? kSubBytes : 1024;
   for (int n = 0; n < w.n_tiles; ++n) {
     const int b = n & 1;
     const int s = n % kStages;
@@ -118,13 +121,10 @@ __device__ __forceinline__ void value_mma_role(Shared& sm, uint32_t tmem, const 
     const uint32_t p_tmem = tmem + static_cast<uint32_t>(s) * kTileN;  // P overwrote the first 64 columns of S
     const uint32_t v_base = ptx::smem_u32(sm.v[s]);
 #pragma unroll
-    for (int h = 0; h < kSub; ++h) {
-#pragma unroll
-      for (int kk = 0; kk < kTileN / 16; ++kk) {
-        // A = P from tensor memory, 16 keys = 8 columns; B = V: head_dim contiguous (MN-major), 16 keys = 2048 bytes
-        const uint64_t b_desc = ptx::make_smem_desc_sw128(v_base + h * kSubBytes + kk * 2048, 1024, 1024);
-        ptx::mma_bf16_ts(o_tmem + h * 64, p_tmem + kk * 8, b_desc, idesc_pv, (n > 1) || (kk > 0));
-      }
+    for (int kk = 0; kk < kTileN / 16; ++kk) {
+      // A = P from tensor memory, 16 keys = 8 columns; B = V: head_dim contiguous (MN-major), 16 keys = 2048 bytes
+      const uint64_t b_desc = ptx::make_smem_desc_sw128(v_base + kk * 2048, kHalfStep, 1024);
+      ptx::mma_bf16_ts(o_tmem, p_tmem + kk * 8, b_desc, idesc_pv, (n > 1) || (kk > 0));
     }
     ptx::mma_commit(&sm.pv_done[s]);
     trace_event(sm, 500 + n);
