@@ -119,8 +119,9 @@ def test_cyclic_gradients_on_the_tensor_cores(stride, residue, length, heads, kv
         assert_parity(g.float(), s.float(), what=f"{name} against the SIMT family", **BF16_TOL)
 
 
+@pytest.mark.parametrize("masked", [False, True])
 @pytest.mark.parametrize("D", [128, 96])
-def test_dense_strict_gradients_with_nan_capacity(D):
+def test_dense_strict_gradients_with_nan_capacity(D, masked):
     """Several query tiles per key tile, grouped heads, and NaN in the slots no query may read."""
     torch.manual_seed(10)
     B, H, HKV, Q, N = 2, 4, 2, 300, 700
@@ -128,16 +129,21 @@ def test_dense_strict_gradients_with_nan_capacity(D):
     starts = lengths - Q
     q, probe = (torch.randn(B, H, Q, D).bfloat16() for _ in range(2))
     k, v = (torch.randn(B, HKV, N, D).bfloat16() for _ in range(2))
+    key_mask = (torch.rand(B, N) > 0.3) if masked else None
     kn, vn = k.clone(), v.clone()
     for b in range(B):
         kn[b, :, int(lengths[b]):] = float("nan")
         vn[b, :, int(lengths[b]):] = float("nan")
+        if masked:
+            kn[b][:, ~key_mask[b]] = float("nan")
+            vn[b][:, ~key_mask[b]] = float("nan")
     qq, kk, vv = (t.cuda().requires_grad_() for t in (q, kn, vn))
-    out = strict_causal_attention(qq, kk, vv, query_start=starts.cuda(), kv_lengths=lengths.cuda(), backend="sm100_tcgen05")
+    out = strict_causal_attention(qq, kk, vv, query_start=starts.cuda(), kv_lengths=lengths.cuda(), backend="sm100_tcgen05",
+                                  key_mask=None if key_mask is None else key_mask.cuda())
     grads = torch.autograd.grad(out, (qq, kk, vv), probe.transpose(1, 2).cuda())
     assert _native.device_status(True) == 0
     qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
-    exp = oracle.strict_causal_oracle(qo, ko, vo, query_start=starts, kv_lengths=lengths)
+    exp = oracle.strict_causal_oracle(qo, ko, vo, query_start=starts, kv_lengths=lengths, key_mask=key_mask)
     exp_grads = torch.autograd.grad(exp, (qo, ko, vo), probe.transpose(1, 2).double())
     for g, e, name in zip(grads, exp_grads, ("dq", "dk", "dv")):
         assert torch.isfinite(g).all(), name

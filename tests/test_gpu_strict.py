@@ -5,7 +5,7 @@ import torch
 
 from helpers import BF16_TOL, F32_TOL, Golden, assert_parity, geometric_documents
 from oracle import attention_oracle as oracle
-from white_matter_b200 import prepare_strict_causal_metadata, strict_causal_attention
+from white_matter_b200 import _native, prepare_strict_causal_metadata, strict_causal_attention
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not torch.cuda.is_available(), reason="requires CUDA")]
 G = Golden()
@@ -212,8 +212,6 @@ def test_softmax_scale_is_honoured_on_every_route(pads, backend):
 def test_gradients_with_nan_in_unused_capacity(length, masked, backend):
     """Cached-prefix prefill with gradients: slots at or beyond kv_lengths hold NaN; the gradients must be finite,
     match the oracle, and be exactly zero for the slots nobody sees."""
-    if masked and backend == "sm100_tcgen05":
-        pytest.skip("the tcgen05 gradient kernels take no key_mask (the forward does, see the test below)")
     torch.manual_seed(41)
     B, H, N, D = 2, 2, 333, 64
     lengths = torch.tensor([150, 290])
@@ -278,11 +276,16 @@ def test_key_mask_prefill_on_the_tcgen05_forward(length, heads, kv_heads, dummy)
     assert torch.isfinite(out).all()
     assert_parity(out.float(), exp, what="tcgen05 forward with key_mask", **BF16_TOL)
     assert_parity(out.float(), simt.float(), what="tcgen05 vs simt", **BF16_TOL)
-    # with gradients the default backend runs this forward and the SIMT gradient kernels: one function
-    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, k, v))
-    out2 = strict_causal_attention(qq, kk, vv, **args)
+    # gradients: the key-stationary tensor-core backward clears the rows the mask removes in shared memory as well
+    qq, kk, vv = (t.cuda().requires_grad_() for t in (q, kn, vn))
+    out2 = strict_causal_attention(qq, kk, vv, backend="sm100_tcgen05", **args)
     probe = torch.randn_like(out2)
     grads = torch.autograd.grad(out2, (qq, kk, vv), probe)
+    assert _native.device_status(True) == 0
+    for b in range(B):
+        assert all(torch.isfinite(g).all() for g in grads)
+        assert grads[1][b][:, ~key_mask[b].cuda()].abs().max().item() == 0
+        assert grads[2][b][:, ~key_mask[b].cuda()].abs().max().item() == 0
     qo, ko, vo = (t.double().requires_grad_() for t in (q, k, v))
     exp2 = oracle.strict_causal_oracle(qo, ko, vo, query_start=starts, kv_lengths=lengths, use_dummy_token=dummy, key_mask=key_mask)
     exp_grads = torch.autograd.grad(exp2, (qo, ko, vo), probe.cpu().double())

@@ -3,7 +3,8 @@
 //
 // These kernels are the fp32 path (results within 1e-4 of an fp64 evaluation)
 // and the path for shapes the tensor-core kernels do not take (head sizes
-// other than 64, gathered key lists, key_mask).  One group of TPR lanes owns
+// other than 64, 96 and 128, gathered key lists, rows that are not 16-byte
+// aligned).  One group of TPR lanes owns
 // one query row (forward, dQ) or one key row (dK/dV); each lane keeps 16 of
 // the row's head_dim values in registers; the opposite operand is staged in
 // shared memory as fp32, a tile of 32 rows at a time, and broadcast.

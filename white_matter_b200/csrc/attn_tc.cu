@@ -421,8 +421,7 @@ int tc_device_status(bool reset) {
 }
 
 bool tc_bwd_supported(const wm_attn_args& a) {
-  // the gradient kernels take no key mask
-  if (!tc_fwd_supported(a) || a.key_mask != nullptr) return false;
+  if (!tc_fwd_supported(a)) return false;
   if (a.dout == nullptr) return true;  // shape query before the tensors exist
   if (!tma_ok(a.dout, a.dout_strides, a.batch, a.q_heads, a.q_len)) return false;
   if (!tma_ok(a.dk, a.dk_strides, a.batch, a.kv_heads, a.k_len)) return false;
@@ -437,9 +436,9 @@ bool tc_bwd_supported(const wm_attn_args& a) {
   return true;
 }
 
-// The short-query pipeline keeps both query tiles of a (batch, head) resident (heads of 64 only).
+// The short-query pipeline keeps both query tiles of a (batch, head) resident (heads of 64, no key mask).
 bool bwd_short_queries(const wm_attn_args& a) {
-  return a.head_dim == kHeadDim && a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
+  return a.head_dim == kHeadDim && a.key_mask == nullptr && a.q_len <= 2 * kTileM && a.q_heads == a.kv_heads && a.k_len <= 128 * kTileN;
 }
 
 size_t tc_attn_bwd_workspace(const wm_attn_args& a) {

@@ -47,6 +47,7 @@ struct BwdShared {
   int key_seg[kTileN];
   int key_end[kTileN];
   int summary[4][4];  // per warp: min seg, max seg, min end, max end
+  uint32_t key_keep[4];  // key_mask of the tile, one bit per key slot (all ones without a mask)
   int row_first, row_end;
   uint32_t tmem_base;
   int abort_flag;
@@ -223,9 +224,11 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
   const bool docs = a.q_seg != nullptr;
   const GroupCtx g = group_ctx(a, 0);
 
-  // prologue: key rows at or beyond the last visible slot may hold anything; clear them for the MMAs
+  // prologue: key rows at or beyond the last visible slot, and rows the key mask removes, may hold anything;
+  // clear them for the MMAs
+  const bool masked = a.key_mask != nullptr;
   if (!wait_or_abort(sm, &sm.kv_full, 0, 60)) return;
-  if (j0 + t >= w.kvis) {
+  if (j0 + t >= w.kvis || !((sm.key_keep[t >> 5] >> (t & 31)) & 1u)) {
 #pragma unroll
     for (int h = 0; h < Cfg::kSub; ++h) {
       uint4* krow = reinterpret_cast<uint4*>(sm.k + h * kSubBytes + t * 128);
@@ -265,7 +268,7 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
       dl = delta[stat];
     }
     bool none = !live || j0 >= rb.hi;
-    bool full = live && j0 + kTileN <= rb.hi;
+    bool full = live && j0 + kTileN <= rb.hi && !masked;
     bool own_doc = !docs;  // the tile lies inside the row's own document: only the causal bound can cut it
     if (docs && !none) {
       const bool uniform = smin == smax;
@@ -283,6 +286,7 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
 #pragma unroll 1
     for (int c = 0; c < kTileN / 32; ++c) {
       uint32_t xs[32], ys[32];
+      const uint32_t keep = masked ? sm.key_keep[c] : 0xffffffffu;
       ptx::tmem_ld32(tmem + lane_base + c * 32, xs);
       ptx::tmem_ld32(tmem + kTileN + lane_base + c * 32, ys);
       ptx::tmem_wait_ld();
@@ -293,7 +297,7 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int col = c * 32 + 2 * e + u;
-          bool vis = !none && (full || col < lim);
+          bool vis = !none && (full || (col < lim && ((keep >> (2 * e + u)) & 1u)));
           if (!own_doc) vis = vis & doc_visible_flat(rb, j0 + col, sm.key_seg[col], sm.key_end[col]);
           const float p = fast_exp2(fmaf(__uint_as_float(xs[2 * e + u]), sl2, -lse2));
           pv[u] = vis ? p : 0.f;
@@ -385,6 +389,13 @@ __global__ void __launch_bounds__(kThreadsFwd, 1)
   if (tid == 0) {
     sm.abort_flag = 0;
     sm.epoch = epoch;
+  }
+  if (tid < kSoftmaxThreads) {
+    bool keep = true;
+    if (a.key_mask != nullptr)
+      keep = j0 + tid < a.k_len && a.key_mask[static_cast<long long>(batch) * a.k_len + j0 + tid] != 0;
+    const uint32_t word = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) sm.key_keep[warp] = word;
   }
   if (tid < kSoftmaxThreads && docs) {
     int seg = INT_MIN, end = 0;
