@@ -68,6 +68,18 @@ def test_bf16_matches_reference(case, backend):
             assert_parity(g.float(), e, what=name, **BF16_TOL)
 
 
+TENSOR_CORE_CASES = [n for n in G.names("strict") if G.cases[n]["D"] == 64 and G.cases[n]["T"] > 1]
+
+
+@pytest.mark.parametrize("case", TENSOR_CORE_CASES)
+def test_bf16_reference_cases_on_the_tensor_core_kernels(case):
+    """Every stored strict case with several queries and heads of 64 -- dense, truncated, packed, padded, Jacobi, with
+    and without the dummy slot -- runs the tcgen05 kernels when they are forced (a problem they cannot take is an
+    error then), forward and gradients."""
+    test_bf16_matches_reference(case, "sm100_tcgen05")
+    assert _native.device_status(True) == 0
+
+
 @pytest.mark.parametrize("dummy", [False, True])
 def test_unused_capacity_may_hold_nan(dummy):
     # upstream tests/unit/test_strict_causal_attention.py:80-94
