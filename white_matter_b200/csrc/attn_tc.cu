@@ -28,7 +28,6 @@ constexpr int kTileN = 128;
 constexpr int kHeadDim = 64;
 constexpr int kStages = 3;
 constexpr int kSoftmaxThreads = 128;
-constexpr int kThreadsFwd = 192;  // key-stationary backward: 4 compute warps + producer + MMA
 constexpr uint32_t kTileBytes = kTileN * kHeadDim * 2;  // 16 KB: one Q, K or V tile
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
@@ -452,12 +451,13 @@ template <int D>
 int launch_bwd_key_tiles(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
                          const CUtensorMap& map_g, const wm_attn_args& a, const float* delta, float* dq_acc,
                          cudaStream_t stream) {
-  const size_t smem = sizeof(BwdShared<D>) + 1024;
+  constexpr size_t smem = sizeof(BwdShared<D>) + 1024;
+  static_assert(smem <= 227 * 1024, "the key-stationary backward has outgrown the shared memory of a block");
   static std::atomic<bool> configured[kMaxDevices];
   const int status = allow_shared_memory(attn_bwd_tc_kernel<D>, configured, smem);
   if (status != WM_OK) return status;
   dim3 grid((a.k_len + kTileN - 1) / kTileN, a.kv_heads, a.batch);
-  attn_bwd_tc_kernel<D><<<grid, kThreadsFwd, smem, stream>>>(map_q, map_k, map_v, map_g, a, delta, dq_acc, next_epoch());
+  attn_bwd_tc_kernel<D><<<grid, BwdCfg<D>::kThreads, smem, stream>>>(map_q, map_k, map_v, map_g, a, delta, dq_acc, next_epoch());
   count_launch();
   return cuda_check(cudaGetLastError(), "attn_bwd_tc_kernel");
 }

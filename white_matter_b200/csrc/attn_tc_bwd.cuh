@@ -29,6 +29,12 @@ struct BwdCfg {
   static constexpr uint32_t kBytes = kTileN * D * 2;  // one Q, K, V or dO tile
   static constexpr int kQStages = D == 64 ? 2 : 1;
   static constexpr bool kDqOverS = D > 64;
+  // D = 64 has the room (shared memory for a second P/dS pair, 64 tensor-memory columns for dQ) to overlap the pairs
+  // of a walk: S/dP of the next pair are issued before the gradient products of this one, and four more warps take
+  // dQ out, so the compute warps go from one pair straight to the next
+  static constexpr bool kOverlap = D == 64;
+  static constexpr int kPds = kOverlap ? 2 : 1;
+  static constexpr int kThreads = kOverlap ? 320 : 192;
   static constexpr uint32_t kColDv = 2 * kTileN, kColDk = 2 * kTileN + D;
   static constexpr uint32_t kColDq = kDqOverS ? 0 : 2 * kTileN + 2 * D;
 };
@@ -39,11 +45,11 @@ struct BwdShared {
   unsigned char v[BwdCfg<D>::kBytes];
   unsigned char q[BwdCfg<D>::kQStages][BwdCfg<D>::kBytes];
   unsigned char g[BwdCfg<D>::kQStages][BwdCfg<D>::kBytes];  // dO tiles
-  unsigned char p[2 * kTileBytes];
-  unsigned char ds[2 * kTileBytes];
+  unsigned char p[BwdCfg<D>::kPds][2 * kTileBytes];
+  unsigned char ds[BwdCfg<D>::kPds][2 * kTileBytes];
   uint64_t kv_full, kv_ready;
   uint64_t qg_full[BwdCfg<D>::kQStages], qg_empty[BwdCfg<D>::kQStages];
-  uint64_t sdp_full, pds_full, mma_done, dq_full, dq_free;
+  uint64_t sdp_full, pds_full, mma_done[BwdCfg<D>::kPds], dq_full, dq_free;
   int key_seg[kTileN];
   int key_end[kTileN];
   int summary[4][4];  // per warp: min seg, max seg, min end, max end
@@ -161,13 +167,13 @@ __device__ __forceinline__ void bwd_mma(BwdShared<D>& sm, uint32_t tmem, const B
   constexpr uint32_t idesc_t = ptx::make_idesc_bf16(kTileN, D, 1, 1);           // P^T dO, dS^T Q
   constexpr uint32_t idesc_q = ptx::make_idesc_bf16(kTileM, D, 0, 1);           // dS K
   const uint32_t k_base = ptx::smem_u32(sm.k), v_base = ptx::smem_u32(sm.v);
-  const uint32_t p_base = ptx::smem_u32(sm.p), ds_base = ptx::smem_u32(sm.ds);
-  for (int it = 0; it < w.n_iter; ++it) {
+  // S = Q K^T and dP = dO V^T of pair `it` into their tensor-memory columns
+  auto scores = [&](int it) -> bool {
     const int s = it % kBwdStages;
-    if (!wait_or_abort(sm, &sm.qg_full[s], (it / kBwdStages) & 1, 51)) return;
+    if (!wait_or_abort(sm, &sm.qg_full[s], (it / kBwdStages) & 1, 51)) return false;
     if (Cfg::kDqOverS) {
       // dQ of the previous pair lives in the columns of S until the compute threads have taken it out
-      if (!wait_or_abort(sm, &sm.dq_free, (it & 1) ^ 1, 54)) return;
+      if (!wait_or_abort(sm, &sm.dq_free, (it & 1) ^ 1, 54)) return false;
     }
     ptx::tc_fence_after();
     const uint32_t q_base = ptx::smem_u32(sm.q[s]), g_base = ptx::smem_u32(sm.g[s]);
@@ -184,8 +190,19 @@ __device__ __forceinline__ void bwd_mma(BwdShared<D>& sm, uint32_t tmem, const B
                        ptx::make_smem_desc_sw128(v_base + at, 16, 1024), idesc_s, kk > 0);
     }
     ptx::mma_commit(&sm.sdp_full);
+    return true;
+  };
+  if (Cfg::kOverlap && w.n_iter > 0 && !scores(0)) return;
+  for (int it = 0; it < w.n_iter; ++it) {
+    const int s = it % kBwdStages;
+    const int pb = Cfg::kOverlap ? (it & 1) : 0;  // P/dS buffer of the pair
+    if (!Cfg::kOverlap && !scores(it)) return;
     if (!wait_or_abort(sm, &sm.pds_full, it & 1, 52)) return;
     ptx::tc_fence_after();
+    // the compute threads have read S and dP: the next pair's go out before this pair's gradient products
+    if (Cfg::kOverlap && it + 1 < w.n_iter && !scores(it + 1)) return;
+    const uint32_t q_base = ptx::smem_u32(sm.q[s]), g_base = ptx::smem_u32(sm.g[s]);
+    const uint32_t p_base = ptx::smem_u32(sm.p[pb]), ds_base = ptx::smem_u32(sm.ds[pb]);
     // the gradient products span all D result columns in one instruction: the MN-major B operand steps from one
     // 64-column sub-tile to the next by its leading-dimension offset, like the two 64-key halves of P and dS
 #pragma unroll
@@ -206,8 +223,69 @@ __device__ __forceinline__ void bwd_mma(BwdShared<D>& sm, uint32_t tmem, const B
                        ptx::make_smem_desc_sw128(ds_base + (kk >> 2) * kTileBytes + (kk & 3) * 32, 16, 1024),
                        ptx::make_smem_desc_sw128(k_base + kk * 2048, kHalfStep, 1024), idesc_q, kk > 0);
     ptx::mma_commit(&sm.qg_empty[s]);
-    ptx::mma_commit(&sm.mma_done);
+    ptx::mma_commit(&sm.mma_done[pb]);
     ptx::mma_commit(&sm.dq_full);
+  }
+}
+
+// Whether query row i (bounds rb) sees nothing of the block's key tile.
+__device__ __forceinline__ bool bwd_row_sees_nothing(const RowBound& rb, bool live, int j0, bool docs, int smin, int smax) {
+  bool none = !live || j0 >= rb.hi;
+  if (docs && !none && smin == smax && smin != -1 && smin != rb.seg) none = true;
+  return none;
+}
+
+// dQ of one pair: from tensor memory into the fp32 accumulator in global memory (thread = query row)
+template <int D>
+__device__ __forceinline__ void bwd_dq_out(const wm_attn_args& a, uint32_t tmem_dq, float* dq_acc, long long stat, bool wanted) {
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t raw[32];
+    ptx::tmem_ld32(tmem_dq + c * 32, raw);
+    ptx::tmem_wait_ld();
+    if (wanted && c * 32 < a.head_dim) {
+      float* dst = dq_acc + stat * a.head_dim + c * 32;
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        red_add_v4(dst + 4 * e, __uint_as_float(raw[4 * e]), __uint_as_float(raw[4 * e + 1]),
+                   __uint_as_float(raw[4 * e + 2]), __uint_as_float(raw[4 * e + 3]));
+    }
+  }
+}
+
+// The warps that take dQ out when the pairs overlap (thread = query row = TMEM lane of its warp's quarter).
+template <int D>
+__device__ __forceinline__ void bwd_drain(BwdShared<D>& sm, const wm_attn_args& a, uint32_t tmem, const BwdWalk& w,
+                                          float* dq_acc, int j0, int kv_head, int batch) {
+  using Cfg = BwdCfg<D>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = (warp & 3) * 32 + lane;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const bool docs = a.q_seg != nullptr;
+  const GroupCtx g = group_ctx(a, 0);
+  int smin = 0, smax = 0;
+  if (docs) {
+    smin = min(min(sm.summary[0][0], sm.summary[1][0]), min(sm.summary[2][0], sm.summary[3][0]));
+    smax = max(max(sm.summary[0][1], sm.summary[1][1]), max(sm.summary[2][1], sm.summary[3][1]));
+  }
+  for (int it = 0; it < w.n_iter; ++it) {
+    int head, qt;
+    bwd_iter_coords(w, it, kv_head, head, qt);
+    const int i = qt * kTileM + row;
+    const bool live = i < a.q_len;
+    RowBound rb;
+    rb.lo = 0;
+    rb.hi = 0;
+    rb.seg = 0;
+    rb.qi = i;
+    if (live) rb = row_bound(a, g, batch, i);
+    const bool none = bwd_row_sees_nothing(rb, live, j0, docs, smin, smax);
+    const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + i;
+    if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return;
+    ptx::tc_fence_after();
+    bwd_dq_out<D>(a, tmem + Cfg::kColDq + lane_base, dq_acc, stat, live && !none);
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(&sm.dq_free);
   }
 }
 
@@ -278,10 +356,16 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
     }
     if (!wait_or_abort(sm, &sm.sdp_full, it & 1, 61)) return;
     ptx::tc_fence_after();
-    // the shared P / dS tiles were last read by the MMAs of the previous iteration
-    if (it > 0 && !wait_or_abort(sm, &sm.mma_done, (it - 1) & 1, 62)) return;
-    unsigned char* prow = sm.p + (t >> 3) * 1024 + (t & 7) * 128;
-    unsigned char* drow = sm.ds + (t >> 3) * 1024 + (t & 7) * 128;
+    // the shared P / dS tiles were last read by the gradient products of the pair that used them before: the
+    // previous pair, or with two buffers the one before that
+    const int pb = Cfg::kOverlap ? (it & 1) : 0;
+    if (Cfg::kOverlap) {
+      if (it >= 2 && !wait_or_abort(sm, &sm.mma_done[pb], ((it >> 1) & 1) ^ 1, 62)) return;
+    } else {
+      if (it > 0 && !wait_or_abort(sm, &sm.mma_done[0], (it - 1) & 1, 62)) return;
+    }
+    unsigned char* prow = sm.p[pb] + (t >> 3) * 1024 + (t & 7) * 128;
+    unsigned char* drow = sm.ds[pb] + (t >> 3) * 1024 + (t & 7) * 128;
     const int lim = rb.hi - j0;
 #pragma unroll 1
     for (int c = 0; c < kTileN / 32; ++c) {
@@ -317,27 +401,23 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
     ptx::fence_async_shared();
     ptx::tc_fence_before();
     ptx::mbar_arrive(&sm.pds_full);
-    // dQ of this (query tile, key tile) pair: add to the fp32 accumulator
-    if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return;
-    ptx::tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t raw[32];
-      ptx::tmem_ld32(tmem + Cfg::kColDq + lane_base + c * 32, raw);
-      ptx::tmem_wait_ld();
-      if (live && !none && c * 32 < a.head_dim) {
-        float* dst = dq_acc + stat * a.head_dim + c * 32;
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          red_add_v4(dst + 4 * e, __uint_as_float(raw[4 * e]), __uint_as_float(raw[4 * e + 1]),
-                     __uint_as_float(raw[4 * e + 2]), __uint_as_float(raw[4 * e + 3]));
-      }
+    if (!Cfg::kOverlap) {
+      // dQ of this (query tile, key tile) pair: add to the fp32 accumulator
+      if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return;
+      ptx::tc_fence_after();
+      bwd_dq_out<D>(a, tmem + Cfg::kColDq + lane_base, dq_acc, stat, live && !none);
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&sm.dq_free);
     }
-    ptx::tc_fence_before();
-    ptx::mbar_arrive(&sm.dq_free);
+  }
+  if (Cfg::kOverlap && w.n_iter > 0) {
+    // the gradient products of the last pair (their commit covers every earlier product)
+    const int last = w.n_iter - 1;
+    if (!wait_or_abort(sm, &sm.mma_done[last & 1], (last >> 1) & 1, 64)) return;
+    ptx::tc_fence_after();
   }
 
-  // epilogue: dV and dK rows of this key tile (dq_full of the last iteration covers every earlier MMA)
+  // epilogue: dV and dK rows of this key tile (the last pair's products are complete: dq_full, or mma_done above)
   const int j = j0 + t;
   uint4* dvrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dv) + batch * a.dv_strides[0] +
                                           kv_head * a.dv_strides[1] + static_cast<long long>(j) * a.dv_strides[2]);
@@ -371,7 +451,7 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreadsFwd, 1)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_g,
                        const wm_attn_args a, const float* delta, float* dq_acc, const int epoch) {
@@ -472,7 +552,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1)
     }
     ptx::mbar_init(&sm.sdp_full, 1);
     ptx::mbar_init(&sm.pds_full, kSoftmaxThreads);
-    ptx::mbar_init(&sm.mma_done, 1);
+    for (int b = 0; b < BwdCfg<D>::kPds; ++b) ptx::mbar_init(&sm.mma_done[b], 1);
     ptx::mbar_init(&sm.dq_full, 1);
     ptx::mbar_init(&sm.dq_free, kSoftmaxThreads);
     ptx::mbar_fence_init();
@@ -489,8 +569,10 @@ __global__ void __launch_bounds__(kThreadsFwd, 1)
     bwd_compute(sm, a, tmem, w, delta, dq_acc, j0, kv_head, batch);
   } else if (warp == 4) {
     if (lane == 0) bwd_producer(sm, &map_q, &map_k, &map_v, &map_g, w, j0, kv_head, batch);
-  } else {
+  } else if (warp == 5) {
     if (lane == 0) bwd_mma(sm, tmem, w);
+  } else {
+    bwd_drain(sm, a, tmem, w, dq_acc, j0, kv_head, batch);
   }
   ptx::tc_fence_before();
   __syncthreads();
