@@ -30,11 +30,15 @@ struct BwdCfg {
   static constexpr int kQStages = D == 64 ? 2 : 1;
   static constexpr bool kDqOverS = D > 64;
   // D = 64 has the room (shared memory for a second P/dS pair, 64 tensor-memory columns for dQ) to overlap the pairs
-  // of a walk: S/dP of the next pair are issued before the gradient products of this one, and four more warps take
-  // dQ out, so the compute warps go from one pair straight to the next
+  // of a walk: S/dP of the next pair are issued before the gradient products of this one, the compute warps go from
+  // one pair straight to the next and take dQ out one pair late, when it has long been formed.
   static constexpr bool kOverlap = D == 64;
   static constexpr int kPds = kOverlap ? 2 : 1;
-  static constexpr int kThreads = kOverlap ? 320 : 192;
+  // Eight compute warps at every head size: two per quarter of the rows, each with one half of the columns (the
+  // backward needs no row maximum, so the halves exchange nothing).
+  static constexpr int kComputeWarps = 8;
+  static constexpr int kSplit = kComputeWarps / 4;           // warps per row: each takes kTileN / kSplit columns
+  static constexpr int kThreads = (kComputeWarps + 2) * 32;  // + producer + MMA issuer
   static constexpr uint32_t kColDv = 2 * kTileN, kColDk = 2 * kTileN + D;
   static constexpr uint32_t kColDq = kDqOverS ? 0 : 2 * kTileN + 2 * D;
 };
@@ -235,11 +239,12 @@ __device__ __forceinline__ bool bwd_row_sees_nothing(const RowBound& rb, bool li
   return none;
 }
 
-// dQ of one pair: from tensor memory into the fp32 accumulator in global memory (thread = query row)
+// dQ of one pair: from tensor memory into the fp32 accumulator in global memory (thread = query row; pieces of 32
+// columns from `first`, `count` of them)
 template <int D>
-__device__ __forceinline__ void bwd_dq_out(const wm_attn_args& a, uint32_t tmem_dq, float* dq_acc, long long stat, bool wanted) {
-#pragma unroll
-  for (int c = 0; c < D / 32; ++c) {
+__device__ __forceinline__ void bwd_dq_out(const wm_attn_args& a, uint32_t tmem_dq, float* dq_acc, long long stat, bool wanted,
+                                           int first, int count) {
+  for (int c = first; c < first + count; ++c) {
     uint32_t raw[32];
     ptx::tmem_ld32(tmem_dq + c * 32, raw);
     ptx::tmem_wait_ld();
@@ -253,73 +258,42 @@ __device__ __forceinline__ void bwd_dq_out(const wm_attn_args& a, uint32_t tmem_
   }
 }
 
-// The warps that take dQ out when the pairs overlap (thread = query row = TMEM lane of its warp's quarter).
-template <int D>
-__device__ __forceinline__ void bwd_drain(BwdShared<D>& sm, const wm_attn_args& a, uint32_t tmem, const BwdWalk& w,
-                                          float* dq_acc, int j0, int kv_head, int batch) {
-  using Cfg = BwdCfg<D>;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = (warp & 3) * 32 + lane;
-  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  const bool docs = a.q_seg != nullptr;
-  const GroupCtx g = group_ctx(a, 0);
-  int smin = 0, smax = 0;
-  if (docs) {
-    smin = min(min(sm.summary[0][0], sm.summary[1][0]), min(sm.summary[2][0], sm.summary[3][0]));
-    smax = max(max(sm.summary[0][1], sm.summary[1][1]), max(sm.summary[2][1], sm.summary[3][1]));
-  }
-  for (int it = 0; it < w.n_iter; ++it) {
-    int head, qt;
-    bwd_iter_coords(w, it, kv_head, head, qt);
-    const int i = qt * kTileM + row;
-    const bool live = i < a.q_len;
-    RowBound rb;
-    rb.lo = 0;
-    rb.hi = 0;
-    rb.seg = 0;
-    rb.qi = i;
-    if (live) rb = row_bound(a, g, batch, i);
-    const bool none = bwd_row_sees_nothing(rb, live, j0, docs, smin, smax);
-    const long long stat = (static_cast<long long>(batch) * a.q_heads + head) * a.q_len + i;
-    if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return;
-    ptx::tc_fence_after();
-    bwd_dq_out<D>(a, tmem + Cfg::kColDq + lane_base, dq_acc, stat, live && !none);
-    ptx::tc_fence_before();
-    ptx::mbar_arrive(&sm.dq_free);
-  }
-}
-
 // compute threads of the backward kernel: thread t owns query row t of the current query tile (and, in
 // the prologue / epilogue, key row t of the CTA's key tile)
 template <int D>
 __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args& a, uint32_t tmem, const BwdWalk& w,
                                             const float* delta, float* dq_acc, int j0, int kv_head, int batch) {
   using Cfg = BwdCfg<D>;
-  const int t = threadIdx.x;
-  const int warp = t >> 5;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = (warp & 3) * 32 + lane;  // query row of the pair (and key row of the block's tile) = TMEM lane
+  const int half = warp >> 2;            // which part of the columns (0 when one warp has the whole row)
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   const float sl2 = a.scale * kLog2e;
   const bool docs = a.q_seg != nullptr;
   const GroupCtx g = group_ctx(a, 0);
+  constexpr int kPieces = kTileN / 32 / Cfg::kSplit;    // 32-column pieces of S/dP per thread
+  constexpr int kOutPieces = D / 32 / Cfg::kSplit;      // 32-column pieces of dQ, dK and dV per thread
 
   // prologue: key rows at or beyond the last visible slot, and rows the key mask removes, may hold anything;
-  // clear them for the MMAs
+  // clear them for the MMAs (one thread per key row)
   const bool masked = a.key_mask != nullptr;
-  if (!wait_or_abort(sm, &sm.kv_full, 0, 60)) return;
-  if (j0 + t >= w.kvis || !((sm.key_keep[t >> 5] >> (t & 31)) & 1u)) {
+  if (half == 0) {
+    if (!wait_or_abort(sm, &sm.kv_full, 0, 60)) return;
+    if (j0 + t >= w.kvis || !((sm.key_keep[t >> 5] >> (t & 31)) & 1u)) {
 #pragma unroll
-    for (int h = 0; h < Cfg::kSub; ++h) {
-      uint4* krow = reinterpret_cast<uint4*>(sm.k + h * kSubBytes + t * 128);
-      uint4* vrow = reinterpret_cast<uint4*>(sm.v + h * kSubBytes + t * 128);
+      for (int h = 0; h < Cfg::kSub; ++h) {
+        uint4* krow = reinterpret_cast<uint4*>(sm.k + h * kSubBytes + t * 128);
+        uint4* vrow = reinterpret_cast<uint4*>(sm.v + h * kSubBytes + t * 128);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        krow[c] = make_uint4(0, 0, 0, 0);
-        vrow[c] = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < 8; ++c) {
+          krow[c] = make_uint4(0, 0, 0, 0);
+          vrow[c] = make_uint4(0, 0, 0, 0);
+        }
       }
     }
+    ptx::fence_async_shared();
+    ptx::mbar_arrive(&sm.kv_ready);
   }
-  ptx::fence_async_shared();
-  ptx::mbar_arrive(&sm.kv_ready);
 
   int smin = 0, smax = 0, emin = 0;
   if (docs) {
@@ -327,6 +301,18 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
     smax = max(max(sm.summary[0][1], sm.summary[1][1]), max(sm.summary[2][1], sm.summary[3][1]));
     emin = min(min(sm.summary[0][2], sm.summary[1][2]), min(sm.summary[2][2], sm.summary[3][2]));
   }
+
+  // dQ of pair `it` out of tensor memory (this thread's pieces of its row)
+  auto take_dq = [&](int it, long long stat, bool wanted) -> bool {
+    if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return false;
+    ptx::tc_fence_after();
+    bwd_dq_out<D>(a, tmem + Cfg::kColDq + lane_base, dq_acc, stat, wanted, half * kOutPieces, kOutPieces);
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(&sm.dq_free);
+    return true;
+  };
+  long long late_stat = 0;  // the pair whose dQ is still to be taken out (overlapping pairs)
+  bool late_wanted = false;
 
   for (int it = 0; it < w.n_iter; ++it) {
     int head, qt;
@@ -368,7 +354,7 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
     unsigned char* drow = sm.ds[pb] + (t >> 3) * 1024 + (t & 7) * 128;
     const int lim = rb.hi - j0;
 #pragma unroll 1
-    for (int c = 0; c < kTileN / 32; ++c) {
+    for (int c = half * kPieces; c < (half + 1) * kPieces; ++c) {
       uint32_t xs[32], ys[32];
       const uint32_t keep = masked ? sm.key_keep[c] : 0xffffffffu;
       ptx::tmem_ld32(tmem + lane_base + c * 32, xs);
@@ -401,30 +387,29 @@ __device__ __forceinline__ void bwd_compute(BwdShared<D>& sm, const wm_attn_args
     ptx::fence_async_shared();
     ptx::tc_fence_before();
     ptx::mbar_arrive(&sm.pds_full);
-    if (!Cfg::kOverlap) {
-      // dQ of this (query tile, key tile) pair: add to the fp32 accumulator
-      if (!wait_or_abort(sm, &sm.dq_full, it & 1, 63)) return;
-      ptx::tc_fence_after();
-      bwd_dq_out<D>(a, tmem + Cfg::kColDq + lane_base, dq_acc, stat, live && !none);
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(&sm.dq_free);
+    if (Cfg::kOverlap) {
+      // dQ of the pair before this one: its products were issued while this pair was computed
+      if (it > 0 && !take_dq(it - 1, late_stat, late_wanted)) return;
+      late_stat = stat;
+      late_wanted = live && !none;
+    } else {
+      if (!take_dq(it, stat, live && !none)) return;
     }
   }
   if (Cfg::kOverlap && w.n_iter > 0) {
-    // the gradient products of the last pair (their commit covers every earlier product)
-    const int last = w.n_iter - 1;
-    if (!wait_or_abort(sm, &sm.mma_done[last & 1], (last >> 1) & 1, 64)) return;
+    // the last pair's dQ; its barrier covers every product of the walk
+    if (!take_dq(w.n_iter - 1, late_stat, late_wanted)) return;
     ptx::tc_fence_after();
   }
 
-  // epilogue: dV and dK rows of this key tile (the last pair's products are complete: dq_full, or mma_done above)
+  // epilogue: dV and dK rows of this key tile (dq_full of the last pair covers every earlier product); this thread
+  // writes its pieces of key row t
   const int j = j0 + t;
   uint4* dvrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dv) + batch * a.dv_strides[0] +
                                           kv_head * a.dv_strides[1] + static_cast<long long>(j) * a.dv_strides[2]);
   uint4* dkrow = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.dk) + batch * a.dk_strides[0] +
                                           kv_head * a.dk_strides[1] + static_cast<long long>(j) * a.dk_strides[2]);
-#pragma unroll
-  for (int c = 0; c < D / 32; ++c) {
+  for (int c = half * kOutPieces; c < (half + 1) * kOutPieces; ++c) {
     uint32_t dv_pack[16], dk_pack[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) dv_pack[e] = dk_pack[e] = 0u;
@@ -551,13 +536,14 @@ __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
       ptx::mbar_init(&sm.qg_empty[s], 1);
     }
     ptx::mbar_init(&sm.sdp_full, 1);
-    ptx::mbar_init(&sm.pds_full, kSoftmaxThreads);
+    ptx::mbar_init(&sm.pds_full, BwdCfg<D>::kComputeWarps * 32);
     for (int b = 0; b < BwdCfg<D>::kPds; ++b) ptx::mbar_init(&sm.mma_done[b], 1);
     ptx::mbar_init(&sm.dq_full, 1);
-    ptx::mbar_init(&sm.dq_free, kSoftmaxThreads);
+    ptx::mbar_init(&sm.dq_free, BwdCfg<D>::kComputeWarps * 32);
     ptx::mbar_fence_init();
   }
-  if (warp == 4) {
+  constexpr int kCW = BwdCfg<D>::kComputeWarps;
+  if (warp == kCW) {
     ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -565,16 +551,14 @@ __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  if (warp < 4) {
+  if (warp < kCW) {
     bwd_compute(sm, a, tmem, w, delta, dq_acc, j0, kv_head, batch);
-  } else if (warp == 4) {
+  } else if (warp == kCW) {
     if (lane == 0) bwd_producer(sm, &map_q, &map_k, &map_v, &map_g, w, j0, kv_head, batch);
-  } else if (warp == 5) {
-    if (lane == 0) bwd_mma(sm, tmem, w);
   } else {
-    bwd_drain(sm, a, tmem, w, dq_acc, j0, kv_head, batch);
+    if (lane == 0) bwd_mma(sm, tmem, w);
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 4) ptx::tmem_dealloc(tmem, kTmemCols);
+  if (warp == kCW) ptx::tmem_dealloc(tmem, kTmemCols);
 }
