@@ -502,6 +502,16 @@ def bench_jacobi(device, peaks, iters=10):
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_kind": "bf16_tflops (kernel timed alone)"},
     }
+    # gradients of the same call (the key-stationary tensor-core backward: 2048 queries per row are more than the
+    # resident backward keeps)
+    leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+    out = strict_causal_attention(*leaves, metadata=metadata)
+    probe = torch.randn_like(out)
+    grad_call = lambda: torch.autograd.grad(out, leaves, probe, retain_graph=True)
+    bwd_ms = time_steps(grad_call, iters, 3, torch.cuda.synchronize) / iters
+    del out, leaves
+    result["backward"] = {"ms": bwd_ms, "value": 10 * dim * pairs * heads / (bwd_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "kernels": "bwd_delta_kernel, attn_bwd_tc_kernel<64> (one block per key tile), bwd_dq_convert_kernel"}
     # cached-prefix Jacobi with documents: the last 512 tokens of 4096-token rows are the queries, the rest is
     # committed history; the schedule runs as dense per-row bounds plus document tables on the tensor-core kernel,
     # and as gathered index lists on the SIMT kernels
