@@ -140,10 +140,12 @@ struct FwdShared {
   uint64_t q_full;
   // s_full[i] and pv_done[i] also release K and V stage i (score buffers and stages share the ring size)
   uint64_t k_full[FwdCfg<D>::kRing], v_full[FwdCfg<D>::kRing];
-  uint64_t s_full[FwdCfg<D>::kRing], pv_done[FwdCfg<D>::kRing], p_full[2], p_seen[2], docs_full[2], sum_full;
-  int key_seg[2][2][kTileN];  // [group][tile of the group & 1]
-  int key_end[2][2][kTileN];
-  int tile_summary[2][2][4][3];
+  uint64_t s_full[FwdCfg<D>::kRing], pv_done[FwdCfg<D>::kRing], p_full[2], p_seen[2], sum_full;
+  // document id and exclusive query bound of the key slots of a tile: every softmax warp keeps its own copy
+  // ([warp][tile of its group & 1]), brought in one tile ahead by asynchronous copies, so that the warps of a group
+  // never have to meet for it
+  int key_seg[8][2][kTileN];
+  int key_end[8][2][kTileN];
   float row_max[2][kTileM];
   float row_sum[2][kTileM];
   int red_min_lo, red_max_hi, has_dummy;
@@ -175,21 +177,24 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
   const uint32_t o_mine = tmem + kOutCol + grp * D + lane_base;
   const int b = grp;  // P buffer, output accumulator and document tables of this group
 
-  // document id / query bound of key slot (tile start + row), loaded one tile of this group ahead
-  int next_seg = INT_MIN, next_end = 0;
-  auto fetch_key_docs = [&](int n) {
-    next_seg = INT_MIN;
-    next_end = 0;
+  // document id / query bound of the key slots of tile n into this warp's table `buf`, four slots per lane
+  // (32 c + lane); slots beyond the tensor read as zeros (document 0, no query may see them)
+  auto fetch_key_docs = [&](int n, int buf) {
     if (docs && n < w.n_tiles) {
-      const int j = tile_first_key(n, w.first_tile, w.dummy_tile) + row;
-      if (j < a.k_len) {
-        const long long at = static_cast<long long>(batch) * a.k_len + j;
-        next_seg = __ldg(a.k_seg + at);
-        next_end = __ldg(a.k_query_end + at);
+      const int j = tile_first_key(n, w.first_tile, w.dummy_tile);
+      const long long base = static_cast<long long>(batch) * a.k_len;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int slot = j + 32 * c + lane;
+        const bool in = slot < a.k_len;
+        const long long at = base + (in ? slot : 0);
+        ptx::cp_async_4(&sm.key_seg[warp][buf][32 * c + lane], a.k_seg + at, in);
+        ptx::cp_async_4(&sm.key_end[warp][buf][32 * c + lane], a.k_query_end + at, in);
       }
     }
+    ptx::cp_async_commit();
   };
-  fetch_key_docs(grp);
+  fetch_key_docs(grp, 0);
   const int tbase = lane == 0 ? grp * 10000 + (warp & 3) * 2000 : -1;  // lane 0 of every softmax warp leaves a trace
 #define WM_TRACE(tag) if (tbase >= 0) trace_event(sm, tbase + (tag))
 
@@ -199,34 +204,24 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
     const int j0 = tile_first_key(n, w.first_tile, w.dummy_tile);
     int cls = !live || j0 >= rb.hi ? kTileNone : (j0 + kTileN <= rb.hi ? kTileFull : kTileCausal);
     if (docs) {
-      const int seg = next_seg, end = next_end;
-      sm.key_seg[b][it & 1][row] = seg;
-      sm.key_end[b][it & 1][row] = end;
-      const int smin = __reduce_min_sync(0xffffffffu, seg);
-      const int smax = __reduce_max_sync(0xffffffffu, seg);
-      const int emin = __reduce_min_sync(0xffffffffu, end);
-      if (lane == 0) {
-        sm.tile_summary[b][it & 1][warp & 3][0] = smin;
-        sm.tile_summary[b][it & 1][warp & 3][1] = smax;
-        sm.tile_summary[b][it & 1][warp & 3][2] = emin;
-      }
-      fetch_key_docs(n + 2);
-      ptx::mbar_arrive(&sm.docs_full[b]);
-      if (!wait_or_abort(sm, &sm.docs_full[b], it & 1, 30)) return;
-      if (cls != kTileNone) {
-        int tmin = sm.tile_summary[b][it & 1][0][0], tmax = sm.tile_summary[b][it & 1][0][1], tend = sm.tile_summary[b][it & 1][0][2];
-#pragma unroll
-        for (int q = 1; q < 4; ++q) {
-          tmin = min(tmin, sm.tile_summary[b][it & 1][q][0]);
-          tmax = max(tmax, sm.tile_summary[b][it & 1][q][1]);
-          tend = min(tend, sm.tile_summary[b][it & 1][q][2]);
-        }
-        const bool uniform = tmin == tmax;
-        const bool own_doc = uniform && tmin == rb.seg && j0 >= rb.lo && tend > rb.qi;
-        if (uniform && tmin != -1 && tmin != rb.seg) {
-          cls = kTileNone;
-        } else if (!own_doc) {
-          cls = kTileDocs;
+      fetch_key_docs(n + 2, (it + 1) & 1);
+      ptx::cp_async_wait_all_but_last();  // this tile's table has landed; the next one may still be on its way
+      __syncwarp();
+      {
+        // the tile's summary, formed by the whole warp (every lane takes part whatever its row's class)
+        const int* tseg = sm.key_seg[warp][it & 1];
+        const int* tend_of = sm.key_end[warp][it & 1];
+        const int tmin = __reduce_min_sync(0xffffffffu, min(min(tseg[lane], tseg[32 + lane]), min(tseg[64 + lane], tseg[96 + lane])));
+        const int tmax = __reduce_max_sync(0xffffffffu, max(max(tseg[lane], tseg[32 + lane]), max(tseg[64 + lane], tseg[96 + lane])));
+        const int tend = __reduce_min_sync(0xffffffffu, min(min(tend_of[lane], tend_of[32 + lane]), min(tend_of[64 + lane], tend_of[96 + lane])));
+        if (cls != kTileNone) {
+          const bool uniform = tmin == tmax;
+          const bool own_doc = uniform && tmin == rb.seg && j0 >= rb.lo && tend > rb.qi;
+          if (uniform && tmin != -1 && tmin != rb.seg) {
+            cls = kTileNone;
+          } else if (!own_doc) {
+            cls = kTileDocs;
+          }
         }
       }
     }
@@ -255,7 +250,7 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
     if (!warp_full && !warp_none) {
       uint32_t dm[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
       if (__any_sync(0xffffffffu, cls == kTileDocs))
-        warp_doc_masks(rb, cls == kTileDocs, j0, sm.key_seg[b][it & 1], sm.key_end[b][it & 1], dm);
+        warp_doc_masks(rb, cls == kTileDocs, j0, sm.key_seg[warp][it & 1], sm.key_end[warp][it & 1], dm);
       auto causal_mask = [&](int col0) -> uint32_t {
         const int left = lim_eff - col0;
         return left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
@@ -568,7 +563,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&sm.p_full[b], kFwdGroup);
       ptx::mbar_init(&sm.p_seen[b], 1);
-      ptx::mbar_init(&sm.docs_full[b], kFwdGroup);
     }
     ptx::mbar_init(&sm.sum_full, kFwdSoftmax);
     ptx::mbar_fence_init();
