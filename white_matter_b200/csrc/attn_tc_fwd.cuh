@@ -545,6 +545,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     if (live) rb = row_bound(a, g, batch, rb.qi);
   }
 
+  // is key slot 0 the shared dummy?  Asked for at entry by a thread without a row, used after the first barrier
+  int slot0_seg = 0;
+  if (tid == kFwdThreads - 1 && a.q_seg != nullptr) slot0_seg = __ldg(a.k_seg + static_cast<long long>(batch) * a.k_len);
   if (tid == 0) {
     sm.red_min_lo = INT_MAX;
     sm.red_max_hi = 0;
@@ -586,7 +589,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     for (int h = 0; h < kSub; ++h) ptx::tma_load_4d(sm.q + h * kSubBytes, &map_q, &sm.q_full, 64 * h, q0, head, batch);
   }
   // (a thread that has no row waits for this load, beside the rows' own loads)
-  if (tid == kFwdThreads - 1) sm.has_dummy = a.q_seg != nullptr && a.k_seg[static_cast<long long>(batch) * a.k_len] == -1;
+  if (tid == kFwdThreads - 1) sm.has_dummy = a.q_seg != nullptr && slot0_seg == -1;
   if (tid < kFwdSoftmax) {
     const int lo = live && rb.hi > 0 ? rb.lo : INT_MAX;
     const int wlo = __reduce_min_sync(0xffffffffu, lo);
