@@ -158,8 +158,9 @@ struct FwdShared {
 // One softmax group (128 threads, thread = query row = TMEM lane) owns the key tiles of one parity: it keeps its
 // own running reference, row sum and output accumulator, so the two groups never exchange anything per tile and
 // drift out of phase, one in its exponentials while the other reads scores.  The two partial results are merged
-// once, in the epilogue.  A tile is read from TMEM twice (row maximum, then exponentials) in pieces of 64 columns
-// so that the scores never occupy more than 64 registers.
+// once, in the epilogue.  A tile is read from TMEM once, in pieces of 32 columns: a row exponentiates against the
+// reference it has (zero while it has none) and moves the reference afterwards; the row sum is taken over the
+// weights as rounded to bf16, so the output is an exact weighted mean whatever the reference was.
 template <int D>
 __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_args& a, uint32_t tmem, const TileWalk& w,
                                              const RowBound& rb, bool live, int batch, int head) {
@@ -287,10 +288,11 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
       if (!rescale_output(pending)) return;
       pending = 1.f;
     }
-    // Rows normally exponentiate against the reference they already have and look at the maximum afterwards
-    // (one reading of the scores).  A warp with a row that has no reference yet, or whose scores turn out to
-    // exceed the reference by more than 2^kGuard, reads the tile twice: maximum first, exponentials second.
-    bool exact = __any_sync(0xffffffffu, cls != kTileNone && m_ref == -INFINITY);
+    // Rows exponentiate against the reference they already have -- zero for a row that has none yet -- and look at
+    // the maximum afterwards (one reading of the scores).  A warp with a row whose scores turn out to exceed the
+    // reference by more than 2^kGuard (or, for a row on its provisional zero, to lie more than 2^kGuard below it)
+    // moves that row's reference to the tile's maximum and exponentiates once more: the scores are still there.
+    bool fresh = m_ref == -INFINITY;
     float tile_sum = 0.f, tmax = -INFINITY;
     // P as packed bf16 over the first 64 columns of the score buffer, all of which have been read by then
     if (warp_none) {
@@ -300,42 +302,6 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
       ptx::tmem_st32(s_tmem, zeros);
       ptx::tmem_st32(s_tmem + 32, zeros);
     } else {
-      if (exact) {
-        uint32_t r0[32], r1[32], r2[32], r3[32];
-        ptx::tmem_ld32(s_tmem, r0);
-        ptx::tmem_ld32(s_tmem + 32, r1);
-        ptx::tmem_ld32(s_tmem + 64, r2);
-        ptx::tmem_ld32(s_tmem + 96, r3);
-        ptx::tmem_wait_ld();
-        auto max32 = [&](const uint32_t (&raw)[32], uint32_t mask) -> float {
-          float t0 = -INFINITY, t1 = -INFINITY;
-          if (warp_full) {
-#pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              t0 = fmax3(t0, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
-              t1 = fmax3(t1, __uint_as_float(raw[e + 2]), __uint_as_float(raw[e + 3]));
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              t0 = fmax3(t0, (mask >> e) & 1u ? __uint_as_float(raw[e]) : -INFINITY,
-                         (mask >> (e + 1)) & 1u ? __uint_as_float(raw[e + 1]) : -INFINITY);
-              t1 = fmax3(t1, (mask >> (e + 2)) & 1u ? __uint_as_float(raw[e + 2]) : -INFINITY,
-                         (mask >> (e + 3)) & 1u ? __uint_as_float(raw[e + 3]) : -INFINITY);
-            }
-          }
-          return fmaxf(t0, t1);
-        };
-        const float top =
-            fmaxf(fmaxf(max32(r0, vis0), max32(r1, vis1)), fmaxf(max32(r2, vis2), max32(r3, vis3))) * sl2;
-        float corr = 1.f;
-        if (top > m_ref + kRescaleThreshold || (m_ref == -INFINITY && top > -INFINITY)) {
-          corr = m_ref != -INFINITY ? fast_exp2(m_ref - top) : 1.f;
-          m_ref = top;
-          l *= corr;
-        }
-        if (__any_sync(0xffffffffu, corr != 1.f) && !rescale_output(corr)) return;
-      }
       uint32_t pk0[16], pk1[16], pk2[16], pk3[16];
       // all 128 columns against the current reference: packed P, row sum and the largest exponent
       auto exponentiate = [&]() {
@@ -369,13 +335,19 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
             t[u].x = fast_exp2(t[u].x);
             t[u].y = fast_exp2(t[u].y);
           }
+          // the row sum is taken over the weights as the PV product will see them (rounded to bf16): the output is
+          // then an exact weighted mean of the value rows, whatever reference the weights were formed against
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            pk[u] = pack_bf16(t[u].x, t[u].y);
+            t[u].x = __uint_as_float(pk[u] << 16);
+            t[u].y = __uint_as_float(pk[u] & 0xffff0000u);
+          }
 #pragma unroll
           for (int u = 0; u < 16; u += 4) {
             s0 = __fadd2_rn(s0, __fadd2_rn(t[u], t[u + 1]));
             s1 = __fadd2_rn(s1, __fadd2_rn(t[u + 2], t[u + 3]));
           }
-#pragma unroll
-          for (int u = 0; u < 16; ++u) pk[u] = pack_bf16(t[u].x, t[u].y);
         };
         uint32_t even[32], odd[32];
         ptx::tmem_ld32(s_tmem, even);
@@ -394,18 +366,20 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
         tmax = fmaxf(g0, g1);
       };
       exponentiate();
-      if (!exact && __any_sync(0xffffffffu, tmax > kGuard)) {
-        // the tile outgrew its reference by so much that the exponentials may have overflowed: move the
-        // reference of those rows to the tile maximum and exponentiate once more (the scores are still there)
+      const bool redo = tmax > kGuard || (fresh && tmax < -kGuard && tmax > -INFINITY);
+      if (__any_sync(0xffffffffu, redo)) {
         float corr = 1.f;
-        if (tmax > kGuard) {
-          m_ref += tmax;
-          corr = fast_exp2(-tmax);
+        if (redo) {
+          // what has been summed so far (nothing, for a row on its provisional zero) goes over to the new reference
+          corr = fresh ? 1.f : fast_exp2(-tmax);
+          m_ref = (fresh ? 0.f : m_ref) + tmax;
           l *= corr;
+          fresh = false;
         }
         if (!rescale_output(corr)) return;
         exponentiate();
       }
+      if (fresh && tmax > -INFINITY) m_ref = 0.f;  // the row has summed against the provisional zero: that is its reference now
       uint32_t lo[32], hi[32];
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
