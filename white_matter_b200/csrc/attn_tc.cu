@@ -478,10 +478,9 @@ int tc_attn_bwd(const wm_attn_args& a, cudaStream_t stream) {
   if (status != WM_OK) return status;
   status = make_map(&map_g, a.dout, a.batch, a.q_heads, a.q_len, a.dout_strides, kTileM, a.head_dim);
   if (status != WM_OK) return status;
-  const unsigned delta_blocks = static_cast<unsigned>((rows + 127) / 128);
-  if (a.head_dim == 64) bwd_delta_kernel<8><<<delta_blocks, 128, 0, stream>>>(a, delta);
-  else if (a.head_dim == 96) bwd_delta_kernel<12><<<delta_blocks, 128, 0, stream>>>(a, delta);
-  else bwd_delta_kernel<16><<<delta_blocks, 128, 0, stream>>>(a, delta);
+  if (a.head_dim == 64) bwd_delta_kernel<8, 8><<<static_cast<unsigned>((rows * 8 + 255) / 256), 256, 0, stream>>>(a, delta);
+  else if (a.head_dim == 96) bwd_delta_kernel<12, 16><<<static_cast<unsigned>((rows * 16 + 255) / 256), 256, 0, stream>>>(a, delta);
+  else bwd_delta_kernel<16, 16><<<static_cast<unsigned>((rows * 16 + 255) / 256), 256, 0, stream>>>(a, delta);
   count_launch();
   WM_CUDA(cudaGetLastError());
   if (bwd_short_queries(a)) {

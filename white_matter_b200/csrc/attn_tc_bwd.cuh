@@ -64,23 +64,24 @@ struct BwdShared {
   int epoch;
 };
 
-// delta = rowsum(dO * O) in fp32, one thread per (batch, head, query) row of 8 * kChunks values
-template <int kChunks>
+// delta = rowsum(dO * O) in fp32.  kLanes neighbouring lanes share a (batch, head, query) row of 8 * kChunks values,
+// 16 bytes of O and of dO each (a warp reads whole 128-byte lines), and add their parts up with shuffles.
+template <int kChunks, int kLanes>
 __global__ void bwd_delta_kernel(const wm_attn_args a, float* delta) {
+  static_assert(kLanes >= kChunks && (kLanes & (kLanes - 1)) == 0 && kLanes <= 32, "lanes per row");
   const long long rows = static_cast<long long>(a.batch) * a.q_heads * a.q_len;
-  const long long row = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (row >= rows) return;
-  const int i = static_cast<int>(row % a.q_len);
-  const int h = static_cast<int>((row / a.q_len) % a.q_heads);
-  const int b = static_cast<int>(row / (static_cast<long long>(a.q_len) * a.q_heads));
-  const uint4* o = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.out) + b * a.out_strides[0] +
-                                                  h * a.out_strides[1] + static_cast<long long>(i) * a.out_strides[2]);
-  const uint4* g = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.dout) + b * a.dout_strides[0] +
-                                                  h * a.dout_strides[1] + static_cast<long long>(i) * a.dout_strides[2]);
+  const long long at = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long row = at / kLanes;
+  const int c = static_cast<int>(at % kLanes);
   float acc = 0.f;
-#pragma unroll
-  for (int c = 0; c < kChunks; ++c) {
-    const uint4 x = o[c], y = g[c];
+  if (row < rows && c < kChunks) {
+    const int i = static_cast<int>(row % a.q_len);
+    const int h = static_cast<int>((row / a.q_len) % a.q_heads);
+    const int b = static_cast<int>(row / (static_cast<long long>(a.q_len) * a.q_heads));
+    const uint4 x = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.out) + b * a.out_strides[0] +
+                                                   h * a.out_strides[1] + static_cast<long long>(i) * a.out_strides[2])[c];
+    const uint4 y = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.dout) + b * a.dout_strides[0] +
+                                                   h * a.dout_strides[1] + static_cast<long long>(i) * a.dout_strides[2])[c];
     const unsigned xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -88,7 +89,9 @@ __global__ void bwd_delta_kernel(const wm_attn_args a, float* delta) {
       acc = fmaf(__uint_as_float(xs[e] & 0xffff0000u), __uint_as_float(ys[e] & 0xffff0000u), acc);
     }
   }
-  delta[row] = acc;
+#pragma unroll
+  for (int step = kLanes / 2; step > 0; step >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, step);
+  if (row < rows && c == 0) delta[row] = acc;
 }
 
 // dq = bf16(scale * accumulator); accumulator is (batch, heads, queries, head_dim) fp32
