@@ -148,7 +148,7 @@ struct FwdShared {
   int key_end[8][2][kTileN];
   float row_max[2][kTileM];
   float row_sum[2][kTileM];
-  int red_min_lo, red_max_hi, has_dummy;
+  int warp_min_lo[4], warp_max_hi[4], has_dummy;
   uint32_t tmem_base;
   int abort_flag;
   int epoch;
@@ -519,42 +519,30 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     if (live) rb = row_bound(a, g, batch, rb.qi);
   }
 
-  // is key slot 0 the shared dummy?  Asked for at entry by a thread without a row, used after the first barrier
-  int slot0_seg = 0;
-  if (tid == kFwdThreads - 1 && a.q_seg != nullptr) slot0_seg = __ldg(a.k_seg + static_cast<long long>(batch) * a.k_len);
-  if (tid == 0) {
-    sm.red_min_lo = INT_MAX;
-    sm.red_max_hi = 0;
-    sm.abort_flag = 0;
-    sm.epoch = epoch;
-    trace_begin(sm, epoch);
-    ptx::mbar_init(&sm.q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(&sm.k_full[s], 1);
-      ptx::mbar_init(&sm.v_full[s], 1);
-      ptx::mbar_init(&sm.pv_done[s], 1);
+  // Block set-up, one barrier for all of it.  The barriers are initialised by the first lanes of warp 0, a few each
+  // (one thread doing all eighteen took 2 000 cycles and was what the block waited for); the producer lane sets up
+  // the query tile's barrier itself and asks for the tile at once; warp 9 allocates tensor memory; the rows reduce
+  // their bounds to one pair per warp; a thread without a row asks whether key slot 0 is the shared dummy.
+  {
+    // the barriers from k_full to sum_full lie side by side: lane i of warp 0 initialises the i-th, in one instruction
+    constexpr int kBarriers = 4 * kStages + 5;
+    static_assert(offsetof(FwdShared<D>, sum_full) - offsetof(FwdShared<D>, k_full) == (kBarriers - 1) * sizeof(uint64_t),
+                  "the barriers of the forward are expected to be contiguous");
+    if (tid < kBarriers) {
+      const int count = tid < 4 * kStages ? 1 : (tid < 4 * kStages + 2 ? kFwdGroup : (tid < 4 * kStages + 4 ? 1 : kFwdSoftmax));
+      ptx::mbar_init(sm.k_full + tid, count);
+      ptx::mbar_fence_init();
     }
-    for (int b = 0; b < kScoreBuffers; ++b) {
-      ptx::mbar_init(&sm.s_full[b], 1);
+    if (tid == 0) {
+      sm.abort_flag = 0;
+      sm.epoch = epoch;
+      trace_begin(sm, epoch);
     }
-    for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(&sm.p_full[b], kFwdGroup);
-      ptx::mbar_init(&sm.p_seen[b], 1);
-    }
-    ptx::mbar_init(&sm.sum_full, kFwdSoftmax);
-    ptx::mbar_fence_init();
   }
-  if (warp == 8) {
-    ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
   if (tid == 8 * 32) {
     // the query tile does not depend on the key walk: it is on its way while the rows find their bounds
-    trace_event(sm, 1);
+    ptx::mbar_init(&sm.q_full, 1);
+    ptx::mbar_fence_init();
     ptx::prefetch_tmap(&map_q);
     ptx::prefetch_tmap(&map_k);
     ptx::prefetch_tmap(&map_v);
@@ -562,20 +550,30 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 #pragma unroll
     for (int h = 0; h < kSub; ++h) ptx::tma_load_4d(sm.q + h * kSubBytes, &map_q, &sm.q_full, 64 * h, q0, head, batch);
   }
-  // (a thread that has no row waits for this load, beside the rows' own loads)
-  if (tid == kFwdThreads - 1) sm.has_dummy = a.q_seg != nullptr && slot0_seg == -1;
-  if (tid < kFwdSoftmax) {
+  if (warp == 9) {
+    ptx::tmem_alloc(&sm.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (tid == kFwdThreads - 1)
+    sm.has_dummy = a.q_seg != nullptr && __ldg(a.k_seg + static_cast<long long>(batch) * a.k_len) == -1;
+  if (tid < kTileM) {
+    // (the second softmax group has the same rows)
     const int lo = live && rb.hi > 0 ? rb.lo : INT_MAX;
     const int wlo = __reduce_min_sync(0xffffffffu, lo);
     const int whi = __reduce_max_sync(0xffffffffu, rb.hi);
-    if (lane == 0 && tid < kTileM) {
-      atomicMin(&sm.red_min_lo, wlo);
-      atomicMax(&sm.red_max_hi, whi);
+    if (lane == 0) {
+      sm.warp_min_lo[warp] = wlo;
+      sm.warp_max_hi[warp] = whi;
     }
   }
+  ptx::tc_fence_before();
   __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const int red_min_lo = min(min(sm.warp_min_lo[0], sm.warp_min_lo[1]), min(sm.warp_min_lo[2], sm.warp_min_lo[3]));
+  const int red_max_hi = max(max(sm.warp_max_hi[0], sm.warp_max_hi[1]), max(sm.warp_max_hi[2], sm.warp_max_hi[3]));
   TileWalk w;
-  w.kmax = sm.red_max_hi;
+  w.kmax = red_max_hi;
   if (w.kmax == 0) {
     // no row of the tile sees a key: zeros and +inf, then the common exit (the query tile still has to land)
     if (live) {
@@ -590,7 +588,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     if (tid == 0) wait_or_abort(sm, &sm.q_full, 0, 20);
   } else {
     const int end_tile = (w.kmax + kTileN - 1) / kTileN;
-    w.first_tile = a.q_seg != nullptr ? min(sm.red_min_lo / kTileN, end_tile - 1) : 0;
+    w.first_tile = a.q_seg != nullptr ? min(red_min_lo / kTileN, end_tile - 1) : 0;
     w.dummy_tile = (a.q_seg != nullptr && sm.has_dummy && w.first_tile > 0) ? 1 : 0;
     w.n_tiles = end_tile - w.first_tile + w.dummy_tile;
     if (warp < 8) {
@@ -604,5 +602,5 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   ptx::tc_fence_before();
   __syncthreads();
   trace_flush(sm);
-  if (warp == 8) ptx::tmem_dealloc(tmem, kTmemCols);
+  if (warp == 9) ptx::tmem_dealloc(tmem, kTmemCols);
 }
