@@ -308,7 +308,7 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
         const float2 sc = make_float2(sl2, sl2), nm = make_float2(-m_use, -m_use);
         float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
-        float g0 = -INFINITY, g1 = -INFINITY;
+        float g0 = -INFINITY, g1 = -INFINITY, g2 = -INFINITY, g3 = -INFINITY;
         // 32 columns at a time keep the live registers (scores + packed P of the whole tile) under the limit;
         // the load of the next piece is in flight while this one is exponentiated
         auto piece = [&](uint32_t (&raw)[32], uint32_t mask, uint32_t (&pk)[16]) {
@@ -326,9 +326,11 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
 #pragma unroll
           for (int u = 0; u < 16; ++u) t[u] = __ffma2_rn(make_float2(x[2 * u], x[2 * u + 1]), sc, nm);
 #pragma unroll
-          for (int u = 0; u < 16; u += 4) {
-            g0 = fmax3(g0, fmaxf(t[u].x, t[u].y), fmaxf(t[u + 1].x, t[u + 1].y));
-            g1 = fmax3(g1, fmaxf(t[u + 2].x, t[u + 2].y), fmaxf(t[u + 3].x, t[u + 3].y));
+          for (int u = 0; u < 16; u += 4) {  // three-input maxima: two new values per instruction, four chains
+            g0 = fmax3(g0, t[u].x, t[u].y);
+            g1 = fmax3(g1, t[u + 1].x, t[u + 1].y);
+            g2 = fmax3(g2, t[u + 2].x, t[u + 2].y);
+            g3 = fmax3(g3, t[u + 3].x, t[u + 3].y);
           }
 #pragma unroll
           for (int u = 0; u < 16; ++u) {
@@ -363,7 +365,7 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
         ptx::tmem_wait_ld();
         piece(odd, vis3, pk3);
         tile_sum = (s0.x + s0.y) + (s1.x + s1.y);
-        tmax = fmaxf(g0, g1);
+        tmax = fmaxf(fmaxf(g0, g1), fmaxf(g2, g3));
       };
       exponentiate();
       const bool redo = tmax > kGuard || (fresh && tmax < -kGuard && tmax > -INFINITY);
