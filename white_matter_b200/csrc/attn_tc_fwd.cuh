@@ -338,17 +338,13 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
             t[u].y = fast_exp2(t[u].y);
           }
           // the row sum is taken over the weights as the PV product will see them (rounded to bf16): the output is
-          // then an exact weighted mean of the value rows, whatever reference the weights were formed against
+          // then an exact weighted mean of the value rows, whatever reference the weights were formed against.  The
+          // halves of a packed pair are added to fp32 sums as they are (mixed-precision add), without unpacking.
 #pragma unroll
           for (int u = 0; u < 16; ++u) {
             pk[u] = pack_bf16(t[u].x, t[u].y);
-            t[u].x = __uint_as_float(pk[u] << 16);
-            t[u].y = __uint_as_float(pk[u] & 0xffff0000u);
-          }
-#pragma unroll
-          for (int u = 0; u < 16; u += 4) {
-            s0 = __fadd2_rn(s0, __fadd2_rn(t[u], t[u + 1]));
-            s1 = __fadd2_rn(s1, __fadd2_rn(t[u + 2], t[u + 3]));
+            if (u & 1) ptx::add_bf16_halves(pk[u], s1.x, s1.y);
+            else ptx::add_bf16_halves(pk[u], s0.x, s0.y);
           }
         };
         uint32_t even[32], odd[32];

@@ -113,6 +113,18 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 // waits until at most the most recently committed group of this thread is still in flight
 __device__ __forceinline__ void cp_async_wait_all_but_last() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
+// lo += low bf16 half of `packed`, hi += high bf16 half (fp32 sums, the bf16 values taken as they are)
+__device__ __forceinline__ void add_bf16_halves(uint32_t packed, float& lo, float& hi) {
+  asm("{\n"
+      ".reg .b16 l, h;\n"
+      "mov.b32 {l, h}, %2;\n"
+      "add.rn.f32.bf16 %0, l, %0;\n"
+      "add.rn.f32.bf16 %1, h, %1;\n"
+      "}\n"
+      : "+f"(lo), "+f"(hi)
+      : "r"(packed));
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
