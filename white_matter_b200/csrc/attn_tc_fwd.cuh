@@ -174,7 +174,8 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
   const bool docs = a.q_seg != nullptr;
   float m_ref = -INFINITY, l = 0.f;
   float pending = 1.f;  // factor the accumulator still has to be multiplied by
-  constexpr float kGuard = 64.f;  // log2 units a tile may exceed its reference by before it is read twice
+  constexpr float kSumGuard = 1.0995116e12f;  // 2^40: a row sum beyond it sends the tile back for its true maximum
+  constexpr float kSumMove = 4096.f;          // 2^12: a row sum beyond it moves the reference for the tiles to come
   const uint32_t o_mine = tmem + kOutCol + grp * D + lane_base;
   const int b = grp;  // P buffer, output accumulator and document tables of this group
 
@@ -247,20 +248,26 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
     const int lim_eff = cls == kTileFull ? kTileN : (cls == kTileNone ? 0 : lim);
     // visibility of 32 columns as a bit mask: arithmetic for the causal bound, and the key tile's document table
     // (looked at by the whole warp together) for rows whose tile contains a document boundary
-    uint32_t vis0 = 0xffffffffu, vis1 = 0xffffffffu, vis2 = 0xffffffffu, vis3 = 0xffffffffu;
-    if (!warp_full && !warp_none) {
-      uint32_t dm[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-      if (__any_sync(0xffffffffu, cls == kTileDocs))
-        warp_doc_masks(rb, cls == kTileDocs, j0, sm.key_seg[warp][it & 1], sm.key_end[warp][it & 1], dm);
-      auto causal_mask = [&](int col0) -> uint32_t {
-        const int left = lim_eff - col0;
-        return left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
-      };
-      vis0 = causal_mask(0) & dm[0] & km0;
-      vis1 = causal_mask(32) & dm[1] & km1;
-      vis2 = causal_mask(64) & dm[2] & km2;
-      vis3 = causal_mask(96) & dm[3] & km3;
-    }
+    auto visibility = [&](uint32_t& v0, uint32_t& v1, uint32_t& v2, uint32_t& v3) {
+      v0 = v1 = v2 = v3 = 0xffffffffu;
+      if (!warp_full && !warp_none) {
+        uint32_t dm[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        if (__any_sync(0xffffffffu, cls == kTileDocs))
+          warp_doc_masks(rb, cls == kTileDocs, j0, sm.key_seg[warp][it & 1], sm.key_end[warp][it & 1], dm);
+        auto causal_mask = [&](int col0) -> uint32_t {
+          const int left = lim_eff - col0;
+          return left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
+        };
+        v0 = causal_mask(0) & dm[0] & km0;
+        v1 = causal_mask(32) & dm[1] & km1;
+        v2 = causal_mask(64) & dm[2] & km2;
+        v3 = causal_mask(96) & dm[3] & km3;
+      }
+    };
+    uint32_t vis0, vis1, vis2, vis3;
+    visibility(vis0, vis1, vis2, vis3);
+    // does the row see any column of this tile?
+    const bool seen = cls != kTileNone && (warp_full || (vis0 | vis1 | vis2 | vis3) != 0u);
     const uint32_t s_tmem = tmem + static_cast<uint32_t>(sb) * kTileN + lane_base;
     if (!wait_or_abort(sm, &sm.s_full[sb], (n / kScoreBuffers) & 1, 31)) return;
     ptx::tc_fence_after();
@@ -293,7 +300,7 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
     // reference by more than 2^kGuard (or, for a row on its provisional zero, to lie more than 2^kGuard below it)
     // moves that row's reference to the tile's maximum and exponentiates once more: the scores are still there.
     bool fresh = m_ref == -INFINITY;
-    float tile_sum = 0.f, tmax = -INFINITY;
+    float tile_sum = 0.f;
     // P as packed bf16 over the first 64 columns of the score buffer, all of which have been read by then
     if (warp_none) {
       uint32_t zeros[32];
@@ -303,12 +310,11 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
       ptx::tmem_st32(s_tmem + 32, zeros);
     } else {
       uint32_t pk0[16], pk1[16], pk2[16], pk3[16];
-      // all 128 columns against the current reference: packed P, row sum and the largest exponent
+      // all 128 columns against the current reference: packed P and the row sum
       auto exponentiate = [&]() {
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
         const float2 sc = make_float2(sl2, sl2), nm = make_float2(-m_use, -m_use);
         float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
-        float g0 = -INFINITY, g1 = -INFINITY, g2 = -INFINITY, g3 = -INFINITY;
         // 32 columns at a time keep the live registers (scores + packed P of the whole tile) under the limit;
         // the load of the next piece is in flight while this one is exponentiated
         auto piece = [&](uint32_t (&raw)[32], uint32_t mask, uint32_t (&pk)[16]) {
@@ -325,13 +331,6 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
           float2 t[16];
 #pragma unroll
           for (int u = 0; u < 16; ++u) t[u] = __ffma2_rn(make_float2(x[2 * u], x[2 * u + 1]), sc, nm);
-#pragma unroll
-          for (int u = 0; u < 16; u += 4) {  // three-input maxima: two new values per instruction, four chains
-            g0 = fmax3(g0, t[u].x, t[u].y);
-            g1 = fmax3(g1, t[u + 1].x, t[u + 1].y);
-            g2 = fmax3(g2, t[u + 2].x, t[u + 2].y);
-            g3 = fmax3(g3, t[u + 3].x, t[u + 3].y);
-          }
 #pragma unroll
           for (int u = 0; u < 16; ++u) {
             t[u].x = fast_exp2(t[u].x);
@@ -361,23 +360,41 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
         ptx::tmem_wait_ld();
         piece(odd, vis3, pk3);
         tile_sum = (s0.x + s0.y) + (s1.x + s1.y);
-        tmax = fmaxf(fmaxf(g0, g1), fmaxf(g2, g3));
       };
       exponentiate();
-      const bool redo = tmax > kGuard || (fresh && tmax < -kGuard && tmax > -INFINITY);
+      // The row sum tells whether the reference served: a sum beyond 2^kGuard (or not finite: the exponentials
+      // overflowed), or a row on its provisional zero whose visible scores all vanished, sends the warp back to the
+      // scores (they are still in tensor memory) for the row's true maximum, which becomes its reference.
+      const bool redo = !(tile_sum < kSumGuard) || (fresh && seen && tile_sum == 0.f);
       if (__any_sync(0xffffffffu, redo)) {
+        float top = -INFINITY;
+        auto piece_max = [&](int c, uint32_t mask) {
+          uint32_t raw[32];
+          ptx::tmem_ld32(s_tmem + 32 * c, raw);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            top = fmaxf(top, warp_full || ((mask >> e) & 1u) ? __uint_as_float(raw[e]) : -INFINITY);
+        };
+        uint32_t m0, m1, m2, m3;  // (formed again rather than kept alive across the exponentials)
+        visibility(m0, m1, m2, m3);
+        piece_max(0, m0);
+        piece_max(1, m1);
+        piece_max(2, m2);
+        piece_max(3, m3);
+        top *= sl2;
         float corr = 1.f;
-        if (redo) {
+        if (redo && top > -INFINITY) {
           // what has been summed so far (nothing, for a row on its provisional zero) goes over to the new reference
-          corr = fresh ? 1.f : fast_exp2(-tmax);
-          m_ref = (fresh ? 0.f : m_ref) + tmax;
+          corr = fresh ? 1.f : fast_exp2(m_ref - top);
+          m_ref = top;
           l *= corr;
           fresh = false;
         }
         if (!rescale_output(corr)) return;
         exponentiate();
       }
-      if (fresh && tmax > -INFINITY) m_ref = 0.f;  // the row has summed against the provisional zero: that is its reference now
+      if (fresh && seen) m_ref = 0.f;  // the row has summed against the provisional zero: that is its reference now
       uint32_t lo[32], hi[32];
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
@@ -390,10 +407,12 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
       ptx::tmem_st32(s_tmem + 32, hi);
     }
     l += tile_sum;
-    if (tmax > kRescaleThreshold && n + 2 < w.n_tiles) {
-      // the tile outgrew the reference: move it for the tiles to come
-      m_ref += tmax;
-      pending = fast_exp2(-tmax);
+    if (tile_sum > kSumMove && n + 2 < w.n_tiles) {
+      // the tile outgrew the reference (its largest weight lies between 2^-7 and 1 of the sum): move the reference
+      // by the sum's logarithm for the tiles to come
+      const float shift = log2f(tile_sum);
+      m_ref += shift;
+      pending = fast_exp2(-shift);
       l *= pending;
     }
     ptx::tmem_wait_st();
