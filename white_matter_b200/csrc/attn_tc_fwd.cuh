@@ -159,8 +159,9 @@ struct FwdShared {
 // own running reference, row sum and output accumulator, so the two groups never exchange anything per tile and
 // drift out of phase, one in its exponentials while the other reads scores.  The two partial results are merged
 // once, in the epilogue.  A tile is read from TMEM once, in pieces of 32 columns: a row exponentiates against the
-// reference it has (zero while it has none) and moves the reference afterwards; the row sum is taken over the
-// weights as rounded to bf16, so the output is an exact weighted mean whatever the reference was.
+// reference it has (zero while it has none) and judges the reference afterwards by the row sum (no maximum is formed
+// per element); the row sum is taken over the weights as rounded to bf16, so the output is an exact weighted mean
+// whatever the reference was.
 template <int D>
 __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_args& a, uint32_t tmem, const TileWalk& w,
                                              const RowBound& rb, bool live, int batch, int head) {
