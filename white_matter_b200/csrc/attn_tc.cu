@@ -26,7 +26,6 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kTileN = 128;
 constexpr int kHeadDim = 64;
-constexpr int kStages = 3;
 constexpr int kSoftmaxThreads = 128;
 constexpr uint32_t kTileBytes = kTileN * kHeadDim * 2;  // 16 KB: one Q, K or V tile
 constexpr uint32_t kTmemCols = 512;

@@ -192,7 +192,6 @@ int check(const wm_mix_args& a, bool backward) {
   if (a.dtype != WM_F32 && a.dtype != WM_BF16) return fail(WM_EINVAL, "mixing supports fp32 and bf16");
   if (a.n < 0 || a.sources == nullptr || a.logits == nullptr) return fail(WM_EINVAL, "mixing needs sources and logits");
   int vec = a.dtype == WM_F32 ? 4 : 8;
-  size_t es = a.dtype == WM_F32 ? 4 : 2;
   if (a.source_stride % vec || reinterpret_cast<uintptr_t>(a.sources) % 16)
     return fail(WM_EUNSUPPORTED, "sources must be 16-byte aligned with a stride that is a multiple of %d elements", vec);
   if (!backward && (a.out == nullptr || reinterpret_cast<uintptr_t>(a.out) % 16))
@@ -204,7 +203,6 @@ int check(const wm_mix_args& a, bool backward) {
     if (a.dlogits != nullptr && (a.workspace == nullptr || a.workspace_bytes < kMaxSources * sizeof(float)))
       return fail(WM_EWORKSPACE, "mixing backward needs %zu workspace bytes", kMaxSources * sizeof(float));
   }
-  (void)es;
   return WM_OK;
 }
 
