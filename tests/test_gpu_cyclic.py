@@ -274,6 +274,27 @@ def test_scores_that_outgrow_the_running_reference(boost, backend):
             assert cos > 0.995, f"{name}: cosine {cos}"
 
 
+@pytest.mark.parametrize("level", [-60.0, -90.0, -150.0, 120.0])
+def test_scores_far_from_zero_everywhere(level):
+    """All scores of a row near a large negative (or positive) level: the weights formed against the provisional
+    zero reference of a row's first tile would be tiny, subnormal or zero (or overflow); the result must not care."""
+    torch.manual_seed(11)
+    T, S, D = 512, 2, 64
+    u = torch.nn.functional.normalize(torch.randn(D), dim=0)
+    c = (abs(level) * D ** 0.5) ** 0.5
+    q = 0.3 * torch.randn(1, 2, T // S, D) + c * u
+    k = 0.3 * torch.randn(1, 2, T, D) + (c if level > 0 else -c) * u
+    v = torch.randn(1, 2, T, D)
+    q, k, v = (t.bfloat16() for t in (q, k, v))
+    from white_matter_b200 import _native
+
+    with torch.no_grad():
+        out = cyclic_attention(q.cuda(), k.cuda(), v.cuda(), query_stride=S, query_offset=0, backend="sm100_tcgen05")
+    assert _native.device_status(True) == 0
+    exp = oracle.cyclic_attention_oracle(q.double(), k.double(), v.double(), query_stride=S, query_offset=0)
+    assert_parity(out.float(), exp, what=f"out at level {level}", **BF16_TOL)
+
+
 def test_many_launches_leave_the_status_word_clean():
     """The pipelined kernels synchronise their roles through parity barriers with bounded waits: a protocol slip
     shows as a wait that gives up (status word != 0), typically once in hundreds of launches.  Several hundred

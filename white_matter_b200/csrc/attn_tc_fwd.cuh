@@ -177,6 +177,7 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
   float pending = 1.f;  // factor the accumulator still has to be multiplied by
   constexpr float kSumGuard = 1.0995116e12f;  // 2^40: a row sum beyond it sends the tile back for its true maximum
   constexpr float kSumMove = 4096.f;          // 2^12: a row sum beyond it moves the reference for the tiles to come
+  constexpr float kSumTiny = 7.8886091e-31f;  // 2^-100: a row on its provisional zero whose first sum is smaller asks for its true maximum
   const uint32_t o_mine = tmem + kOutCol + grp * D + lane_base;
   const int b = grp;  // P buffer, output accumulator and document tables of this group
 
@@ -364,9 +365,9 @@ __device__ __forceinline__ void softmax_role(FwdShared<D>& sm, const wm_attn_arg
       };
       exponentiate();
       // The row sum tells whether the reference served: a sum beyond 2^kGuard (or not finite: the exponentials
-      // overflowed), or a row on its provisional zero whose visible scores all vanished, sends the warp back to the
+      // overflowed), or a row on its provisional zero whose visible weights (nearly) vanished, sends the warp back to the
       // scores (they are still in tensor memory) for the row's true maximum, which becomes its reference.
-      const bool redo = !(tile_sum < kSumGuard) || (fresh && seen && tile_sum == 0.f);
+      const bool redo = !(tile_sum < kSumGuard) || (fresh && seen && tile_sum < kSumTiny);
       if (__any_sync(0xffffffffu, redo)) {
         float top = -INFINITY;
         auto piece_max = [&](int c, uint32_t mask) {
